@@ -1,0 +1,121 @@
+// Shared device/host declarations of the bmtk_b200 engine (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/bmtk_b200.h"
+
+namespace bmtk {
+
+constexpr int kPorts = BMTK_MAX_PORTS;
+// A window spike-list entry packs (step inside the window, global source id).
+constexpr int kStepBits = 5;
+constexpr int kSrcBits = 32 - kStepBits;
+constexpr uint32_t kSrcMask = (1u << kSrcBits) - 1u;
+constexpr int kMaxWindow = 1 << kStepBits;
+
+// Sticky device-side error bits (Ctl::error_flags).
+enum : uint32_t {
+    kErrSpikeListFull = 1u,
+    kErrLogFull = 2u,
+    kErrVirtListFull = 4u,
+    kErrEventsFull = 8u,
+};
+
+// Per node type constants for one resolution, fp32 copies of fp64 host values.
+// Unused ports and disabled mechanisms are neutral values so the update is branch-free:
+// a port that does not exist has P11 = P21 = P31 = P32 = psc_init = 0; a type without
+// after-spike currents has asc_coeff = asc_amps = 0 and asc_decay = asc_refr = 1.
+struct TypeConsts {
+    float P33, P30;
+    float P11[kPorts], P21[kPorts], P31[kPorts], P32[kPorts], psc_init[kPorts];
+    float asc_decay[2], asc_coeff[2], asc_refr[2], asc_amps[2];
+    float th_inf, v_reset, E_L;
+    float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction, reset_add;
+    float phi, abpara, theta_voltage_decay, inv_G;
+    int32_t n_ref;
+    int32_t flags;  // bit0 spike-dependent threshold, bit1 adapting threshold
+};
+static_assert(sizeof(TypeConsts) % 4 == 0, "TypeConsts is copied word-wise");
+
+// Device-resident control block: everything a replayed CUDA graph needs to find its place.
+struct Ctl {
+    unsigned long long step_base;   // absolute index of the first step of the current window
+    unsigned long long n_events;    // synaptic events delivered so far
+    unsigned long long n_spikes;    // neuron spikes so far
+    unsigned long long n_input_spikes;
+    uint32_t log_count;             // entries in the spike log since the last drain
+    uint32_t error_flags;
+    uint32_t ticket;                // blocks of the window-end kernel that have finished
+    uint32_t sample_base;           // trace samples drained so far (absolute)
+    uint32_t det_items;             // deterministic path: spike rows collected this window
+    uint32_t det_events;            // deterministic path: events expanded this window
+    uint32_t pad0, pad1;
+};
+
+// Neuron state, structure of arrays; every array has n_pad entries (multiple of 4, 16-byte aligned).
+struct StateSoA {
+    float* U;        // membrane potential relative to E_L
+    float* asc0;
+    float* asc1;
+    float* y1;       // [kPorts][n_pad]
+    float* y2;       // [kPorts][n_pad]
+    int32_t* refr;
+    float* th_spike;    // nullptr unless a type uses it
+    float* th_voltage;  // nullptr unless a type uses it
+    float* i_ext;       // nullptr unless clamps exist
+    const uint16_t* type;
+};
+
+struct UpdateArgs {
+    StateSoA st;
+    const TypeConsts* types;
+    int32_t n_types;
+    uint32_t n_local, n_pad;
+    uint32_t lo;              // global id of local neuron 0
+    float* ring;              // [slots][kPorts][n_pad]
+    uint32_t ring_slots;
+    Ctl* ctl;
+    uint32_t step_in_window;  // s: this launch executes step ctl->step_base + s
+    uint32_t* send;           // [0] = count, then entries (s << kSrcBits | global id)
+    uint32_t send_cap;
+    uint32_t* log_stamp;      // spike log (nullptr = not recording)
+    uint32_t* log_id;
+    uint32_t log_cap;
+    // on-line Poisson sources (nullptr = none)
+    const uint4* poisson_thr; // per virtual source: CDF thresholds of k = 0..3
+    uint32_t n_virtual, n_global;
+    uint64_t seed;
+    uint32_t* virt;           // [0] = count, then entries, same packing as `send`
+    uint32_t virt_cap;
+};
+
+struct PropArgs {
+    const unsigned long long* rowptr;  // [n_rows + 1]
+    const uint2* entries;              // {packed, weight bits}
+    uint32_t target_bits;
+    float* ring;
+    uint32_t ring_slots, n_pad;
+    Ctl* ctl;
+    // recurrent spikes: n_seg segments of seg_stride words, word 0 = count
+    const uint32_t* gathered;
+    uint32_t n_seg, seg_stride, seg_cap;
+    // replayed virtual spikes: entries [in_ptr[step_base], in_ptr[step_base + window)) of (in_step, in_src)
+    const uint32_t* in_ptr;            // indexed by absolute step - in_ptr_base, clamped
+    unsigned long long in_ptr_base;
+    uint32_t in_ptr_len;
+    const uint32_t* in_step;
+    const uint32_t* in_src;
+    // on-line Poisson spikes of this window
+    uint32_t* virt;
+    uint32_t virt_cap;
+    uint32_t window;                   // steps this window advanced
+    uint32_t* send;                    // reset for the next window
+};
+
+// Launch wrappers (defined next to their kernels).
+cudaError_t launch_glif_update(const UpdateArgs& a, bool has_theta, bool has_iext, cudaStream_t s);
+cudaError_t launch_propagate_atomic(const PropArgs& a, cudaStream_t s);
+int glif_update_blocks(uint32_t n_pad, uint32_t n_virtual);
+
+}  // namespace bmtk

@@ -1,0 +1,1138 @@
+// Engine object and C ABI of bmtk_b200: owns device memory, builds the CSR, drives the
+// per-window kernel sequence (w x glif_update [+ snapshot] -> [all-gather] -> propagate) on one
+// stream, replays it as a CUDA graph, drains the spike log and traces to the host in chunks.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "csr_build.cuh"
+#include "propagate_det.cuh"
+
+namespace bmtk {
+
+thread_local std::string g_last_error;
+
+static int fail(int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CU(x)                                                                                     \
+    do {                                                                                          \
+        cudaError_t e_ = (x);                                                                     \
+        if (e_ != cudaSuccess)                                                                    \
+            return fail(BMTK_E_CUDA, "%s failed: %s (%s:%d)", #x, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Per-type constants (fp64 on the host, stored fp32): exact-integration propagators of the
+// linear sub-threshold system for one resolution h.
+
+// x + expm1(-x) without cancellation for small |x|.
+static double cross_term(double x) {
+    if (std::fabs(x) < 1e-3)
+        return x * x * (0.5 + x * (-1.0 / 6.0 + x * (1.0 / 24.0 + x * (-1.0 / 120.0 + x / 720.0))));
+    return x + std::expm1(-x);
+}
+
+static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& c) {
+    if (!(p.C_m > 0) || !(p.g > 0)) return fail(BMTK_E_INVALID, "C_m and g must be positive");
+    if (!(p.t_ref > 0)) return fail(BMTK_E_INVALID, "t_ref must be positive");
+    if (p.n_ports < 1 || p.n_ports > kPorts) return fail(BMTK_E_INVALID, "n_ports must be 1..%d", kPorts);
+    std::memset(&c, 0, sizeof(c));
+    const double tau = p.C_m / p.g;
+    c.P33 = (float)std::exp(-h / tau);
+    c.P30 = (float)(-std::expm1(-h / tau) / p.g);
+    for (int k = 0; k < p.n_ports; ++k) {
+        const double ts = p.tau_syn[k];
+        if (!(ts > 0)) return fail(BMTK_E_INVALID, "tau_syn must be positive");
+        const double a = 1.0 / ts, b = 1.0 / tau, d = b - a, x = d * h;
+        const double ea = std::exp(-a * h);
+        c.P11[k] = (float)ea;
+        c.P21[k] = (float)(h * ea);
+        c.psc_init[k] = (float)(std::exp(1.0) / ts);
+        if (x == 0.0) {
+            c.P32[k] = (float)(h * std::exp(-b * h) / p.C_m);
+            c.P31[k] = (float)(0.5 * h * h * std::exp(-b * h) / p.C_m);
+        } else {
+            c.P32[k] = (float)(ea * (-std::expm1(-x)) / (d * p.C_m));
+            c.P31[k] = (float)(ea * cross_term(x) / (d * d * p.C_m));
+        }
+    }
+    for (int j = 0; j < 2; ++j) {
+        if (p.after_spike_currents) {
+            const double k = p.asc_decay[j];
+            if (!(k > 0)) return fail(BMTK_E_INVALID, "asc_decay must be positive");
+            c.asc_decay[j] = (float)std::exp(-k * h);
+            c.asc_coeff[j] = (float)(-std::expm1(-k * h) / (k * h));
+            c.asc_refr[j] = (float)(p.asc_r[j] * std::exp(-k * p.t_ref));
+            c.asc_amps[j] = (float)p.asc_amps[j];
+        } else {
+            c.asc_decay[j] = 1.f;
+            c.asc_coeff[j] = 0.f;
+            c.asc_refr[j] = 1.f;
+            c.asc_amps[j] = 0.f;
+        }
+    }
+    c.th_inf = (float)(p.V_th - p.E_L);
+    c.v_reset = (float)(p.V_reset - p.E_L);
+    c.E_L = (float)p.E_L;
+    // NEST counts the refractory period down in double precision, h per step, until <= 0.
+    double r = p.t_ref;
+    int n = 0;
+    do {
+        r -= h;
+        ++n;
+    } while (r > 0.0 && n < (1 << 30));
+    c.n_ref = n;
+    c.flags = (p.spike_dependent_threshold ? 1 : 0) | (p.adapting_threshold ? 2 : 0);
+    c.theta_spike_decay = (float)std::exp(-p.th_spike_decay * h);
+    c.theta_spike_refr = (float)std::exp(-p.th_spike_decay * p.t_ref);
+    c.th_spike_add = (float)p.th_spike_add;
+    c.reset_fraction = (float)p.voltage_reset_fraction;
+    c.reset_add = (float)p.voltage_reset_add;
+    c.inv_G = (float)(1.0 / p.g);
+    if (p.adapting_threshold) {
+        c.theta_voltage_decay = (float)std::exp(-p.th_voltage_decay * h);
+        c.phi = (float)(p.th_voltage_index / (p.th_voltage_decay - p.g / p.C_m));
+        c.abpara = (float)(p.th_voltage_index / p.th_voltage_decay);
+    }
+    return BMTK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Small kernels owned by the engine.
+
+__global__ void init_state_kernel(StateSoA st, const TypeConsts* types, const float* init /*[n_types][3]*/,
+                                  uint32_t n_pad) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pad) return;
+    const uint16_t t = st.type[i];
+    st.U[i] = init[t * 3 + 0];
+    st.asc0[i] = init[t * 3 + 1];
+    st.asc1[i] = init[t * 3 + 2];
+    for (int p = 0; p < kPorts; ++p) {
+        st.y1[(size_t)p * n_pad + i] = 0.f;
+        st.y2[(size_t)p * n_pad + i] = 0.f;
+    }
+    st.refr[i] = 0;
+    if (st.th_spike) st.th_spike[i] = 0.f;
+    if (st.th_voltage) st.th_voltage[i] = 0.f;
+    if (st.i_ext) st.i_ext[i] = 0.f;
+}
+
+// Clamp events [b, e): i_ext[target - lo] += delta. Events of one step may repeat a target.
+__global__ void apply_clamp_kernel(float* i_ext, const uint32_t* target, const float* delta, uint32_t b, uint32_t e,
+                                   uint32_t lo) {
+    const uint32_t k = b + blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < e) atomicAdd(&i_ext[target[k] - lo], delta[k]);
+}
+
+// V_m probe: after the step that ends at a multiple of `interval`, writes V_m = U + E_L of the
+// probed neurons into trace[sample][q].
+__global__ void snapshot_kernel(Ctl* ctl, uint32_t step_in_window, uint32_t interval, const uint32_t* ids,
+                                uint32_t n_ids, const float* U, const uint16_t* type, const TypeConsts* types,
+                                float* trace, uint32_t cap_samples) {
+    const unsigned long long done = ctl->step_base + step_in_window + 1ull;
+    if (done % interval) return;
+    const unsigned long long sample = done / interval - 1ull - ctl->sample_base;
+    if (sample >= cap_samples) return;  // the host sizes chunks so that this cannot happen
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < n_ids; q += stride) {
+        const uint32_t i = ids[q];
+        trace[(size_t)sample * n_ids + q] = U[i] + types[type[i]].E_L;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// NCCL through dlopen: the library has no link-time dependency on it.
+
+struct Uid {
+    char internal[128];
+};
+struct NcclApi {
+    void* handle = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, /*ncclUniqueId by value*/ Uid, int) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+static NcclApi g_nccl;
+
+static int load_nccl(const char* path) {
+    if (g_nccl.handle) return BMTK_OK;
+    const char* p = path && path[0] ? path : "libnccl.so.2";
+    void* h = dlopen(p, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(BMTK_E_COMM, "cannot load NCCL from '%s': %s", p, dlerror());
+    g_nccl.GetUniqueId = (int (*)(void*))dlsym(h, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (int (*)(void**, int, Uid, int))dlsym(h, "ncclCommInitRank");
+    g_nccl.AllGather = (int (*)(const void*, void*, size_t, int, void*, cudaStream_t))dlsym(h, "ncclAllGather");
+    g_nccl.CommDestroy = (int (*)(void*))dlsym(h, "ncclCommDestroy");
+    g_nccl.GetErrorString = (const char* (*)(int))dlsym(h, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllGather || !g_nccl.CommDestroy) {
+        dlclose(h);
+        return fail(BMTK_E_COMM, "'%s' lacks the NCCL entry points", p);
+    }
+    g_nccl.handle = h;
+    return BMTK_OK;
+}
+constexpr int kNcclUint32 = 3;  // ncclUint32 in nccl.h's ncclDataType_t
+
+}  // namespace bmtk
+
+using namespace bmtk;
+
+struct bmtk_engine {
+    int device = 0;
+    double dt = 0.1;
+    cudaStream_t stream = nullptr;
+    bool finalized = false;
+
+    // nodes
+    uint64_t n_global = 0, lo = 0, n_local = 0, n_virtual = 0;
+    uint32_t n_pad = 0;
+    std::vector<uint16_t> type_index;
+    std::vector<bmtk_glif_params> types;
+    bool has_theta = false;
+
+    // edges (host accumulators until finalize)
+    std::vector<uint32_t> e_src, e_trg;
+    std::vector<float> e_w;
+    std::vector<uint16_t> e_delay;
+    std::vector<uint8_t> e_port;
+    uint64_t n_edges = 0;
+    uint32_t max_delay = 1, min_delay = 0, target_bits = 1, ring_slots = 2;
+
+    // options
+    bool deterministic = false, use_graph = true, record_spikes = false, profile = false;
+    uint32_t window_opt = 0, window = 1;
+    uint64_t spike_cap_opt = 0, log_cap = 1u << 24, event_cap = 1u << 22, chunk_steps = 4096;
+    uint32_t send_cap = 0, virt_cap = 0;
+
+    // comm
+    void* comm = nullptr;
+    int rank = 0, n_ranks = 1;
+
+    // device memory
+    StateSoA st{};
+    uint16_t* d_type = nullptr;
+    TypeConsts* d_types = nullptr;
+    float* ring = nullptr;
+    Ctl* d_ctl = nullptr;
+    unsigned long long* d_rowptr = nullptr;
+    uint2* d_entries = nullptr;
+    uint32_t *d_send = nullptr, *d_gathered = nullptr, *d_virt = nullptr;
+    uint32_t *d_log_stamp = nullptr, *d_log_id = nullptr;
+    uint4* d_poisson_thr = nullptr;
+    uint64_t seed = 0;
+    std::vector<float> poisson_rates;
+    bool has_poisson = false;
+
+    // replayed input spikes
+    uint32_t *d_in_ptr = nullptr, *d_in_step = nullptr, *d_in_src = nullptr;
+    uint64_t in_ptr_base = 0;
+    uint32_t in_ptr_len = 0;
+    std::vector<uint32_t> pending_in_virt, pending_in_stamp;
+    bool has_pending_inputs = false;
+
+    // clamps
+    std::vector<uint64_t> ce_step;
+    uint32_t* d_ce_target = nullptr;
+    float* d_ce_delta = nullptr;
+    size_t ce_next = 0;
+    bool has_iext = false;
+    std::vector<uint64_t> ce_step_in;
+    std::vector<uint32_t> ce_target_in;
+    std::vector<float> ce_delta_in;
+
+    // probes
+    std::vector<uint32_t> probe_ids;
+    uint32_t probe_interval = 1;
+    uint32_t* d_probe_ids = nullptr;
+    float* d_trace = nullptr;
+    uint32_t trace_cap = 0;
+    uint64_t samples_drained = 0;
+    std::vector<float> h_trace;
+
+    // host stores
+    std::vector<uint32_t> h_spk_stamp, h_spk_id;
+    uint64_t step = 0;
+    uint64_t launches = 0;
+    uint64_t events_total = 0, spikes_total = 0, input_spikes_total = 0;
+
+    // graph
+    cudaGraphExec_t graph_exec = nullptr;
+    bool graph_valid = false;
+
+    // profiling
+    std::vector<cudaEvent_t> ev_pool;
+    std::vector<std::pair<int, int>> ev_update, ev_prop;  // indices into ev_pool
+    double update_ns = 0, prop_ns = 0;
+    uint64_t update_launches = 0, prop_launches = 0;
+
+    DetWorkspace det{};
+};
+
+namespace bmtk {
+
+static int set_device(bmtk_engine* e) {
+    CU(cudaSetDevice(e->device));
+    return BMTK_OK;
+}
+
+static UpdateArgs make_update_args(bmtk_engine* e, uint32_t s) {
+    UpdateArgs a{};
+    a.st = e->st;
+    a.types = e->d_types;
+    a.n_types = (int32_t)e->types.size();
+    a.n_local = (uint32_t)e->n_local;
+    a.n_pad = e->n_pad;
+    a.lo = (uint32_t)e->lo;
+    a.ring = e->ring;
+    a.ring_slots = e->ring_slots;
+    a.ctl = e->d_ctl;
+    a.step_in_window = s;
+    a.send = e->d_send;
+    a.send_cap = e->send_cap;
+    a.log_stamp = e->record_spikes ? e->d_log_stamp : nullptr;
+    a.log_id = e->d_log_id;
+    a.log_cap = (uint32_t)e->log_cap;
+    a.poisson_thr = e->has_poisson ? e->d_poisson_thr : nullptr;
+    a.n_virtual = (uint32_t)e->n_virtual;
+    a.n_global = (uint32_t)e->n_global;
+    a.seed = e->seed;
+    a.virt = e->d_virt;
+    a.virt_cap = e->virt_cap;
+    return a;
+}
+
+static PropArgs make_prop_args(bmtk_engine* e, uint32_t w) {
+    PropArgs a{};
+    a.rowptr = e->d_rowptr;
+    a.entries = e->d_entries;
+    a.target_bits = e->target_bits;
+    a.ring = e->ring;
+    a.ring_slots = e->ring_slots;
+    a.n_pad = e->n_pad;
+    a.ctl = e->d_ctl;
+    a.gathered = e->n_ranks > 1 ? e->d_gathered : e->d_send;
+    a.n_seg = (uint32_t)e->n_ranks;
+    a.seg_stride = e->send_cap + 4;
+    a.seg_cap = e->send_cap;
+    a.in_ptr = e->d_in_ptr;
+    a.in_ptr_base = e->in_ptr_base;
+    a.in_ptr_len = e->in_ptr_len;
+    a.in_step = e->d_in_step;
+    a.in_src = e->d_in_src;
+    a.virt = e->has_poisson ? e->d_virt : nullptr;
+    a.virt_cap = e->virt_cap;
+    a.window = w;
+    a.send = e->d_send;
+    return a;
+}
+
+static int get_event(bmtk_engine* e, int* idx) {
+    cudaEvent_t ev;
+    CU(cudaEventCreate(&ev));
+    e->ev_pool.push_back(ev);
+    *idx = (int)e->ev_pool.size() - 1;
+    return BMTK_OK;
+}
+
+// Enqueues one window of `w` steps starting at host step e->step. `capturing` skips everything
+// that cannot be part of a graph (profiling events, clamp launches).
+static int enqueue_window(bmtk_engine* e, uint32_t w, bool capturing) {
+    for (uint32_t s = 0; s < w; ++s) {
+        if (!capturing && e->has_iext) {
+            const uint64_t n = e->step + s;
+            size_t b = e->ce_next;
+            while (e->ce_next < e->ce_step.size() && e->ce_step[e->ce_next] <= n) ++e->ce_next;
+            if (e->ce_next > b) {
+                const uint32_t cnt = (uint32_t)(e->ce_next - b);
+                apply_clamp_kernel<<<(cnt + 127) / 128, 128, 0, e->stream>>>(e->st.i_ext, e->d_ce_target, e->d_ce_delta,
+                                                                            (uint32_t)b, (uint32_t)e->ce_next,
+                                                                            (uint32_t)e->lo);
+                CU(cudaGetLastError());
+                ++e->launches;
+            }
+        }
+        int e0 = -1, e1 = -1;
+        if (e->profile && !capturing) {
+            int rc = get_event(e, &e0);
+            if (rc) return rc;
+            CU(cudaEventRecord(e->ev_pool[e0], e->stream));
+        }
+        const UpdateArgs ua = make_update_args(e, s);
+        CU(launch_glif_update(ua, e->has_theta, e->has_iext, e->stream));
+        ++e->launches;
+        if (e->profile && !capturing) {
+            int rc = get_event(e, &e1);
+            if (rc) return rc;
+            CU(cudaEventRecord(e->ev_pool[e1], e->stream));
+            e->ev_update.emplace_back(e0, e1);
+        }
+        if (!e->probe_ids.empty()) {
+            const uint32_t n_ids = (uint32_t)e->probe_ids.size();
+            const int blocks = (int)std::min<uint32_t>((n_ids + 255) / 256, 148 * 4);
+            snapshot_kernel<<<blocks, 256, 0, e->stream>>>(e->d_ctl, s, e->probe_interval, e->d_probe_ids, n_ids,
+                                                           e->st.U, e->d_type, e->d_types, e->d_trace, e->trace_cap);
+            CU(cudaGetLastError());
+            ++e->launches;
+        }
+    }
+    if (e->n_ranks > 1) {
+        const int rc = g_nccl.AllGather(e->d_send, e->d_gathered, (size_t)e->send_cap + 4, kNcclUint32, e->comm,
+                                        e->stream);
+        if (rc != 0)
+            return fail(BMTK_E_COMM, "ncclAllGather failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?");
+    }
+    const PropArgs pa = make_prop_args(e, w);
+    int p0 = -1, p1 = -1;
+    if (e->profile && !capturing) {
+        int rc = get_event(e, &p0);
+        if (rc) return rc;
+        CU(cudaEventRecord(e->ev_pool[p0], e->stream));
+    }
+    if (e->deterministic) {
+        const int rc = propagate_det_window(pa, e->det, e->stream, &e->launches);
+        if (rc == -2) return fail(BMTK_E_OVERFLOW, "deterministic propagate: more than %llu events in one window "
+                                  "(raise option event_capacity)", (unsigned long long)e->event_cap);
+        if (rc != 0) return fail(BMTK_E_CUDA, "deterministic propagate failed: %s", cudaGetErrorString(cudaGetLastError()));
+    } else {
+        CU(launch_propagate_atomic(pa, e->stream));
+        ++e->launches;
+    }
+    if (e->profile && !capturing) {
+        int rc = get_event(e, &p1);
+        if (rc) return rc;
+        CU(cudaEventRecord(e->ev_pool[p1], e->stream));
+        e->ev_prop.emplace_back(p0, p1);
+    }
+    return BMTK_OK;
+}
+
+static void drop_graph(bmtk_engine* e) {
+    if (e->graph_exec) cudaGraphExecDestroy(e->graph_exec);
+    e->graph_exec = nullptr;
+    e->graph_valid = false;
+}
+
+static int capture_graph(bmtk_engine* e) {
+    drop_graph(e);
+    cudaGraph_t graph = nullptr;
+    CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const uint64_t launches_before = e->launches;
+    const int rc = enqueue_window(e, e->window, true);
+    e->launches = launches_before;
+    cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+    if (rc != BMTK_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+    ce = cudaGraphInstantiate(&e->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "graph instantiate failed: %s", cudaGetErrorString(ce));
+    e->graph_valid = true;
+    return BMTK_OK;
+}
+
+static uint32_t launches_per_window(bmtk_engine* e, uint32_t w) {
+    return w * (1u + (e->probe_ids.empty() ? 0u : 1u)) + 1u;
+}
+
+// Uploads pending replay spikes: keeps stamps > current step, sorts by emitting step, builds the
+// per-step pointer table.
+static int upload_inputs(bmtk_engine* e) {
+    if (!e->has_pending_inputs) return BMTK_OK;
+    e->has_pending_inputs = false;
+    drop_graph(e);
+    const size_t n_in = e->pending_in_virt.size();
+    std::vector<std::pair<uint32_t, uint32_t>> ev;  // (emit step, source row)
+    ev.reserve(n_in);
+    for (size_t i = 0; i < n_in; ++i) {
+        const uint64_t stamp = e->pending_in_stamp[i];
+        if (stamp <= e->step) continue;  // already in the past
+        ev.emplace_back((uint32_t)(stamp - 1), (uint32_t)(e->n_global + e->pending_in_virt[i]));
+    }
+    std::sort(ev.begin(), ev.end());
+    e->pending_in_virt.clear();
+    e->pending_in_stamp.clear();
+    cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
+    e->d_in_ptr = e->d_in_step = e->d_in_src = nullptr;
+    e->in_ptr_len = 0;
+    if (ev.empty()) return BMTK_OK;
+    const uint64_t base = e->step;
+    const uint64_t last = ev.back().first;
+    const uint64_t len = last - base + 2;  // entries for steps base..last, plus the end
+    if (len > (1ull << 31)) return fail(BMTK_E_INVALID, "input spikes span too many steps");
+    std::vector<uint32_t> ptr(len), st(ev.size()), sr(ev.size());
+    size_t k = 0;
+    for (uint64_t i = 0; i < len; ++i) {
+        while (k < ev.size() && ev[k].first < base + i) ++k;
+        ptr[i] = (uint32_t)k;
+    }
+    for (size_t i = 0; i < ev.size(); ++i) {
+        st[i] = ev[i].first;
+        sr[i] = ev[i].second;
+    }
+    CU(cudaMalloc(&e->d_in_ptr, 4 * len));
+    CU(cudaMalloc(&e->d_in_step, 4 * ev.size()));
+    CU(cudaMalloc(&e->d_in_src, 4 * ev.size()));
+    CU(cudaMemcpyAsync(e->d_in_ptr, ptr.data(), 4 * len, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_in_step, st.data(), 4 * ev.size(), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_in_src, sr.data(), 4 * ev.size(), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    e->in_ptr_base = base;
+    e->in_ptr_len = (uint32_t)len;
+    return BMTK_OK;
+}
+
+// Brings counters, spike log and traces of the finished chunk to the host.
+static int drain(bmtk_engine* e) {
+    Ctl h{};
+    CU(cudaMemcpyAsync(&h, e->d_ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    e->events_total = h.n_events;
+    e->spikes_total = h.n_spikes;
+    e->input_spikes_total = h.n_input_spikes;
+    if (h.step_base != e->step)
+        return fail(BMTK_E_INVALID, "device clock %llu differs from host clock %llu", (unsigned long long)h.step_base,
+                    (unsigned long long)e->step);
+    if (e->profile) {
+        for (auto& pr : e->ev_update) {
+            float ms = 0;
+            CU(cudaEventElapsedTime(&ms, e->ev_pool[pr.first], e->ev_pool[pr.second]));
+            e->update_ns += (double)ms * 1e6;
+            ++e->update_launches;
+        }
+        for (auto& pr : e->ev_prop) {
+            float ms = 0;
+            CU(cudaEventElapsedTime(&ms, e->ev_pool[pr.first], e->ev_pool[pr.second]));
+            e->prop_ns += (double)ms * 1e6;
+            ++e->prop_launches;
+        }
+        for (auto ev : e->ev_pool) cudaEventDestroy(ev);
+        e->ev_pool.clear();
+        e->ev_update.clear();
+        e->ev_prop.clear();
+    }
+    if (h.error_flags) {
+        const uint32_t f = h.error_flags;
+        CU(cudaMemsetAsync(&e->d_ctl->error_flags, 0, 4, e->stream));
+        if (f & kErrSpikeListFull)
+            return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank): raise option spike_capacity",
+                        e->send_cap);
+        if (f & kErrVirtListFull)
+            return fail(BMTK_E_OVERFLOW, "Poisson spike list full (capacity %u): raise option spike_capacity", e->virt_cap);
+        if (f & kErrLogFull)
+            return fail(BMTK_E_OVERFLOW, "spike log full (capacity %llu): raise log_capacity or lower chunk_steps",
+                        (unsigned long long)e->log_cap);
+        return fail(BMTK_E_OVERFLOW, "device buffer overflow (flags %u)", f);
+    }
+    if (e->record_spikes && h.log_count) {
+        const size_t n0 = e->h_spk_stamp.size(), n = h.log_count;
+        e->h_spk_stamp.resize(n0 + n);
+        e->h_spk_id.resize(n0 + n);
+        CU(cudaMemcpyAsync(e->h_spk_stamp.data() + n0, e->d_log_stamp, 4 * n, cudaMemcpyDeviceToHost, e->stream));
+        CU(cudaMemcpyAsync(e->h_spk_id.data() + n0, e->d_log_id, 4 * n, cudaMemcpyDeviceToHost, e->stream));
+        CU(cudaMemsetAsync(&e->d_ctl->log_count, 0, 4, e->stream));
+        CU(cudaStreamSynchronize(e->stream));
+    }
+    if (!e->probe_ids.empty()) {
+        const uint64_t have = e->step / e->probe_interval;
+        const uint64_t n_new = have - e->samples_drained;
+        if (n_new) {
+            const size_t n_ids = e->probe_ids.size(), n0 = e->h_trace.size();
+            e->h_trace.resize(n0 + n_new * n_ids);
+            CU(cudaMemcpyAsync(e->h_trace.data() + n0, e->d_trace, 4 * n_new * n_ids, cudaMemcpyDeviceToHost, e->stream));
+            e->samples_drained = have;
+            const uint32_t sb = (uint32_t)have;
+            CU(cudaMemcpyAsync(&e->d_ctl->sample_base, &sb, 4, cudaMemcpyHostToDevice, e->stream));
+            CU(cudaStreamSynchronize(e->stream));
+        }
+    }
+    return BMTK_OK;
+}
+
+static int run_steps(bmtk_engine* e, uint64_t n_steps) {
+    int rc = upload_inputs(e);
+    if (rc) return rc;
+    uint64_t left = n_steps;
+    while (left) {
+        uint64_t chunk = std::min<uint64_t>(left, e->chunk_steps);
+        if (!e->probe_ids.empty()) {
+            // the trace buffer holds trace_cap samples
+            const uint64_t room = (uint64_t)e->trace_cap * e->probe_interval;
+            chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(room - e->probe_interval + 1, 1));
+        }
+        uint64_t done = 0;
+        while (done < chunk) {
+            const uint32_t w = (uint32_t)std::min<uint64_t>(e->window, chunk - done);
+            bool clamp_in_window = false;
+            if (e->has_iext && e->ce_next < e->ce_step.size() && e->ce_step[e->ce_next] < e->step + w)
+                clamp_in_window = true;
+            const bool graph_ok = e->use_graph && !e->deterministic && !e->profile && w == e->window && !clamp_in_window;
+            if (graph_ok) {
+                if (!e->graph_valid) {
+                    rc = capture_graph(e);
+                    if (rc) return rc;
+                }
+                CU(cudaGraphLaunch(e->graph_exec, e->stream));
+                e->launches += launches_per_window(e, w);
+            } else {
+                rc = enqueue_window(e, w, false);
+                if (rc) return rc;
+            }
+            e->step += w;
+            done += w;
+        }
+        left -= chunk;
+        rc = drain(e);
+        if (rc) return rc;
+    }
+    return BMTK_OK;
+}
+
+}  // namespace bmtk
+
+// =============================================================================================
+// C ABI
+
+extern "C" {
+
+const char* bmtk_last_error(void) { return g_last_error.c_str(); }
+const char* bmtk_version(void) { return "bmtk_b200 0.1 sm_100a"; }
+
+int bmtk_engine_create(bmtk_engine** out, int device, double dt_ms) {
+    if (!out) return fail(BMTK_E_INVALID, "out is NULL");
+    if (!(dt_ms > 0)) return fail(BMTK_E_INVALID, "dt must be positive");
+    int n_dev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&n_dev);
+    if (ce != cudaSuccess || n_dev == 0)
+        return fail(BMTK_E_CUDA, "no CUDA device available (%s): this engine has no CPU path",
+                    ce != cudaSuccess ? cudaGetErrorString(ce) : "device count 0");
+    if (device < 0 || device >= n_dev) return fail(BMTK_E_INVALID, "device %d out of range (%d present)", device, n_dev);
+    bmtk_engine* e = new bmtk_engine();
+    e->device = device;
+    e->dt = dt_ms;
+    ce = cudaSetDevice(device);
+    if (ce == cudaSuccess) ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    if (ce != cudaSuccess) {
+        delete e;
+        return fail(BMTK_E_CUDA, "cannot initialise device %d: %s", device, cudaGetErrorString(ce));
+    }
+    *out = e;
+    return BMTK_OK;
+}
+
+int bmtk_engine_destroy(bmtk_engine* e) {
+    if (!e) return BMTK_OK;
+    cudaSetDevice(e->device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    drop_graph(e);
+    for (auto ev : e->ev_pool) cudaEventDestroy(ev);
+    if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
+    det_free(e->det);
+    cudaFree(e->st.U); cudaFree(e->st.asc0); cudaFree(e->st.asc1); cudaFree(e->st.y1); cudaFree(e->st.y2);
+    cudaFree(e->st.refr); cudaFree(e->st.th_spike); cudaFree(e->st.th_voltage); cudaFree(e->st.i_ext);
+    cudaFree(e->d_type); cudaFree(e->d_types); cudaFree(e->ring); cudaFree(e->d_ctl);
+    cudaFree(e->d_rowptr); cudaFree(e->d_entries); cudaFree(e->d_send); cudaFree(e->d_gathered); cudaFree(e->d_virt);
+    cudaFree(e->d_log_stamp); cudaFree(e->d_log_id); cudaFree(e->d_poisson_thr);
+    cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
+    cudaFree(e->d_ce_target); cudaFree(e->d_ce_delta); cudaFree(e->d_probe_ids); cudaFree(e->d_trace);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_nodes(bmtk_engine* e, uint64_t n_global, uint64_t lo, uint64_t n_local, const uint16_t* type_index,
+                          int32_t n_types, const bmtk_glif_params* types) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "set_nodes: engine missing or already finalized");
+    if (n_types < 1 || n_types > 65535 || !types) return fail(BMTK_E_INVALID, "set_nodes: need 1..65535 node types");
+    if (lo + n_local > n_global) return fail(BMTK_E_INVALID, "set_nodes: block [%llu,%llu) outside 0..%llu",
+                                             (unsigned long long)lo, (unsigned long long)(lo + n_local),
+                                             (unsigned long long)n_global);
+    if (n_local && !type_index) return fail(BMTK_E_INVALID, "set_nodes: type_index is NULL");
+    if (n_global >= (1ull << kSrcBits)) return fail(BMTK_E_UNSUPPORTED, "more than 2^%d sources", kSrcBits);
+    for (uint64_t i = 0; i < n_local; ++i)
+        if (type_index[i] >= n_types) return fail(BMTK_E_INVALID, "set_nodes: type_index[%llu] out of range", (unsigned long long)i);
+    TypeConsts tmp;
+    for (int t = 0; t < n_types; ++t) {
+        const int rc = compute_type_consts(types[t], e->dt, tmp);
+        if (rc) return rc;
+    }
+    e->n_global = n_global;
+    e->lo = lo;
+    e->n_local = n_local;
+    e->type_index.assign(type_index, type_index + n_local);
+    e->types.assign(types, types + n_types);
+    e->has_theta = false;
+    for (auto& t : e->types) e->has_theta |= (t.spike_dependent_threshold || t.adapting_threshold);
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_virtual(bmtk_engine* e, uint64_t n_virtual) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "set_virtual: engine missing or already finalized");
+    if (e->n_global + n_virtual >= (1ull << kSrcBits)) return fail(BMTK_E_UNSUPPORTED, "more than 2^%d sources", kSrcBits);
+    e->n_virtual = n_virtual;
+    return BMTK_OK;
+}
+
+int bmtk_engine_add_edges(bmtk_engine* e, uint64_t n, const uint32_t* src, const uint32_t* trg, const float* weight,
+                          const uint16_t* delay_steps, const uint8_t* port) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "add_edges: engine missing or already finalized");
+    if (n == 0) return BMTK_OK;
+    if (!src || !trg || !weight || !delay_steps || !port) return fail(BMTK_E_INVALID, "add_edges: NULL array");
+    const uint64_t n_rows = e->n_global + e->n_virtual;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (delay_steps[i] < 1)
+            return fail(BMTK_E_DELAY, "edge %llu: delay shorter than the resolution dt = %g ms",
+                        (unsigned long long)i, e->dt);
+        if (src[i] >= n_rows) return fail(BMTK_E_INVALID, "edge %llu: source %u out of range", (unsigned long long)i, src[i]);
+        if (trg[i] < e->lo || trg[i] >= e->lo + e->n_local)
+            return fail(BMTK_E_INVALID, "edge %llu: target %u outside this engine's block", (unsigned long long)i, trg[i]);
+        if (port[i] >= kPorts) return fail(BMTK_E_INVALID, "edge %llu: port %u out of range", (unsigned long long)i, port[i]);
+    }
+    e->e_src.insert(e->e_src.end(), src, src + n);
+    e->e_trg.insert(e->e_trg.end(), trg, trg + n);
+    e->e_w.insert(e->e_w.end(), weight, weight + n);
+    e->e_delay.insert(e->e_delay.end(), delay_steps, delay_steps + n);
+    e->e_port.insert(e->e_port.end(), port, port + n);
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_input_spikes(bmtk_engine* e, uint64_t n, const uint32_t* virt_index, const uint32_t* stamp_step) {
+    if (!e) return fail(BMTK_E_INVALID, "engine is NULL");
+    if (n && (!virt_index || !stamp_step)) return fail(BMTK_E_INVALID, "set_input_spikes: NULL array");
+    for (uint64_t i = 0; i < n; ++i) {
+        if (virt_index[i] >= e->n_virtual)
+            return fail(BMTK_E_INVALID, "input spike %llu: virtual cell %u out of range", (unsigned long long)i, virt_index[i]);
+        if (stamp_step[i] < 1)
+            return fail(BMTK_E_INVALID, "input spike %llu: spike time must be greater than zero", (unsigned long long)i);
+    }
+    e->pending_in_virt.assign(virt_index, virt_index + n);
+    e->pending_in_stamp.assign(stamp_step, stamp_step + n);
+    e->has_pending_inputs = true;
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_poisson(bmtk_engine* e, const float* rate_hz, uint64_t seed) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "set_poisson: engine missing or already finalized");
+    if (!rate_hz || e->n_virtual == 0) return fail(BMTK_E_INVALID, "set_poisson: no virtual cells or NULL rates");
+    for (uint64_t v = 0; v < e->n_virtual; ++v) {
+        const double lam = (double)rate_hz[v] * e->dt * 1e-3;
+        if (!(lam >= 0) || lam > 0.25)
+            return fail(BMTK_E_UNSUPPORTED, "virtual cell %llu: rate*dt = %g outside [0, 0.25]", (unsigned long long)v, lam);
+    }
+    e->poisson_rates.assign(rate_hz, rate_hz + e->n_virtual);
+    e->seed = seed;
+    e->has_poisson = true;
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_clamp_events(bmtk_engine* e, uint64_t n, const uint64_t* step, const uint32_t* target,
+                                 const float* delta_pA) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "set_clamp_events: engine missing or already finalized");
+    if (n && (!step || !target || !delta_pA)) return fail(BMTK_E_INVALID, "set_clamp_events: NULL array");
+    for (uint64_t i = 0; i < n; ++i)
+        if (target[i] < e->lo || target[i] >= e->lo + e->n_local)
+            return fail(BMTK_E_INVALID, "clamp event %llu: target %u outside this engine's block", (unsigned long long)i, target[i]);
+    e->ce_step_in.assign(step, step + n);
+    e->ce_target_in.assign(target, target + n);
+    e->ce_delta_in.assign(delta_pA, delta_pA + n);
+    e->has_iext = n > 0;
+    return BMTK_OK;
+}
+
+int bmtk_engine_record_spikes(bmtk_engine* e, int enable) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "record_spikes: engine missing or already finalized");
+    e->record_spikes = enable != 0;
+    return BMTK_OK;
+}
+
+int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "record_vm: engine missing or already finalized");
+    if (interval_steps < 1) return fail(BMTK_E_INVALID, "record_vm: interval must be at least one step");
+    for (uint64_t i = 0; i < n_ids; ++i)
+        if (ids[i] < e->lo || ids[i] >= e->lo + e->n_local)
+            return fail(BMTK_E_INVALID, "record_vm: id %u outside this engine's block", ids[i]);
+    e->probe_ids.resize(n_ids);
+    for (uint64_t i = 0; i < n_ids; ++i) e->probe_ids[i] = ids[i] - (uint32_t)e->lo;
+    e->probe_interval = interval_steps;
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
+    if (!e || !key) return fail(BMTK_E_INVALID, "set_option: NULL argument");
+    const std::string k(key);
+    if (k == "profile") { e->profile = value != 0; return BMTK_OK; }
+    if (k == "use_graph") { e->use_graph = value != 0; return BMTK_OK; }
+    if (k == "chunk_steps") {
+        if (value < 1) return fail(BMTK_E_INVALID, "chunk_steps must be positive");
+        e->chunk_steps = (uint64_t)value;
+        return BMTK_OK;
+    }
+    if (e->finalized) return fail(BMTK_E_INVALID, "option '%s' must be set before finalize", key);
+    if (value < 0) return fail(BMTK_E_INVALID, "option '%s' must not be negative", key);
+    if (k == "deterministic") e->deterministic = value != 0;
+    else if (k == "window") e->window_opt = (uint32_t)value;
+    else if (k == "spike_capacity") e->spike_cap_opt = (uint64_t)value;
+    else if (k == "log_capacity") e->log_cap = std::max<uint64_t>(1024, (uint64_t)value);
+    else if (k == "event_capacity") e->event_cap = std::max<uint64_t>(1024, (uint64_t)value);
+    else return fail(BMTK_E_INVALID, "unknown option '%s'", key);
+    return BMTK_OK;
+}
+
+int bmtk_comm_unique_id(void* uid128, const char* libnccl) {
+    if (!uid128) return fail(BMTK_E_INVALID, "uid128 is NULL");
+    int rc = load_nccl(libnccl);
+    if (rc) return rc;
+    Uid id;
+    std::memset(&id, 0, sizeof(id));
+    rc = g_nccl.GetUniqueId(&id);
+    if (rc != 0) return fail(BMTK_E_COMM, "ncclGetUniqueId failed (%d)", rc);
+    std::memcpy(uid128, &id, sizeof(id));
+    return BMTK_OK;
+}
+
+int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ranks, const char* libnccl) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "comm_init: engine missing or already finalized");
+    if (n_ranks < 1 || rank < 0 || rank >= n_ranks) return fail(BMTK_E_INVALID, "comm_init: bad rank %d of %d", rank, n_ranks);
+    if (n_ranks > 16) return fail(BMTK_E_UNSUPPORTED, "at most 16 ranks");
+    e->rank = rank;
+    e->n_ranks = n_ranks;
+    if (n_ranks == 1) return BMTK_OK;
+    if (!uid128) return fail(BMTK_E_INVALID, "comm_init: uid128 is NULL");
+    int rc = load_nccl(libnccl);
+    if (rc) return rc;
+    rc = set_device(e);
+    if (rc) return rc;
+    Uid id;
+    std::memcpy(&id, uid128, sizeof(id));
+    rc = g_nccl.CommInitRank(&e->comm, n_ranks, id, rank);
+    if (rc != 0) return fail(BMTK_E_COMM, "ncclCommInitRank failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?");
+    return BMTK_OK;
+}
+
+int bmtk_engine_finalize(bmtk_engine* e) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "finalize: engine missing or already finalized");
+    if (e->types.empty()) return fail(BMTK_E_INVALID, "finalize: set_nodes has not been called");
+    int rc = set_device(e);
+    if (rc) return rc;
+    const uint64_t n_rows = e->n_global + e->n_virtual;
+    e->n_edges = e->e_src.size();
+    e->n_pad = (uint32_t)((e->n_local + 3) / 4 * 4);
+    if (e->n_pad == 0) e->n_pad = 4;
+
+    // delays and the bit layout of a CSR entry
+    uint32_t dmax = 1, dmin = 0xffffffffu;
+    for (uint16_t d : e->e_delay) {
+        dmax = std::max<uint32_t>(dmax, d);
+        dmin = std::min<uint32_t>(dmin, d);
+    }
+    if (e->n_edges == 0) dmin = kMaxWindow;
+    e->max_delay = dmax;
+    e->min_delay = dmin;
+    uint32_t tb = 1;
+    while ((1ull << tb) < e->n_pad) ++tb;
+    uint32_t db = 1;
+    while ((1u << db) <= dmax) ++db;
+    if (tb + 2 + db > 32)
+        return fail(BMTK_E_UNSUPPORTED, "CSR entry needs %u target + 2 port + %u delay bits > 32", tb, db);
+    e->target_bits = tb;
+
+    // exchange window: at most the minimum delay (every spike of a window lands in a later one)
+    uint32_t w = e->window_opt ? e->window_opt : dmin;
+    w = std::min<uint32_t>(w, dmin);
+    w = std::min<uint32_t>(w, kMaxWindow);
+    w = std::max<uint32_t>(w, 1);
+    e->window = w;
+    e->ring_slots = dmax + w;
+    const uint64_t ring_cells = (uint64_t)e->ring_slots * kPorts * e->n_pad;
+    if (ring_cells >= (1ull << 32) && e->deterministic)
+        return fail(BMTK_E_UNSUPPORTED, "deterministic mode needs fewer than 2^32 ring cells");
+
+    // CSR
+    rc = BMTK_OK;
+    {
+        cudaError_t ce = build_csr_device(n_rows, e->n_edges, e->e_src.data(), e->e_trg.data(), e->e_w.data(),
+                                          e->e_delay.data(), e->e_port.data(), (uint32_t)e->lo, tb, e->stream,
+                                          &e->d_rowptr, &e->d_entries);
+        if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "CSR build failed: %s", cudaGetErrorString(ce));
+    }
+    std::vector<uint32_t>().swap(e->e_src);
+    std::vector<uint32_t>().swap(e->e_trg);
+    std::vector<float>().swap(e->e_w);
+    std::vector<uint16_t>().swap(e->e_delay);
+    std::vector<uint8_t>().swap(e->e_port);
+
+    // state
+    const size_t np = e->n_pad;
+    CU(cudaMalloc(&e->st.U, 4 * np));
+    CU(cudaMalloc(&e->st.asc0, 4 * np));
+    CU(cudaMalloc(&e->st.asc1, 4 * np));
+    CU(cudaMalloc(&e->st.y1, 4 * np * kPorts));
+    CU(cudaMalloc(&e->st.y2, 4 * np * kPorts));
+    CU(cudaMalloc(&e->st.refr, 4 * np));
+    if (e->has_theta) {
+        CU(cudaMalloc(&e->st.th_spike, 4 * np));
+        CU(cudaMalloc(&e->st.th_voltage, 4 * np));
+    }
+    if (e->has_iext) CU(cudaMalloc(&e->st.i_ext, 4 * np));
+    CU(cudaMalloc(&e->d_type, 2 * np));
+    {
+        std::vector<uint16_t> ty(np, 0);
+        std::copy(e->type_index.begin(), e->type_index.end(), ty.begin());
+        CU(cudaMemcpy(e->d_type, ty.data(), 2 * np, cudaMemcpyHostToDevice));
+    }
+    e->st.type = e->d_type;
+    const size_t nt = e->types.size();
+    std::vector<TypeConsts> tc(nt);
+    std::vector<float> init(nt * 3);
+    for (size_t t = 0; t < nt; ++t) {
+        rc = compute_type_consts(e->types[t], e->dt, tc[t]);
+        if (rc) return rc;
+        init[t * 3 + 0] = (float)(e->types[t].V_m - e->types[t].E_L);
+        init[t * 3 + 1] = (float)e->types[t].asc_init[0];
+        init[t * 3 + 2] = (float)e->types[t].asc_init[1];
+    }
+    CU(cudaMalloc(&e->d_types, sizeof(TypeConsts) * nt));
+    CU(cudaMemcpy(e->d_types, tc.data(), sizeof(TypeConsts) * nt, cudaMemcpyHostToDevice));
+    float* d_init = nullptr;
+    CU(cudaMalloc(&d_init, 4 * init.size()));
+    CU(cudaMemcpy(d_init, init.data(), 4 * init.size(), cudaMemcpyHostToDevice));
+    init_state_kernel<<<(unsigned)((np + 255) / 256), 256, 0, e->stream>>>(e->st, e->d_types, d_init, e->n_pad);
+    CU(cudaGetLastError());
+    CU(cudaMalloc(&e->ring, 4 * ring_cells));
+    CU(cudaMemsetAsync(e->ring, 0, 4 * ring_cells, e->stream));
+    CU(cudaMalloc(&e->d_ctl, sizeof(Ctl)));
+    CU(cudaMemsetAsync(e->d_ctl, 0, sizeof(Ctl), e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    cudaFree(d_init);
+
+    // spike lists. Automatic capacity: every local neuron may fire in 1 of 8 steps of a window.
+    uint64_t cap = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, (uint64_t)e->n_local * w / 8);
+    cap = std::min<uint64_t>(cap, (uint64_t)e->n_local * w + 4);
+    cap = (cap + 3) / 4 * 4;
+    if (cap + 4 >= (1ull << 31)) return fail(BMTK_E_UNSUPPORTED, "spike_capacity too large");
+    e->send_cap = (uint32_t)cap;
+    const size_t seg = (size_t)e->send_cap + 4;  // word 0 = count, 3 words of padding keep 16-byte alignment
+    CU(cudaMalloc(&e->d_send, 4 * seg));
+    CU(cudaMemset(e->d_send, 0, 4 * seg));
+    if (e->n_ranks > 1) {
+        CU(cudaMalloc(&e->d_gathered, 4 * seg * e->n_ranks));
+        CU(cudaMemset(e->d_gathered, 0, 4 * seg * e->n_ranks));
+    }
+    if (e->has_poisson) {
+        uint64_t vc = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, e->n_virtual * w / 4);
+        e->virt_cap = (uint32_t)vc;
+        CU(cudaMalloc(&e->d_virt, 4 * ((size_t)e->virt_cap + 4)));
+        CU(cudaMemset(e->d_virt, 0, 4 * ((size_t)e->virt_cap + 4)));
+        std::vector<uint4> thr(e->n_virtual);
+        for (uint64_t v = 0; v < e->n_virtual; ++v) {
+            const double lam = (double)e->poisson_rates[v] * e->dt * 1e-3;
+            double p = std::exp(-lam), cdf = 0.0;
+            uint32_t t[4];
+            for (int k = 0; k < 4; ++k) {
+                cdf += p;
+                const double x = std::floor(cdf * 4294967296.0);
+                t[k] = x >= 4294967295.0 ? 0xFFFFFFFFu : (uint32_t)x;
+                p *= lam / (double)(k + 1);
+            }
+            thr[v] = make_uint4(t[0], t[1], t[2], t[3]);
+        }
+        CU(cudaMalloc(&e->d_poisson_thr, sizeof(uint4) * e->n_virtual));
+        CU(cudaMemcpy(e->d_poisson_thr, thr.data(), sizeof(uint4) * e->n_virtual, cudaMemcpyHostToDevice));
+    }
+    if (e->record_spikes) {
+        if (e->log_cap >= (1ull << 32)) return fail(BMTK_E_UNSUPPORTED, "log_capacity too large");
+        CU(cudaMalloc(&e->d_log_stamp, 4 * e->log_cap));
+        CU(cudaMalloc(&e->d_log_id, 4 * e->log_cap));
+    }
+    // clamps: sort by step
+    if (e->has_iext) {
+        const size_t n = e->ce_step_in.size();
+        std::vector<size_t> ord(n);
+        for (size_t i = 0; i < n; ++i) ord[i] = i;
+        std::stable_sort(ord.begin(), ord.end(), [&](size_t a, size_t b) { return e->ce_step_in[a] < e->ce_step_in[b]; });
+        std::vector<uint32_t> tg(n);
+        std::vector<float> dl(n);
+        e->ce_step.resize(n);
+        for (size_t i = 0; i < n; ++i) {
+            e->ce_step[i] = e->ce_step_in[ord[i]];
+            tg[i] = e->ce_target_in[ord[i]];
+            dl[i] = e->ce_delta_in[ord[i]];
+        }
+        CU(cudaMalloc(&e->d_ce_target, 4 * n));
+        CU(cudaMalloc(&e->d_ce_delta, 4 * n));
+        CU(cudaMemcpy(e->d_ce_target, tg.data(), 4 * n, cudaMemcpyHostToDevice));
+        CU(cudaMemcpy(e->d_ce_delta, dl.data(), 4 * n, cudaMemcpyHostToDevice));
+    }
+    // probes
+    if (!e->probe_ids.empty()) {
+        const size_t n_ids = e->probe_ids.size();
+        // at most 256 MiB of trace between drains, at least 64 samples
+        uint64_t cap_s = std::max<uint64_t>(64, (256ull << 20) / (4 * n_ids));
+        cap_s = std::min<uint64_t>(cap_s, 1u << 20);
+        e->trace_cap = (uint32_t)cap_s;
+        CU(cudaMalloc(&e->d_probe_ids, 4 * n_ids));
+        CU(cudaMemcpy(e->d_probe_ids, e->probe_ids.data(), 4 * n_ids, cudaMemcpyHostToDevice));
+        CU(cudaMalloc(&e->d_trace, 4 * n_ids * cap_s));
+    }
+    if (e->deterministic) {
+        cudaError_t ce = det_alloc(e->det, (uint32_t)e->event_cap,
+                                   (uint32_t)((size_t)e->send_cap * e->n_ranks + e->virt_cap + 65536), ring_cells);
+        if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "deterministic workspace: %s", cudaGetErrorString(ce));
+    }
+    e->finalized = true;
+    return BMTK_OK;
+}
+
+int bmtk_engine_run(bmtk_engine* e, uint64_t n_steps) {
+    if (!e || !e->finalized) return fail(BMTK_E_INVALID, "run: engine missing or not finalized");
+    int rc = set_device(e);
+    if (rc) return rc;
+    if (e->step + n_steps >= (1ull << 32)) return fail(BMTK_E_UNSUPPORTED, "more than 2^32 steps");
+    return run_steps(e, n_steps);
+}
+
+int bmtk_engine_spike_count(bmtk_engine* e, uint64_t* n) {
+    if (!e || !n) return fail(BMTK_E_INVALID, "NULL argument");
+    *n = e->h_spk_stamp.size();
+    return BMTK_OK;
+}
+
+int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step, uint32_t* id, uint64_t* n_out) {
+    if (!e || !n_out) return fail(BMTK_E_INVALID, "NULL argument");
+    const size_t n = e->h_spk_stamp.size();
+    if (cap < n) return fail(BMTK_E_INVALID, "fetch_spikes: capacity %llu < %llu spikes", (unsigned long long)cap,
+                             (unsigned long long)n);
+    if (n && (!stamp_step || !id)) return fail(BMTK_E_INVALID, "fetch_spikes: NULL array");
+    // canonical order (stamp, id): the device appends in no particular order inside a step
+    std::vector<uint64_t> key(n);
+    for (size_t i = 0; i < n; ++i) key[i] = ((uint64_t)e->h_spk_stamp[i] << 32) | e->h_spk_id[i];
+    std::sort(key.begin(), key.end());
+    for (size_t i = 0; i < n; ++i) {
+        stamp_step[i] = (uint32_t)(key[i] >> 32);
+        id[i] = (uint32_t)key[i];
+    }
+    *n_out = n;
+    e->h_spk_stamp.clear();
+    e->h_spk_id.clear();
+    return BMTK_OK;
+}
+
+int bmtk_engine_trace_samples(bmtk_engine* e, uint64_t* n_samples) {
+    if (!e || !n_samples) return fail(BMTK_E_INVALID, "NULL argument");
+    *n_samples = e->probe_ids.empty() ? 0 : e->h_trace.size() / e->probe_ids.size();
+    return BMTK_OK;
+}
+
+int bmtk_engine_fetch_trace(bmtk_engine* e, uint64_t cap_samples, float* vm, uint64_t* n_out) {
+    if (!e || !n_out) return fail(BMTK_E_INVALID, "NULL argument");
+    const size_t n_ids = e->probe_ids.size();
+    const size_t n = n_ids ? e->h_trace.size() / n_ids : 0;
+    if (cap_samples < n) return fail(BMTK_E_INVALID, "fetch_trace: capacity too small");
+    if (n) std::memcpy(vm, e->h_trace.data(), 4 * n * n_ids);
+    *n_out = n;
+    e->h_trace.clear();
+    return BMTK_OK;
+}
+
+int bmtk_engine_get_state(bmtk_engine* e, const char* var, float* out) {
+    if (!e || !e->finalized || !var || !out) return fail(BMTK_E_INVALID, "get_state: bad argument");
+    int rc = set_device(e);
+    if (rc) return rc;
+    const std::string v(var);
+    const size_t n = e->n_local, np = e->n_pad;
+    const float* src = nullptr;
+    if (v == "U" || v == "V_m") src = e->st.U;
+    else if (v == "asc0") src = e->st.asc0;
+    else if (v == "asc1") src = e->st.asc1;
+    else if (v == "i_ext") src = e->st.i_ext;
+    else if (v == "th_spike") src = e->st.th_spike;
+    else if (v == "th_voltage") src = e->st.th_voltage;
+    else if (v.size() == 4 && v[0] == 'y' && (v[1] == '1' || v[1] == '2') && v[2] == '_' && v[3] >= '0' && v[3] < '0' + kPorts)
+        src = (v[1] == '1' ? e->st.y1 : e->st.y2) + (size_t)(v[3] - '0') * np;
+    else if (v == "refr") {
+        std::vector<int32_t> r(n);
+        CU(cudaStreamSynchronize(e->stream));
+        CU(cudaMemcpy(r.data(), e->st.refr, 4 * n, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < n; ++i) out[i] = (float)r[i];
+        return BMTK_OK;
+    } else return fail(BMTK_E_INVALID, "get_state: unknown variable '%s'", var);
+    if (!src) {
+        for (size_t i = 0; i < n; ++i) out[i] = 0.f;
+        return BMTK_OK;
+    }
+    CU(cudaStreamSynchronize(e->stream));
+    CU(cudaMemcpy(out, src, 4 * n, cudaMemcpyDeviceToHost));
+    if (v == "V_m")
+        for (size_t i = 0; i < n; ++i) out[i] += (float)e->types[e->type_index[i]].E_L;
+    return BMTK_OK;
+}
+
+int bmtk_engine_csr_info(bmtk_engine* e, uint64_t* n_rows, uint64_t* n_edges, uint32_t* target_bits, uint32_t* max_delay,
+                         uint32_t* min_delay, uint32_t* ring_slots) {
+    if (!e || !e->finalized) return fail(BMTK_E_INVALID, "csr_info: engine missing or not finalized");
+    if (n_rows) *n_rows = e->n_global + e->n_virtual;
+    if (n_edges) *n_edges = e->n_edges;
+    if (target_bits) *target_bits = e->target_bits;
+    if (max_delay) *max_delay = e->max_delay;
+    if (min_delay) *min_delay = e->min_delay;
+    if (ring_slots) *ring_slots = e->ring_slots;
+    return BMTK_OK;
+}
+
+int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, float* weight) {
+    if (!e || !e->finalized) return fail(BMTK_E_INVALID, "get_csr: engine missing or not finalized");
+    int rc = set_device(e);
+    if (rc) return rc;
+    const uint64_t n_rows = e->n_global + e->n_virtual;
+    CU(cudaStreamSynchronize(e->stream));
+    if (rowptr) CU(cudaMemcpy(rowptr, e->d_rowptr, 8 * (n_rows + 1), cudaMemcpyDeviceToHost));
+    if ((packed || weight) && e->n_edges) {
+        std::vector<uint2> h(e->n_edges);
+        CU(cudaMemcpy(h.data(), e->d_entries, 8 * e->n_edges, cudaMemcpyDeviceToHost));
+        for (uint64_t i = 0; i < e->n_edges; ++i) {
+            if (packed) packed[i] = h[i].x;
+            if (weight) std::memcpy(&weight[i], &h[i].y, 4);
+        }
+    }
+    return BMTK_OK;
+}
+
+int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
+    if (!e || !name || !out) return fail(BMTK_E_INVALID, "get_counter: NULL argument");
+    const std::string k(name);
+    if (k == "events") *out = e->events_total;
+    else if (k == "spikes") *out = e->spikes_total;
+    else if (k == "input_spikes") *out = e->input_spikes_total;
+    else if (k == "steps") *out = e->step;
+    else if (k == "launches") *out = e->launches;
+    else if (k == "window") *out = e->window;
+    else if (k == "update_ns") *out = (uint64_t)e->update_ns;
+    else if (k == "propagate_ns") *out = (uint64_t)e->prop_ns;
+    else if (k == "update_launches") *out = e->update_launches;
+    else if (k == "propagate_launches") *out = e->prop_launches;
+    else if (k == "spike_capacity") *out = e->send_cap;
+    else if (k == "n_pad") *out = e->n_pad;
+    else return fail(BMTK_E_INVALID, "unknown counter '%s'", name);
+    return BMTK_OK;
+}
+
+}  // extern "C"

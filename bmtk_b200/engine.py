@@ -1,0 +1,205 @@
+"""Python handle on one engine of the C ABI (one GPU / one rank).
+
+Plays the part PyNEST plays for bmtk.simulator.pointnet: nodes are created per node type, edges
+connected one-to-one with weight / delay / receptor arrays, virtual cells replay spike times,
+`run` is nest.Simulate, recorders are read back as arrays instead of NEST's .dat files.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import GlifParams, check
+
+# NEST's glif_psc defaults for keys a dynamics_params file omits.
+GLIF_PSC_DEFAULTS = dict(
+    V_m=-78.85, V_th=-51.68, g=9.43, E_L=-78.85, C_m=58.72, t_ref=3.75, V_reset=-78.85,
+    asc_init=(0.0, 0.0), asc_decay=(0.003, 0.1), asc_amps=(-9.18, -198.94), asc_r=(1.0, 1.0),
+    tau_syn=(2.0,), th_spike_add=0.37, th_spike_decay=0.009, voltage_reset_fraction=0.20,
+    voltage_reset_add=18.51, th_voltage_index=0.005, th_voltage_decay=0.09,
+    spike_dependent_threshold=False, after_spike_currents=False, adapting_threshold=False)
+
+
+def glif_params(d):
+    """NEST-format glif_psc parameter dict -> GlifParams (unknown keys are rejected)."""
+    if isinstance(d, GlifParams):
+        return d
+    unknown = set(d) - set(GLIF_PSC_DEFAULTS)
+    if unknown:
+        raise ValueError('unknown glif_psc parameter(s): %s' % ', '.join(sorted(unknown)))
+    q = dict(GLIF_PSC_DEFAULTS)
+    q.update(d)
+    p = GlifParams()
+    for k in ('V_m', 'V_th', 'g', 'E_L', 'C_m', 't_ref', 'V_reset', 'th_spike_add', 'th_spike_decay',
+              'voltage_reset_fraction', 'voltage_reset_add', 'th_voltage_index', 'th_voltage_decay'):
+        setattr(p, k, float(q[k]))
+    for k in ('asc_init', 'asc_decay', 'asc_amps', 'asc_r'):
+        v = [float(x) for x in q[k]]
+        if len(v) != 2:
+            raise ValueError('%s must have 2 entries' % k)
+        setattr(p, k, (C.c_double * 2)(*v))
+    ts = [float(x) for x in np.atleast_1d(q['tau_syn'])]
+    if not 1 <= len(ts) <= _cabi.MAX_PORTS:
+        raise ValueError('tau_syn must have 1..%d entries' % _cabi.MAX_PORTS)
+    p.n_ports = len(ts)
+    p.tau_syn = (C.c_double * _cabi.MAX_PORTS)(*(ts + [1.0] * (_cabi.MAX_PORTS - len(ts))))
+    p.spike_dependent_threshold = int(bool(q['spike_dependent_threshold']))
+    p.after_spike_currents = int(bool(q['after_spike_currents']))
+    p.adapting_threshold = int(bool(q['adapting_threshold']))
+    return p
+
+
+def _arr(a, dtype):
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def time_to_stamp(t_ms, dt):
+    """Spike time in ms -> stamp in steps: the first grid point at or after t (spike_generator
+    with precise_times, bmtk/simulator/pointnet/pointsimulator.py:69)."""
+    t = np.asarray(t_ms, dtype=np.float64)
+    return np.ceil(t / dt - 1e-9).astype(np.int64)
+
+
+class Engine(object):
+    def __init__(self, dt, device=0):
+        self._lib = _cabi.load()
+        self._h = C.c_void_p()
+        self.dt = float(dt)
+        self.device = int(device)
+        check(self._lib.bmtk_engine_create(C.byref(self._h), self.device, self.dt))
+        self.n_local = 0
+        self.lo = 0
+        self.n_probe = 0
+
+    def close(self):
+        if getattr(self, '_h', None) is not None and self._h:
+            self._lib.bmtk_engine_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- construction
+    def set_nodes(self, types, type_index, n_global=None, lo=0):
+        ti = _arr(type_index, np.uint16)
+        params = (GlifParams * len(types))(*[glif_params(t) for t in types])
+        n_local = len(ti)
+        n_global = n_local if n_global is None else int(n_global)
+        check(self._lib.bmtk_engine_set_nodes(self._h, n_global, int(lo), n_local, _ptr(ti), len(types),
+                                              C.cast(params, C.c_void_p)))
+        self.n_local, self.lo, self.n_global = n_local, int(lo), n_global
+
+    def set_virtual(self, n_virtual):
+        check(self._lib.bmtk_engine_set_virtual(self._h, int(n_virtual)))
+        self.n_virtual = int(n_virtual)
+
+    def add_edges(self, src, trg, weight, delay_steps, port):
+        src, trg = _arr(src, np.uint32), _arr(trg, np.uint32)
+        weight = _arr(weight, np.float32)
+        d = np.asarray(delay_steps)
+        if d.size and (d.max() > 65535 or d.min() < 0):
+            raise ValueError('delay_steps outside 0..65535')
+        delay_steps, port = _arr(d, np.uint16), _arr(port, np.uint8)
+        n = len(src)
+        if not (len(trg) == len(weight) == len(delay_steps) == len(port) == n):
+            raise ValueError('edge arrays differ in length')
+        check(self._lib.bmtk_engine_add_edges(self._h, n, _ptr(src), _ptr(trg), _ptr(weight), _ptr(delay_steps),
+                                              _ptr(port)))
+
+    def set_input_spikes(self, virt_index, stamp_step):
+        v, s = _arr(virt_index, np.uint32), _arr(stamp_step, np.uint32)
+        if len(v) != len(s):
+            raise ValueError('input spike arrays differ in length')
+        check(self._lib.bmtk_engine_set_input_spikes(self._h, len(v), _ptr(v), _ptr(s)))
+
+    def set_poisson(self, rate_hz, seed):
+        r = _arr(rate_hz, np.float32)
+        if len(r) != getattr(self, 'n_virtual', 0):
+            raise ValueError('one rate per virtual cell is required')
+        check(self._lib.bmtk_engine_set_poisson(self._h, _ptr(r), int(seed)))
+
+    def set_clamp_events(self, step, target, delta_pA):
+        s, t, d = _arr(step, np.uint64), _arr(target, np.uint32), _arr(delta_pA, np.float32)
+        check(self._lib.bmtk_engine_set_clamp_events(self._h, len(s), _ptr(s), _ptr(t), _ptr(d)))
+
+    def record_spikes(self, enable=True):
+        check(self._lib.bmtk_engine_record_spikes(self._h, int(bool(enable))))
+
+    def record_vm(self, ids, interval_steps=1):
+        ids = _arr(ids, np.uint32)
+        check(self._lib.bmtk_engine_record_vm(self._h, len(ids), _ptr(ids), int(interval_steps)))
+        self.n_probe = len(ids)
+
+    def set_option(self, key, value):
+        check(self._lib.bmtk_engine_set_option(self._h, key.encode(), int(value)))
+
+    def comm_init(self, uid, rank, n_ranks, libnccl=None):
+        buf = (C.c_char * 128).from_buffer_copy(bytes(uid)) if uid is not None else None
+        check(self._lib.bmtk_engine_comm_init(self._h, buf, int(rank), int(n_ranks),
+                                              libnccl.encode() if libnccl else None))
+
+    def finalize(self):
+        check(self._lib.bmtk_engine_finalize(self._h))
+
+    # ---- simulation
+    def run(self, n_steps):
+        check(self._lib.bmtk_engine_run(self._h, int(n_steps)))
+
+    def fetch_spikes(self):
+        """(stamp_step uint32[], id uint32[]) sorted by (stamp, id); drains the store."""
+        n = C.c_uint64()
+        check(self._lib.bmtk_engine_spike_count(self._h, C.byref(n)))
+        st = np.empty(n.value, dtype=np.uint32)
+        ids = np.empty(n.value, dtype=np.uint32)
+        out = C.c_uint64()
+        check(self._lib.bmtk_engine_fetch_spikes(self._h, n.value, _ptr(st), _ptr(ids), C.byref(out)))
+        return st[:out.value], ids[:out.value]
+
+    def fetch_trace(self):
+        """float32[samples, n_probe] of V_m; drains the store."""
+        n = C.c_uint64()
+        check(self._lib.bmtk_engine_trace_samples(self._h, C.byref(n)))
+        tr = np.empty((n.value, self.n_probe), dtype=np.float32)
+        out = C.c_uint64()
+        check(self._lib.bmtk_engine_fetch_trace(self._h, n.value, _ptr(tr), C.byref(out)))
+        return tr[:out.value]
+
+    def state(self, var):
+        out = np.empty(self.n_local, dtype=np.float32)
+        check(self._lib.bmtk_engine_get_state(self._h, var.encode(), _ptr(out)))
+        return out
+
+    def csr_info(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        c, d, e, f = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        check(self._lib.bmtk_engine_csr_info(self._h, C.byref(a), C.byref(b), C.byref(c), C.byref(d), C.byref(e),
+                                             C.byref(f)))
+        return dict(n_rows=a.value, n_edges=b.value, target_bits=c.value, max_delay=d.value, min_delay=e.value,
+                    ring_slots=f.value)
+
+    def csr(self):
+        """(rowptr uint64[n_rows+1], packed uint32[E], weight float32[E])."""
+        info = self.csr_info()
+        rowptr = np.empty(info['n_rows'] + 1, dtype=np.uint64)
+        packed = np.empty(info['n_edges'], dtype=np.uint32)
+        weight = np.empty(info['n_edges'], dtype=np.float32)
+        check(self._lib.bmtk_engine_get_csr(self._h, _ptr(rowptr), _ptr(packed), _ptr(weight)))
+        return rowptr, packed, weight
+
+    def counter(self, name):
+        v = C.c_uint64()
+        check(self._lib.bmtk_engine_get_counter(self._h, name.encode(), C.byref(v)))
+        return v.value
+
+
+def nccl_unique_id(libnccl=None):
+    buf = (C.c_char * 128)()
+    check(_cabi.load().bmtk_comm_unique_id(buf, libnccl.encode() if libnccl else None))
+    return bytes(buf)

@@ -1,0 +1,169 @@
+/*
+ * bmtk_b200 C ABI — the B200 point-neuron engine that stands where BMTK PointNet calls NEST.
+ *
+ * The reference has no native FFI on this path: bmtk.simulator.pointnet talks to its engine
+ * only through PyNEST calls. Each entry point below names the PyNEST call site(s) it replaces
+ * (paths relative to the bmtk source tree). Host code binds these with ctypes
+ * (bmtk_b200/_cabi.py).
+ *
+ * Conventions: every function returns 0 on success or a negative BMTK_E_* code;
+ * bmtk_last_error() gives the message of the calling thread's last failure. Nothing throws
+ * across the boundary and no device trap is ever raised on purpose. All pointers are HOST
+ * pointers unless a parameter is named d_*; the engine copies what it needs. One engine per
+ * GPU / per rank, driven by one host thread.
+ */
+#ifndef BMTK_B200_H
+#define BMTK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define BMTK_MAX_PORTS 4
+
+enum {
+    BMTK_OK = 0,
+    BMTK_E_INVALID = -1,    /* bad argument / call order */
+    BMTK_E_CUDA = -2,       /* a CUDA call failed (message has the CUDA error string) */
+    BMTK_E_OVERFLOW = -3,   /* a fixed-capacity device buffer (spike list, log, events) filled up */
+    BMTK_E_UNSUPPORTED = -4,
+    BMTK_E_COMM = -5,       /* NCCL unavailable or a collective failed */
+    BMTK_E_DELAY = -6       /* a synaptic delay is shorter than one step */
+};
+
+/* NEST `glif_psc` parameters under their NEST names, as found in a NEST-format
+ * dynamics_params file or produced by convert_aibs2nest
+ * (bmtk/simulator/pointnet/glif_utils.py:259-418). Units: mV, pF, nS, ms, pA, 1/ms. */
+typedef struct bmtk_glif_params {
+    double V_m, V_th, g, E_L, C_m, t_ref, V_reset;
+    double asc_init[2], asc_decay[2], asc_amps[2], asc_r[2];
+    double tau_syn[BMTK_MAX_PORTS];
+    double th_spike_add, th_spike_decay, voltage_reset_fraction, voltage_reset_add;
+    double th_voltage_index, th_voltage_decay;
+    int32_t n_ports;                    /* length of tau_syn in use, 1..BMTK_MAX_PORTS */
+    int32_t spike_dependent_threshold;  /* "R" */
+    int32_t after_spike_currents;       /* "ASC" */
+    int32_t adapting_threshold;         /* "A" */
+} bmtk_glif_params;
+
+typedef struct bmtk_engine bmtk_engine;
+
+const char* bmtk_last_error(void);
+/* Library version string, e.g. "bmtk_b200 0.1 sm_100a". */
+const char* bmtk_version(void);
+
+/* nest.ResetKernel + nest.SetKernelStatus({'resolution': dt, ...})
+ * (bmtk/simulator/pointnet/pointsimulator.py:73-74). `device` is a CUDA ordinal. */
+int bmtk_engine_create(bmtk_engine** out, int device, double dt_ms);
+int bmtk_engine_destroy(bmtk_engine* e);
+
+/* nest.Create(model, n, params), one call per node type
+ * (bmtk/simulator/pointnet/sonata_adaptors.py:64-66, pointnetwork.py:144-159).
+ * The network has n_global neurons with ids 0..n_global-1; this engine owns the contiguous
+ * block [lo, lo+n_local). type_index[i] (i local) selects types[]. */
+int bmtk_engine_set_nodes(bmtk_engine* e, uint64_t n_global, uint64_t lo, uint64_t n_local,
+                          const uint16_t* type_index, int32_t n_types, const bmtk_glif_params* types);
+
+/* nest.Create('spike_generator', n) for virtual cells (pointnetwork.py:187-216). Virtual cell v
+ * is source id n_global + v in edge lists. */
+int bmtk_engine_set_virtual(bmtk_engine* e, uint64_t n_virtual);
+
+/* nest.Connect(srcs, trgs, 'one_to_one', syn_spec{weight[], delay[], receptor_type})
+ * (pointnetwork.py:229-248; per-edge-type values from sonata_adaptors.py:268-357).
+ * src: global source id (neuron or n_global+virtual); trg: global neuron id inside this engine's
+ * block; weight in pA; delay in steps (>= 1, else BMTK_E_DELAY — the reference raises BadDelay,
+ * pointnetwork.py:234-243); port 0-based (NEST receptor_type - 1). May be called several times
+ * before finalize; edges accumulate in call order. */
+int bmtk_engine_add_edges(bmtk_engine* e, uint64_t n_edges, const uint32_t* src, const uint32_t* trg,
+                          const float* weight, const uint16_t* delay_steps, const uint8_t* port);
+
+/* nest.SetStatus(spike_generator, {'spike_times': ...}) (pointnetwork.py:52-61). Spikes are given
+ * as (virtual index, stamp in steps = ceil(t/dt) >= 1), any order. Replaces all stamps greater
+ * than the current step; may be called between runs to stream inputs. */
+int bmtk_engine_set_input_spikes(bmtk_engine* e, uint64_t n, const uint32_t* virt_index,
+                                 const uint32_t* stamp_step);
+
+/* On-line Poisson virtual cells (no counterpart in the reference, which only replays files made
+ * by PoissonSpikeGenerator, bmtk/utils/reports/spike_trains/spike_trains.py:166-206): source v
+ * fires k times in step n with k ~ Poisson(rate_hz[v]*dt), drawn from Philox4x32-10 with
+ * counter (v, n) and key `seed`. rate_hz has n_virtual entries; rate*dt must be <= 0.25. */
+int bmtk_engine_set_poisson(bmtk_engine* e, const float* rate_hz, uint64_t seed);
+
+/* nest.Create('step_current_generator', {amplitude_times, amplitude_values}) + Connect with
+ * delay = dt (bmtk/simulator/pointnet/modules/iclamp.py:42-54). Events: at the start of step
+ * `step[i]` the external current of global neuron target[i] changes by delta_pA[i]. An amplitude
+ * listed at time T becomes effective at step round(T/dt)+1. */
+int bmtk_engine_set_clamp_events(bmtk_engine* e, uint64_t n, const uint64_t* step, const uint32_t* target,
+                                 const float* delta_pA);
+
+/* nest.Create('spike_recorder') + Connect(all gids, recorder)
+ * (bmtk/simulator/pointnet/modules/record_spikes.py:134-136). */
+int bmtk_engine_record_spikes(bmtk_engine* e, int enable);
+
+/* nest.Create('multimeter', {'record_from': ['V_m'], 'interval': ...}) + Connect(mm, gids)
+ * (bmtk/simulator/pointnet/modules/multimeter_reporter.py:103-115). ids are global neuron ids in
+ * this engine's block; sample k (k >= 1) is V_m after the step that ends at k*interval. */
+int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps);
+
+/* Options (before finalize unless noted):
+ *  "deterministic"  0|1  sorted segmented reduction instead of atomics in spike delivery
+ *  "window"         steps per exchange window, 0 = min delay (default)
+ *  "spike_capacity" entries of the per-window spike list, 0 = automatic
+ *  "log_capacity"   entries of the device spike log between host drains
+ *  "event_capacity" events per window the deterministic path can sort
+ *  "use_graph"      0|1 replay each window as a CUDA graph (default 1)
+ *  "chunk_steps"    steps between host drains of the spike log / traces */
+int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
+
+/* Multi-GPU spike exchange: replaces NEST's MPI exchange inside nest.Simulate. uid is the
+ * 128-byte ncclUniqueId made by bmtk_comm_unique_id on rank 0 and distributed by the caller;
+ * libnccl is the path of the NCCL shared object to use (NULL = "libnccl.so.2"). */
+int bmtk_comm_unique_id(void* uid128, const char* libnccl);
+int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ranks, const char* libnccl);
+
+/* Builds the delay-bucketed CSR on the device, allocates state and ring buffers, initialises
+ * V = V_m, ASC = asc_init. Must precede run. */
+int bmtk_engine_finalize(bmtk_engine* e);
+
+/* nest.Simulate(n_steps*dt) (bmtk/simulator/pointnet/pointsimulator.py:166). */
+int bmtk_engine_run(bmtk_engine* e, uint64_t n_steps);
+
+/* Recorder read-out (record_spikes.py:138-161 / multimeter_reporter.py:117-167 read NEST's .dat
+ * files instead). Spikes are returned sorted by (stamp, id); stamp is in steps (time = stamp*dt),
+ * id is the global neuron id. Fetching drains the host-side store. */
+int bmtk_engine_spike_count(bmtk_engine* e, uint64_t* n);
+int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step, uint32_t* id, uint64_t* n_out);
+int bmtk_engine_trace_samples(bmtk_engine* e, uint64_t* n_samples);
+int bmtk_engine_fetch_trace(bmtk_engine* e, uint64_t cap_samples, float* vm /* [samples][n_ids] */,
+                            uint64_t* n_out);
+
+/* State read-out for tests/checkpoints: var in {"V_m","U","asc0","asc1","y1_0".."y1_3","y2_0".."y2_3",
+ * "i_ext","th_spike","th_voltage"}; out has n_local floats. "refr" returns the counter as float. */
+int bmtk_engine_get_state(bmtk_engine* e, const char* var, float* out);
+
+/* CSR read-out for bit-exact checks against an independent build. rowptr has n_rows+1 entries;
+ * packed[k] = delay << (target_bits+2) | port << target_bits | local_target. Pass NULL to query
+ * sizes only. */
+int bmtk_engine_csr_info(bmtk_engine* e, uint64_t* n_rows, uint64_t* n_edges, uint32_t* target_bits,
+                         uint32_t* max_delay, uint32_t* min_delay, uint32_t* ring_slots);
+int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, float* weight);
+
+/* Counters: "events" (synaptic events delivered), "spikes" (neuron spikes), "steps",
+ * "launches" (kernels launched by run), "update_ns"/"propagate_ns" (device time when
+ * option "profile" is 1), "window". */
+int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BMTK_B200_H */

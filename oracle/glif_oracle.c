@@ -406,3 +406,25 @@ int32_t orc_poisson_count(uint32_t source, uint64_t step, uint64_t seed, const u
     for (int j = 0; j < 4; ++j) k += out[0] >= thr[j];
     return k;
 }
+
+/* All Poisson spikes of steps [step0, step0+n_steps) for n_virtual sources with per-source
+ * thresholds thr[4*v..4*v+3], ordered by (step, source); a count of k gives k entries.
+ * Returns the number of spikes (entries beyond cap are counted, not stored). */
+int64_t orc_poisson_fill(int64_t n_virtual, const uint32_t* thr, uint64_t seed, int64_t step0, int64_t n_steps,
+                         int64_t cap, int64_t* emit_step, int32_t* source)
+{
+    int64_t n = 0;
+    for (int64_t s = step0; s < step0 + n_steps; ++s) {
+        for (int64_t v = 0; v < n_virtual; ++v) {
+            const int32_t k = orc_poisson_count((uint32_t)v, (uint64_t)s, seed, thr + 4 * v);
+            for (int32_t j = 0; j < k; ++j) {
+                if (n < cap) {
+                    emit_step[n] = s;
+                    source[n] = (int32_t)v;
+                }
+                ++n;
+            }
+        }
+    }
+    return n;
+}

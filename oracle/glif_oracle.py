@@ -131,6 +131,9 @@ def lib():
         _lib.orc_poisson_thresholds.argtypes = [C.c_double, C.POINTER(C.c_uint32)]
         _lib.orc_poisson_count.argtypes = [C.c_uint32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint32)]
         _lib.orc_poisson_count.restype = C.c_int32
+        _lib.orc_poisson_fill.argtypes = [C.c_int64, C.c_void_p, C.c_uint64, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_void_p, C.c_void_p]
+        _lib.orc_poisson_fill.restype = C.c_int64
     return _lib
 
 
@@ -162,16 +165,17 @@ def poisson_spikes(rates_hz, dt, seed, step0, n_steps):
     (step, source)."""
     L = lib()
     rates_hz = np.asarray(rates_hz, dtype=np.float64)
-    thr = [poisson_thresholds(r * dt * 1e-3) for r in rates_hz]
-    thr_c = [(C.c_uint32 * 4)(*[int(x) for x in t]) for t in thr]
-    steps, srcs = [], []
-    for n in range(step0, step0 + n_steps):
-        for v in range(len(rates_hz)):
-            k = L.orc_poisson_count(v, n, int(seed), thr_c[v])
-            for _ in range(k):
-                steps.append(n)
-                srcs.append(v)
-    return np.asarray(steps, dtype=np.int64), np.asarray(srcs, dtype=np.int32)
+    thr = np.ascontiguousarray(np.concatenate([poisson_thresholds(r * dt * 1e-3) for r in rates_hz])
+                               if len(rates_hz) else np.zeros(0, dtype=np.uint32), dtype=np.uint32)
+    cap = int(rates_hz.sum() * dt * 1e-3 * n_steps * 1.5 + 1000)
+    while True:
+        steps = np.zeros(cap, dtype=np.int64)
+        srcs = np.zeros(cap, dtype=np.int32)
+        n = L.orc_poisson_fill(len(rates_hz), _ptr(thr), int(seed), int(step0), int(n_steps), cap,
+                               _ptr(steps), _ptr(srcs))
+        if n <= cap:
+            return steps[:n].copy(), srcs[:n].copy()
+        cap = int(n)
 
 
 def build_csr(n_rows, src, trg, weight, delay_steps, port):
