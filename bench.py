@@ -1,0 +1,386 @@
+"""Benchmark of the point-neuron hot path on the V1-scale synthetic network.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("c3"): 230 924 GLIF-3 neurons in 17 types, ~70 M synapses from a Gaussian distance
+rule, 17 400 Poisson virtual cells, dt = 0.25 ms (bmtk_b200.workloads.c3; synthetic, seeded).
+One bench STEP simulates 1000 ms of biological time = 4000 update steps. Metric: synaptic events
+delivered per wall second (whole job), with sim-ms per wall-ms beside it.
+
+  value  device-resident: Poisson cells generated on the GPU (Philox), spikes logged on the GPU;
+         timed with CUDA events on the engine's stream, max over ranks.
+  e2e    through the public Engine API with HOST buffers: every step hands that second's virtual
+         spikes over from pinned host memory (set_input_spikes), runs, and reads the spike
+         list back (fetch_spikes); wall clock between barriers.
+  roofline  per-launch CUDA-event time of the dominant kernel in a profiled pass of the same
+         workload, against algorithmic bytes (128 B per neuron-step, 16 B per synaptic event).
+  cpu_baseline  the fp64 CPU oracle (OpenMP port; the reference's own engine, NEST, is not
+         available) on a bounded slice of the same network, rank 0, N = 1 only.
+
+With N > 1 the neurons are split into N contiguous blocks (strong scaling: the network is fixed);
+each rank owns the CSR rows of its targets and the ranks all-gather the spike ids of every
+min-delay window with NCCL.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BYTES_PER_NEURON_STEP = 128.0
+BYTES_PER_EVENT = 16.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu (see profiles/); None until captured
+NCU_TRAFFIC_BYTES = {'glif_update': None, 'propagate': None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--scale', type=float, default=1.0, help='shrink the network (testing only)')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-cpu', action='store_true')
+    ap.add_argument('--cpu-slice-ms', type=float, default=250.0)
+    ap.add_argument('--step-ms', type=float, default=1000.0, help='simulated ms per bench step (1000 = the configuration)')
+    return ap.parse_args()
+
+
+def make_network(scale, lo_hi=None, poisson_online=True):
+    from bmtk_b200 import workloads as W
+    n = int(round(230924 * scale))
+    nv = max(8, int(round(17400 * scale)))
+    radius = 845.0 * np.sqrt(scale)
+    lo, hi = lo_hi if lo_hi else (0, n)
+    return W.c3(n=n, n_virtual=nv, radius_um=radius, lo=lo, hi=hi, poisson_online=poisson_online)
+
+
+def peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        return float(json.load(open(p))['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler(object):
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms during the timed region."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+         'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(['nvidia-smi', '-i', str(gpu_index), '--query-gpu=' + self.Q,
+                                       '--format=csv,noheader,nounits', '-lms', '100'], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons, pw = [], [], set(), []
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in self.f.read().splitlines():
+            c = [x.strip() for x in line.split(',')]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2])); pw.append(float(c[3]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, c[5:9]):
+                if v.lower().startswith('active'):
+                    reasons.add(nm)
+        self.f.close()
+        os.unlink(self.f.name)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
+                       samples=len(sm), power_w_max=float(max(pw)))
+        return out
+
+
+def poisson_chunk(rng, rates_hz, dt, step0, n_steps):
+    """Virtual spikes of one chunk for the replayed (host-buffer) mode: a superposition of Poisson
+    processes has a Poisson total count, sources drawn in proportion to their rate, times uniform."""
+    lam = rates_hz.sum() * n_steps * dt * 1e-3
+    n = rng.poisson(lam)
+    src = rng.choice(len(rates_hz), size=n, p=rates_hz / rates_hz.sum()).astype(np.uint32)
+    stamp = (step0 + 1 + rng.integers(0, n_steps, size=n)).astype(np.uint32)
+    return src, stamp
+
+
+def run_cpu(net, slice_ms, threads, n_slices=1):
+    """Oracle (OpenMP port of the engine contract) prepared for `n_slices` runs of `slice_ms`."""
+    from oracle import glif_oracle as O
+    O.build()
+    n_steps = int(round(slice_ms / net.dt))
+    t0 = time.time()
+    sim = O.OracleSim(net.types, net.type_index, net.dt, n_virtual=net.n_virtual, src=net.src, trg=net.trg,
+                      weight=net.weight, delay_steps=net.delay_steps, port=net.port, n_threads=threads,
+                      canonical_csr=False)
+    steps, srcs = O.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, n_steps * n_slices)
+    sim.set_input_spikes(steps, srcs)
+    t_setup = time.time() - t0
+    return sim, n_steps, t_setup
+
+
+def reference_arm(args):
+    """Times the CPU implementation of the path on the host cores. The reference's own engine is
+    NEST (third-party C++, not in the reference tree, not installed), so this is the repo's fp64
+    oracle port with all host threads; each step is a bounded slice of the same workload."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    net = make_network(args.scale)
+    slice_ms = 100.0
+    sim, n_steps, _ = run_cpu(net, slice_ms, threads, args.warmup + args.steps)
+    for _ in range(args.warmup):
+        sim.run(n_steps, record_spikes=False)
+    ev = 0
+    t0 = time.time()
+    for _ in range(args.steps):
+        ev += sim.run(n_steps, record_spikes=False)['n_events']
+    wall = time.time() - t0
+    val = ev / wall
+    line = {
+        'impl': 'reference', 'metric': 'synaptic_events_per_sec', 'value': val, 'unit': 'events/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * wall / args.steps,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f64', 'data': 'synthetic',
+        'sim_ms_per_wall_ms': slice_ms * args.steps / (wall * 1e3),
+        'config': {'workload': 'c3: %d GLIF-3 neurons, %d synapses, %d Poisson cells, dt 0.25 ms'
+                               % (net.n_neurons, net.n_edges, net.n_virtual),
+                   'step': '%g ms of simulated time per step (bounded slice of the 1000 ms bench step)' % slice_ms},
+        'cpu_baseline': {'value': val, 'unit': 'events/s', 'cores': threads, 'kind': 'port',
+                         'sample': '%d consecutive %g ms slices after %d warm-up slices, fp64 oracle, OpenMP'
+                                   % (args.steps, slice_ms, args.warmup)},
+        'e2e': {'value': val, 'unit': 'events/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse_args()
+    STEP_MS = args.step_ms
+    if args.impl == 'reference':
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from bmtk_b200 import workloads as W
+    from bmtk_b200.engine import nccl_unique_id
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: bmtk_b200 has no CPU path')
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    uid, libnccl = None, None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=dev)
+        libnccl = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), 'nvidia', 'nccl', 'lib', 'libnccl.so.2')
+        if not os.path.exists(libnccl):
+            libnccl = None
+        buf = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            buf.copy_(torch.frombuffer(bytearray(nccl_unique_id(libnccl)), dtype=torch.uint8))
+        dist.broadcast(buf, 0)
+        uid = bytes(buf.cpu().numpy().tobytes())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def reduce(x, op):
+        if world == 1:
+            return x
+        t = torch.tensor([float(x)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    n_total = int(round(230924 * args.scale))
+    bounds = np.linspace(0, n_total, world + 1).astype(np.int64)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    t0 = time.time()
+    net = make_network(args.scale, (lo, hi))
+    t_gen = time.time() - t0
+    steps_per_bench_step = int(round(STEP_MS / net.dt))
+
+    # ---------------- device-resident run
+    t0 = time.time()
+    eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
+                         options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=uid,
+                         libnccl=libnccl)
+    t_build = time.time() - t0
+    for _ in range(args.warmup):
+        eng.run(steps_per_bench_step)
+        eng.fetch_spikes()
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, sp0, l0 = eng.counter('events'), eng.counter('spikes'), eng.counter('launches')
+    eng.mark(0)
+    w0 = time.time()
+    for _ in range(args.steps):
+        eng.run(steps_per_bench_step)
+    eng.mark(1)
+    dev_ms = eng.elapsed_ms(0, 1)
+    torch.cuda.synchronize()
+    wall_ms = (time.time() - w0) * 1e3
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    eng.fetch_spikes()
+    dev_ms = reduce(dev_ms, dist.ReduceOp.MAX if world > 1 else None)
+    wall_ms = reduce(wall_ms, dist.ReduceOp.MAX if world > 1 else None)
+    events = reduce(eng.counter('events') - ev0, dist.ReduceOp.SUM if world > 1 else None)
+    spikes = reduce(eng.counter('spikes') - sp0, dist.ReduceOp.SUM if world > 1 else None)
+    launches = reduce(eng.counter('launches') - l0, dist.ReduceOp.SUM if world > 1 else None)
+    value = events / (dev_ms * 1e-3)
+
+    # ---------------- profiled pass: per-launch CUDA events around both kernels
+    prof_steps = min(steps_per_bench_step, 800)
+    eng.set_option('profile', 1)
+    e0 = eng.counter('events')
+    eng.run(prof_steps)
+    eng.set_option('profile', 0)
+    eng.fetch_spikes()
+    up_ns, up_n = eng.counter('update_ns'), max(1, eng.counter('update_launches'))
+    pr_ns, pr_n = eng.counter('propagate_ns'), max(1, eng.counter('propagate_launches'))
+    prof_events = eng.counter('events') - e0
+    n_pad = eng.counter('n_pad')
+    peak, peak_kind = peaks()
+    up_bytes = BYTES_PER_NEURON_STEP * n_pad
+    pr_bytes = BYTES_PER_EVENT * prof_events / pr_n
+    kernels = {
+        'glif_update': {'launches': up_n, 'avg_us': up_ns / up_n * 1e-3, 'bytes_per_launch': up_bytes,
+                        'achieved_gbs': up_bytes / (up_ns / up_n), 'traffic': NCU_TRAFFIC_BYTES['glif_update']},
+        'propagate': {'launches': pr_n, 'avg_us': pr_ns / pr_n * 1e-3, 'bytes_per_launch': pr_bytes,
+                      'achieved_gbs': pr_bytes / (pr_ns / pr_n), 'traffic': NCU_TRAFFIC_BYTES['propagate']},
+    }
+    dom = 'glif_update' if up_ns >= pr_ns else 'propagate'
+    roofline = {'kernel': dom, 'bound': 'hbm', 'achieved': kernels[dom]['achieved_gbs'], 'peak': peak, 'unit': 'GB/s',
+                'frac': kernels[dom]['achieved_gbs'] / peak, 'traffic': kernels[dom]['traffic'], 'peak_kind': peak_kind,
+                'kernels': kernels}
+    window = eng.counter('window')
+    eng.close()
+
+    # ---------------- end to end with host buffers (replayed virtual spikes)
+    e2e = None
+    if not args.no_e2e:
+        net.poisson_rate_hz, rates = None, net.poisson_rate_hz.astype(np.float64)
+        eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
+                             options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=uid,
+                             libnccl=libnccl)
+        rng = np.random.default_rng(99)   # same seed on every rank: virtual cells are replicated
+        n_chunks = 1 + args.steps
+        cap = int(rates.sum() * STEP_MS * 1e-3 * 1.2) + 4096
+        pin_src = torch.empty((n_chunks, cap), dtype=torch.int32).pin_memory()
+        pin_stamp = torch.empty((n_chunks, cap), dtype=torch.int32).pin_memory()
+        counts = []
+        for c in range(n_chunks):
+            s, st = poisson_chunk(rng, rates, net.dt, c * steps_per_bench_step, steps_per_bench_step)
+            k = min(len(s), cap)
+            pin_src[c, :k] = torch.from_numpy(s[:k].astype(np.int32))
+            pin_stamp[c, :k] = torch.from_numpy(st[:k].astype(np.int32))
+            counts.append(k)
+        h2d = d2h = 0
+        ev_start = 0
+        for c in range(n_chunks):
+            if c == 1:
+                torch.cuda.synchronize()
+                barrier()
+                ev_start = eng.counter('events')
+                t_start = time.time()
+            k = counts[c]
+            eng.set_input_spikes(pin_src[c, :k].numpy().view(np.uint32), pin_stamp[c, :k].numpy().view(np.uint32))
+            eng.run(steps_per_bench_step)
+            st, ids = eng.fetch_spikes()
+            if c >= 1:
+                h2d += 8 * k
+                d2h += 8 * len(st)
+        torch.cuda.synchronize()
+        barrier()
+        e2e_wall = reduce(time.time() - t_start, dist.ReduceOp.MAX if world > 1 else None)
+        e2e_events = reduce(eng.counter('events') - ev_start, dist.ReduceOp.SUM if world > 1 else None)
+        e2e = {'value': e2e_events / e2e_wall, 'unit': 'events/s',
+               'h2d_bytes_per_step': int(reduce(h2d, dist.ReduceOp.SUM if world > 1 else None) / args.steps),
+               'd2h_bytes_per_step': int(reduce(d2h, dist.ReduceOp.SUM if world > 1 else None) / args.steps),
+               'sim_ms_per_wall_ms': STEP_MS * args.steps / (e2e_wall * 1e3),
+               'timing': 'wall clock between barriers, includes host-side packing and sorting of spikes'}
+        eng.close()
+        net.poisson_rate_hz = rates.astype(np.float32)
+
+    # ---------------- CPU baseline (rank 0, N = 1 only)
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sim, n_steps, t_setup = run_cpu(net, args.cpu_slice_ms, threads, 2)
+        sim.run(n_steps, record_spikes=False)      # untimed: lets the onset transient pass
+        t0 = time.time()
+        r = sim.run(n_steps, record_spikes=False)
+        t_cpu = time.time() - t0
+        cpu = {'value': r['n_events'] / t_cpu, 'unit': 'events/s', 'cores': threads, 'kind': 'port',
+               'sim_ms_per_wall_ms': args.cpu_slice_ms / (t_cpu * 1e3),
+               'sample': '%g ms of the same network after a %g ms untimed lead-in from rest (%d events, %d spikes, %.1f s), fp64 oracle, OpenMP'
+                         % (args.cpu_slice_ms, args.cpu_slice_ms, r['n_events'], r['n_spikes'], t_cpu)}
+
+    if rank == 0:
+        line = {
+            'metric': 'synaptic_events_per_sec', 'value': value, 'unit': 'events/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dev_ms / args.steps,
+            'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'sim_ms_per_wall_ms': STEP_MS * args.steps / dev_ms,
+            'config': {'workload': 'c3: %d GLIF-3 neurons in 17 types, %d synapses%s, %d Poisson cells, dt 0.25 ms'
+                                   % (n_total, int(reduce_edges(net, world, dist, dev)), '' if world == 1 else ' (all ranks)',
+                                      net.n_virtual),
+                       'step': '%g ms of simulated time = %d update steps' % (STEP_MS, steps_per_bench_step),
+                       'partition': 'neurons in %d contiguous blocks, one NCCL all-gather of spike ids per %d-step window'
+                                    % (world, window) if world > 1 else 'single GPU',
+                       'l2': 'state + ring (~80 MB) are re-read every step; the 560 MB CSR exceeds L2',
+                       'mean_rate_hz': spikes / n_total / (STEP_MS * 1e-3 * args.steps)},
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline, 'cpu_baseline': cpu,
+            'wall_ms_per_step': wall_ms / args.steps, 'setup_s': {'generate': t_gen, 'build_engine': t_build},
+        }
+        print(json.dumps(line))
+    else:
+        reduce_edges(net, world, dist, dev)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def reduce_edges(net, world, dist, dev):
+    if world == 1:
+        return net.n_edges
+    import torch
+    t = torch.tensor([float(net.n_edges)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t)
+    return t.item()
+
+
+if __name__ == '__main__':
+    main()

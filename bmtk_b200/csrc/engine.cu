@@ -284,6 +284,7 @@ struct bmtk_engine {
     uint64_t update_launches = 0, prop_launches = 0;
 
     DetWorkspace det{};
+    cudaEvent_t marks[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 namespace bmtk {
@@ -645,6 +646,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     drop_graph(e);
     for (auto ev : e->ev_pool) cudaEventDestroy(ev);
+    for (auto ev : e->marks) if (ev) cudaEventDestroy(ev);
     if (e->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(e->comm);
     det_free(e->det);
     cudaFree(e->st.U); cudaFree(e->st.asc0); cudaFree(e->st.asc1); cudaFree(e->st.y1); cudaFree(e->st.y2);
@@ -1113,6 +1115,28 @@ int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, floa
             if (weight) std::memcpy(&weight[i], &h[i].y, 4);
         }
     }
+    return BMTK_OK;
+}
+
+int bmtk_engine_mark(bmtk_engine* e, int slot) {
+    if (!e || slot < 0 || slot >= 8) return fail(BMTK_E_INVALID, "mark: slot must be 0..7");
+    int rc = set_device(e);
+    if (rc) return rc;
+    if (!e->marks[slot]) CU(cudaEventCreate(&e->marks[slot]));
+    CU(cudaEventRecord(e->marks[slot], e->stream));
+    return BMTK_OK;
+}
+
+int bmtk_engine_elapsed_ms(bmtk_engine* e, int from_slot, int to_slot, double* ms) {
+    if (!e || !ms || from_slot < 0 || from_slot >= 8 || to_slot < 0 || to_slot >= 8 || !e->marks[from_slot] ||
+        !e->marks[to_slot])
+        return fail(BMTK_E_INVALID, "elapsed_ms: both slots must have been marked");
+    int rc = set_device(e);
+    if (rc) return rc;
+    CU(cudaEventSynchronize(e->marks[to_slot]));
+    float f = 0.f;
+    CU(cudaEventElapsedTime(&f, e->marks[from_slot], e->marks[to_slot]));
+    *ms = (double)f;
     return BMTK_OK;
 }
 

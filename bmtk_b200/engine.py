@@ -193,6 +193,16 @@ class Engine(object):
         check(self._lib.bmtk_engine_get_csr(self._h, _ptr(rowptr), _ptr(packed), _ptr(weight)))
         return rowptr, packed, weight
 
+    def mark(self, slot):
+        """Records a CUDA event on the engine's stream in slot 0..7."""
+        check(self._lib.bmtk_engine_mark(self._h, int(slot)))
+
+    def elapsed_ms(self, from_slot, to_slot):
+        """Device time between two marks (waits for the later one)."""
+        ms = C.c_double()
+        check(self._lib.bmtk_engine_elapsed_ms(self._h, int(from_slot), int(to_slot), C.byref(ms)))
+        return ms.value
+
     def counter(self, name):
         v = C.c_uint64()
         check(self._lib.bmtk_engine_get_counter(self._h, name.encode(), C.byref(v)))

@@ -246,8 +246,8 @@ def c2(n=50000, in_degree=1000, t_stop_ms=1000.0, dt=0.1, seed=1236, n_virtual=2
     return net
 
 
-def c3(n=230924, mean_in_degree=303.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_virtual=17400, lo=0, hi=None,
-       radius_um=845.0, input_weight=25.0, poisson_online=True, w_scale=1.0, virt_out_degree=200):
+def c3(n=230924, mean_in_degree=330.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_virtual=17400, lo=0, hi=None,
+       radius_um=845.0, input_weight=45.0, poisson_online=True, w_scale=1.0, virt_out_degree=200):
     """V1-scale network: n GLIF-3 neurons in 17 types (13 excitatory, 4 inhibitory; 85 % / 15 %)
     placed uniformly on a disk; P(i -> j) proportional to exp(-d^2 / 2 sigma^2) with sigma drawn in
     100-200 um per (source class, target type); weights lognormal per (source type, target type)
@@ -256,9 +256,11 @@ def c3(n=230924, mean_in_degree=303.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_v
 
     Sampling: for every target a Poisson number of candidate synapses is drawn; each candidate
     picks a source class, a Gaussian displacement with that pair's sigma, and then a uniformly
-    random neuron of that class inside the 10 um grid cell the displaced point falls in
-    (candidates landing outside the disk or in an empty cell are dropped, which thins in-degree
-    near the rim exactly as a distance rule does).
+    random neuron of that class inside the 20 um grid cell the displaced point falls in; a cell
+    holding c neurons keeps the candidate with probability c / c_max, which makes every neuron's
+    chance proportional to the kernel at its cell. Candidates landing outside the disk are
+    dropped, which thins in-degree near the rim exactly as a distance rule does; mean_in_degree
+    = 330 candidates gives ~303 synapses per neuron, ~70 M in all.
     """
     hi = n if hi is None else hi
     rng = np.random.default_rng(seed)
@@ -280,8 +282,8 @@ def c3(n=230924, mean_in_degree=303.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_v
     w_mu = np.log(rng.uniform(0.8, 2.5, size=(n_types, n_types)))  # (source type, target type)
     w_sigma = 0.5
     is_inh = inh[net.type_index]
-    # 10 um grid per source class: neurons of the class sorted by cell
-    cell = 10.0
+    # 20 um grid per source class: neurons of the class sorted by cell
+    cell = 20.0
     g = int(np.ceil(2 * radius_um / cell)) + 1
     grids = []
     for c in (False, True):
@@ -292,46 +294,52 @@ def c3(n=230924, mean_in_degree=303.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_v
         order = np.argsort(key, kind='stable')
         cnt = np.bincount(key, minlength=g * g)
         start = np.concatenate([[0], np.cumsum(cnt)[:-1]])
-        grids.append((ids[order], start, cnt))
+        grids.append((ids[order], start, cnt, float(cnt.max())))
     n_class = np.array([np.sum(~is_inh), np.sum(is_inh)], dtype=np.float64)
+    # expected fraction of candidates that survive the density correction, per class
+    acc = np.array([n_class[c] / (np.count_nonzero(grids[c][2]) * grids[c][3]) for c in (0, 1)])
     n_blocks = (n + BLOCK - 1) // BLOCK
     rngs = _block_rngs(seed + 1, n_blocks)
-    parts = []
-    for b in range(n_blocks):
+
+    def make_block(b):
         b0, b1 = b * BLOCK, min((b + 1) * BLOCK, n)
-        if b1 <= lo or b0 >= hi:
-            continue
         r = rngs[b]
         tb0, tb1 = max(b0, lo), min(b1, hi)
-        # draw for the whole block (keeps the stream independent of the partition), then filter
-        k = r.poisson(mean_in_degree, size=b1 - b0)
+        # candidates are drawn for the whole block (the stream does not depend on the partition)
+        tt_blk = net.type_index[b0:b1]
+        pe = n_class[0] * sigma[0, tt_blk] ** 2
+        pi = n_class[1] * sigma[1, tt_blk] ** 2
+        # oversample so that mean_in_degree survives the density correction on average
+        lam = mean_in_degree * (pe / acc[0] + pi / acc[1]) / (pe + pi)
+        k = r.poisson(lam)
         t = np.repeat(np.arange(b0, b1, dtype=np.int64), k)
         tt = net.type_index[t]
-        # source class with probability proportional to n_class * sigma^2
-        pe = n_class[0] * sigma[0, tt] ** 2
-        pi = n_class[1] * sigma[1, tt] ** 2
-        sc = (r.random(len(t)) * (pe + pi) >= pe).astype(np.int64)
+        qe = np.repeat(pe / acc[0], k)
+        qi = np.repeat(pi / acc[1], k)
+        sc = (r.random(len(t)) * (qe + qi) >= qe).astype(np.int64)
         sg = sigma[sc, tt]
         px = x[t] + r.normal(size=len(t)) * sg
         py = y[t] + r.normal(size=len(t)) * sg
         u = r.random(len(t))
+        u2 = r.random(len(t))
         wz = r.normal(size=len(t))
         dd = r.uniform(0.5, 4.0, size=len(t))
         ok = px * px + py * py < radius_um * radius_um
         ok &= (t >= tb0) & (t < tb1)
-        t, sc, px, py, u, wz, dd = t[ok], sc[ok], px[ok], py[ok], u[ok], wz[ok], dd[ok]
+        t, sc, px, py, u, u2, wz, dd = t[ok], sc[ok], px[ok], py[ok], u[ok], u2[ok], wz[ok], dd[ok]
         key = ((px + radius_um) / cell).astype(np.int64) * g + ((py + radius_um) / cell).astype(np.int64)
-        s = np.empty(len(t), dtype=np.int64)
+        s = np.zeros(len(t), dtype=np.int64)
         good = np.zeros(len(t), dtype=bool)
         for c in (0, 1):
-            m = sc == c
-            ids, start, cnt = grids[c]
+            m = np.nonzero(sc == c)[0]
+            ids, start, cnt, cmax = grids[c]
             kc = key[m]
             cn = cnt[kc]
-            has = cn > 0
+            # density correction: a cell with cn neurons keeps a candidate with probability cn/cmax,
+            # so every neuron is hit in proportion to the kernel at its cell, not to 1/local density
+            has = u2[m] * cmax < cn
             pick = start[kc] + np.minimum((u[m] * cn).astype(np.int64), np.maximum(cn - 1, 0))
-            sel = np.where(has, ids[np.minimum(pick, len(ids) - 1)], 0)
-            s[m] = sel
+            s[m] = np.where(has, ids[np.minimum(pick, len(ids) - 1)], 0)
             good[m] = has
         good &= s != t
         t, s, wz, dd = t[good], s[good], wz[good], dd[good]
@@ -340,7 +348,13 @@ def c3(n=230924, mean_in_degree=303.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_v
         w = np.where(inh[st], np.float32(-4.0) * w, w).astype(np.float32)
         d = np.maximum(np.round(dd / dt), 1).astype(np.uint16)
         p = _port_of(inh[st], inh[tt])
-        parts.append((s, t, w, d, p))
+        return (s.astype(np.uint32), t.astype(np.uint32), w, d, p)
+
+    todo = [b for b in range(n_blocks) if not (min((b + 1) * BLOCK, n) <= lo or b * BLOCK >= hi)]
+    import concurrent.futures
+    import os
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(16, os.cpu_count() or 1))) as ex:
+        parts = list(ex.map(make_block, todo))
     net.n_virtual = n_virtual
     vr = np.random.default_rng(seed + 2)
     ve = _virtual_edges(vr, n, n_virtual, virt_out_degree, input_weight, max(1, round(1.0 / dt)), lo, hi)

@@ -159,6 +159,12 @@ int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, floa
  * option "profile" is 1), "window". */
 int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out);
 
+/* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
+ * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
+ * and returns the device time between two marks. */
+int bmtk_engine_mark(bmtk_engine* e, int slot);
+int bmtk_engine_elapsed_ms(bmtk_engine* e, int from_slot, int to_slot, double* ms);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

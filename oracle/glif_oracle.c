@@ -428,3 +428,26 @@ int64_t orc_poisson_fill(int64_t n_virtual, const uint32_t* thr, uint64_t seed, 
     }
     return n;
 }
+
+/* CSR by source with a stable counting sort (rows keep edge-list order). Used where the
+ * canonical in-row order does not matter (timed CPU baseline on tens of millions of edges);
+ * the lexsort construction in glif_oracle.py is the one the device CSR is compared with. */
+void orc_csr_by_source(int64_t n_rows, int64_t n_edges, const uint32_t* src, const uint32_t* trg,
+                       const float* weight, const uint16_t* delay, const uint8_t* port, int64_t* rowptr,
+                       int32_t* o_trg, int32_t* o_port, int32_t* o_delay, double* o_weight)
+{
+    for (int64_t r = 0; r <= n_rows; ++r) rowptr[r] = 0;
+    for (int64_t k = 0; k < n_edges; ++k) ++rowptr[src[k] + 1];
+    for (int64_t r = 0; r < n_rows; ++r) rowptr[r + 1] += rowptr[r];
+    int64_t* fill = (int64_t*)malloc(sizeof(int64_t) * (size_t)(n_rows > 0 ? n_rows : 1));
+    if (!fill) return;
+    memcpy(fill, rowptr, sizeof(int64_t) * (size_t)n_rows);
+    for (int64_t k = 0; k < n_edges; ++k) {
+        const int64_t pos = fill[src[k]]++;
+        o_trg[pos] = (int32_t)trg[k];
+        o_port[pos] = port[k];
+        o_delay[pos] = delay[k];
+        o_weight[pos] = (double)weight[k];
+    }
+    free(fill);
+}

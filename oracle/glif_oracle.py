@@ -134,6 +134,8 @@ def lib():
         _lib.orc_poisson_fill.argtypes = [C.c_int64, C.c_void_p, C.c_uint64, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_void_p, C.c_void_p]
         _lib.orc_poisson_fill.restype = C.c_int64
+        _lib.orc_csr_by_source.argtypes = [C.c_int64, C.c_int64] + [C.c_void_p] * 10
+        _lib.orc_csr_by_source.restype = None
     return _lib
 
 
@@ -207,7 +209,7 @@ class OracleSim:
     """
 
     def __init__(self, types, type_index, dt, n_virtual=0, src=None, trg=None, weight=None,
-                 delay_steps=None, port=None, n_threads=1):
+                 delay_steps=None, port=None, n_threads=1, canonical_csr=True):
         self.L = lib()
         self.dt = float(dt)
         self.N = int(len(type_index))
@@ -222,12 +224,25 @@ class OracleSim:
         delay_steps = np.asarray(delay_steps, dtype=np.int64)
         if delay_steps.size and delay_steps.min() < 1:
             raise ValueError('delay below one step')
-        self.rowptr, order = build_csr(n_rows, src, trg, weight, delay_steps, port)
-        self.order = order
-        self.target = np.ascontiguousarray(np.asarray(trg)[order], dtype=np.int32)
-        self.port = np.ascontiguousarray(np.asarray(port)[order], dtype=np.int32)
-        self.delay = np.ascontiguousarray(delay_steps[order], dtype=np.int32)
-        self.weight = np.ascontiguousarray(np.asarray(weight)[order], dtype=np.float64)
+        if canonical_csr:
+            self.rowptr, order = build_csr(n_rows, src, trg, weight, delay_steps, port)
+            self.order = order
+            self.target = np.ascontiguousarray(np.asarray(trg)[order], dtype=np.int32)
+            self.port = np.ascontiguousarray(np.asarray(port)[order], dtype=np.int32)
+            self.delay = np.ascontiguousarray(delay_steps[order], dtype=np.int32)
+            self.weight = np.ascontiguousarray(np.asarray(weight)[order], dtype=np.float64)
+        else:
+            # large networks: stable counting sort by source in C (row order = edge-list order)
+            E = len(src)
+            s32 = np.ascontiguousarray(src, dtype=np.uint32); t32 = np.ascontiguousarray(trg, dtype=np.uint32)
+            w32 = np.ascontiguousarray(weight, dtype=np.float32); d16 = np.ascontiguousarray(delay_steps, dtype=np.uint16)
+            p8 = np.ascontiguousarray(port, dtype=np.uint8)
+            self.rowptr = np.zeros(n_rows + 1, dtype=np.int64)
+            self.target = np.zeros(E, dtype=np.int32); self.port = np.zeros(E, dtype=np.int32)
+            self.delay = np.zeros(E, dtype=np.int32); self.weight = np.zeros(E, dtype=np.float64)
+            self.L.orc_csr_by_source(n_rows, E, _ptr(s32), _ptr(t32), _ptr(w32), _ptr(d16), _ptr(p8), _ptr(self.rowptr),
+                                     _ptr(self.target), _ptr(self.port), _ptr(self.delay), _ptr(self.weight))
+            self.order = None
         self.max_delay = int(self.delay.max()) if self.delay.size else 1
         N, S = self.N, self.max_delay + 1
         self.U = np.zeros(N); self.asc = np.zeros(2 * N)
