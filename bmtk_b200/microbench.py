@@ -6,8 +6,9 @@ and prints achieved GB/s against algorithmic bytes.
 
 `update`    unconnected GLIF-3 neurons (the shape of the current-clamp configuration): only the
             fused state-update kernel does work; 128 B per neuron-step.
-`propagate` an E/I network with fixed in-degree driven hard by Poisson cells, so that every window
-            delivers many synaptic events; 16 B per event.
+`propagate` an E/I network with fixed in-degree whose neurons are all held in tonic firing by a
+            constant current (recurrent weights scaled down so they do not matter), so that every
+            window delivers millions of synaptic events; 16 B per event.
 Times come from CUDA events recorded around every launch (engine option "profile").
 """
 import argparse
@@ -34,6 +35,7 @@ def main():
     ap.add_argument('--steps', type=int, default=64)
     ap.add_argument('--warmup', type=int, default=16)
     ap.add_argument('--input-weight', type=float, default=60.0)
+    ap.add_argument('--drive-pa', type=float, default=600.0, help='propagate: mean tonic current per neuron')
     ap.add_argument('--profile', type=int, default=1, help='0: plain launches only (for ncu captures)')
     a = ap.parse_args()
     if a.kernel == 'update':
@@ -43,8 +45,14 @@ def main():
         net.clamp_delta = net.clamp_delta[:0]
         eng = W.build_engine(net, record_spikes=False, record_vm=False, options=dict(use_graph=0, window=8))
     else:
-        net = W.c2(n=a.neurons, in_degree=a.in_degree, input_weight=a.input_weight, n_virtual=max(64, a.neurons // 25))
-        eng = W.build_engine(net, record_spikes=False, record_vm=False, options=dict(use_graph=0))
+        net = W.c2(n=a.neurons, in_degree=a.in_degree, input_weight=a.input_weight, n_virtual=64, w_scale=0.01)
+        rng = np.random.default_rng(5)
+        ids = np.arange(a.neurons, dtype=np.uint32)
+        net.clamp_step = np.ones(a.neurons, dtype=np.uint64)
+        net.clamp_target = ids
+        net.clamp_delta = rng.uniform(a.drive_pa * 0.6, a.drive_pa * 1.4, size=a.neurons).astype(np.float32)
+        eng = W.build_engine(net, record_spikes=False, record_vm=False,
+                             options=dict(use_graph=0, spike_capacity=a.neurons * 2))
     eng.run(a.warmup)
     eng.set_option('profile', a.profile)
     e0, s0 = eng.counter('events'), eng.counter('spikes')
