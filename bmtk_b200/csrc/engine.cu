@@ -1118,6 +1118,73 @@ int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, floa
     return BMTK_OK;
 }
 
+int bmtk_propagate_spikes(const uint64_t* d_rowptr, const void* d_entries, uint32_t target_bits, uint32_t n_spikes,
+                          const uint32_t* d_spike_src, const uint32_t* d_spike_step, float* d_ring,
+                          uint32_t ring_slots, uint32_t n_pad, int deterministic, void* stream) {
+    if (!d_rowptr || !d_entries || !d_ring) return fail(BMTK_E_INVALID, "propagate_spikes: NULL device pointer");
+    if (n_spikes && (!d_spike_src || !d_spike_step)) return fail(BMTK_E_INVALID, "propagate_spikes: NULL spike list");
+    if (ring_slots < 1 || n_pad < 1 || target_bits < 1 || target_bits > 29)
+        return fail(BMTK_E_INVALID, "propagate_spikes: bad ring geometry");
+    if (n_spikes == 0) return BMTK_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    Ctl* d_ctl = nullptr;
+    uint32_t* d_in_ptr = nullptr;
+    CU(cudaMalloc(&d_ctl, sizeof(Ctl)));
+    if (cudaMalloc(&d_in_ptr, 8) != cudaSuccess) {
+        cudaFree(d_ctl);
+        return fail(BMTK_E_CUDA, "propagate_spikes: cudaMalloc failed");
+    }
+    const uint32_t h_ptr[2] = {0u, n_spikes};
+    int rc = BMTK_OK;
+    DetWorkspace ws{};
+    do {
+        if (cudaMemsetAsync(d_ctl, 0, sizeof(Ctl), st) != cudaSuccess ||
+            cudaMemcpyAsync(d_in_ptr, h_ptr, 8, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            rc = fail(BMTK_E_CUDA, "propagate_spikes: set-up copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        PropArgs a{};
+        a.rowptr = (const unsigned long long*)d_rowptr;
+        a.entries = (const uint2*)d_entries;
+        a.target_bits = target_bits;
+        a.ring = d_ring;
+        a.ring_slots = ring_slots;
+        a.n_pad = n_pad;
+        a.ctl = d_ctl;
+        a.n_seg = 0;
+        a.in_ptr = d_in_ptr;
+        a.in_ptr_base = 0;
+        a.in_ptr_len = 2;
+        a.in_step = d_spike_step;
+        a.in_src = d_spike_src;
+        a.window = 1;
+        if (deterministic) {
+            const uint64_t cells = (uint64_t)ring_slots * kPorts * n_pad;
+            if (cells >= (1ull << 32)) { rc = fail(BMTK_E_UNSUPPORTED, "propagate_spikes: ring too large"); break; }
+            const uint32_t event_cap = 1u << 22;
+            if (det_alloc(ws, event_cap, n_spikes, cells) != cudaSuccess) {
+                rc = fail(BMTK_E_CUDA, "propagate_spikes: workspace allocation failed");
+                break;
+            }
+            uint64_t launches = 0;
+            const int r = propagate_det_window(a, ws, st, &launches);
+            if (r == -2) { rc = fail(BMTK_E_OVERFLOW, "propagate_spikes: more than %u events in one call", event_cap); break; }
+            if (r != 0) { rc = fail(BMTK_E_CUDA, "propagate_spikes: %s", cudaGetErrorString(cudaGetLastError())); break; }
+        } else {
+            if (launch_propagate_atomic(a, st) != cudaSuccess) {
+                rc = fail(BMTK_E_CUDA, "propagate_spikes: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+                break;
+            }
+        }
+        if (cudaStreamSynchronize(st) != cudaSuccess)
+            rc = fail(BMTK_E_CUDA, "propagate_spikes: %s", cudaGetErrorString(cudaGetLastError()));
+    } while (0);
+    det_free(ws);
+    cudaFree(d_ctl);
+    cudaFree(d_in_ptr);
+    return rc;
+}
+
 int bmtk_engine_mark(bmtk_engine* e, int slot) {
     if (!e || slot < 0 || slot >= 8) return fail(BMTK_E_INVALID, "mark: slot must be 0..7");
     int rc = set_device(e);

@@ -159,6 +159,19 @@ int bmtk_engine_get_csr(bmtk_engine* e, uint64_t* rowptr, uint32_t* packed, floa
  * option "profile" is 1), "window". */
 int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out);
 
+/* The delivery step of nest.Simulate on its own (event delivery into the targets' ring buffers,
+ * bmtk/simulator/pointnet/pointsimulator.py:166), for callers that keep the CSR and the ring
+ * buffer in their own device memory. All d_* are DEVICE pointers: d_rowptr[n_rows+1],
+ * d_entries[E] as {uint32 packed, float weight} pairs in the layout of bmtk_engine_get_csr,
+ * the spikes as (source row, emitting step) pairs, d_ring[ring_slots][4][n_pad]. Every listed
+ * spike adds its row's weights to ring[(step + delay) mod ring_slots][port][target].
+ * deterministic = 1 sums in a fixed order (sorted segmented reduction), 0 uses atomics.
+ * Allocates and frees its workspace with cudaMalloc on every call; returns after the stream
+ * has finished. `stream` is a cudaStream_t (NULL = default stream). */
+int bmtk_propagate_spikes(const uint64_t* d_rowptr, const void* d_entries, uint32_t target_bits,
+                          uint32_t n_spikes, const uint32_t* d_spike_src, const uint32_t* d_spike_step,
+                          float* d_ring, uint32_t ring_slots, uint32_t n_pad, int deterministic, void* stream);
+
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
  * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
  * and returns the device time between two marks. */
