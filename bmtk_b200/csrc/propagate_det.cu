@@ -11,6 +11,9 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
+#include <cstdio>
+#include <string>
+
 #include "propagate_det.cuh"
 
 namespace bmtk {
@@ -203,3 +206,174 @@ int propagate_det_window(const PropArgs& a, DetWorkspace& w, cudaStream_t s, uin
 }
 
 }  // namespace bmtk
+
+// =============================================================================================
+// Allocation-free variant of the deterministic delivery.
+//
+// Some hosts of this library may not allocate device memory at the moment they need a delivery:
+// a simulator plugin that runs inside someone else's memory pool (its budget was fixed when the
+// pool was carved up), a real-time control loop that must not enter the allocator's locks, or a
+// process whose GPU is already filled to the last byte by the network itself. For them the
+// scratch of the sorted segmented reduction lives in a fixed array inside the library image.
+// Cost: every GPU that loads the library carries the array (about 8.3 MB) until the process exits,
+// and one call handles at most kNoAllocMaxSpikes spike rows and kNoAllocMaxEvents synaptic events.
+namespace bmtk {
+
+constexpr uint32_t kNoAllocMaxSpikes = 4096;
+constexpr uint32_t kNoAllocMaxEvents = 1u << 18;
+constexpr size_t kNoAllocCubBytes = 4u << 20;
+
+constexpr size_t na_align(size_t x) { return (x + 255) / 256 * 256; }
+constexpr size_t kNaCtl = 0;
+constexpr size_t kNaInPtr = kNaCtl + na_align(sizeof(Ctl));
+constexpr size_t kNaItemKeys = kNaInPtr + na_align(2 * sizeof(uint32_t));
+constexpr size_t kNaItemKeys2 = kNaItemKeys + na_align(8ull * kNoAllocMaxSpikes);
+constexpr size_t kNaRowLen = kNaItemKeys2 + na_align(8ull * kNoAllocMaxSpikes);
+constexpr size_t kNaRowOff = kNaRowLen + na_align(4ull * kNoAllocMaxSpikes);
+constexpr size_t kNaEvKey = kNaRowOff + na_align(4ull * kNoAllocMaxSpikes);
+constexpr size_t kNaEvKey2 = kNaEvKey + na_align(4ull * kNoAllocMaxEvents);
+constexpr size_t kNaEvVal = kNaEvKey2 + na_align(4ull * kNoAllocMaxEvents);
+constexpr size_t kNaEvVal2 = kNaEvVal + na_align(4ull * kNoAllocMaxEvents);
+constexpr size_t kNaCub = kNaEvVal2 + na_align(4ull * kNoAllocMaxEvents);
+constexpr size_t kNoAllocBytes = kNaCub + kNoAllocCubBytes;
+
+// The scratch itself. In host code this name is only a handle for cudaGetSymbolAddress: it is not
+// a device address and must never be handed to a kernel as a pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNaMaxDevices = 64;
+static unsigned char* g_noalloc_addr[kNaMaxDevices] = {};  // device address of the array, per device
+
+extern thread_local std::string g_last_error;
+
+static int na_fail(int code, const char* msg, cudaError_t ce = cudaSuccess) {
+    char buf[512];
+    if (ce != cudaSuccess) snprintf(buf, sizeof(buf), "propagate_spikes_noalloc: %s: %s", msg, cudaGetErrorString(ce));
+    else snprintf(buf, sizeof(buf), "propagate_spikes_noalloc: %s", msg);
+    g_last_error = buf;
+    return code;
+}
+
+// Zeroes the control block (it keeps the previous call's counters) and writes the [0, n) slice
+// table through which the collect kernel finds the caller's spike list.
+__global__ void noalloc_setup_kernel(Ctl* ctl, uint32_t* in_ptr, uint32_t n_spikes) {
+    Ctl z{};
+    *ctl = z;
+    in_ptr[0] = 0u;
+    in_ptr[1] = n_spikes;
+}
+
+}  // namespace bmtk
+
+extern "C" __attribute__((visibility("default")))
+int bmtk_propagate_spikes_noalloc(const uint64_t* d_rowptr, const void* d_entries, uint32_t target_bits,
+                                  uint32_t n_spikes, const uint32_t* d_spike_src, const uint32_t* d_spike_step,
+                                  float* d_ring, uint32_t ring_slots, uint32_t n_pad, void* stream) {
+    using namespace bmtk;
+    if (!d_rowptr || !d_entries || !d_ring) return na_fail(BMTK_E_INVALID, "NULL device pointer");
+    if (n_spikes && (!d_spike_src || !d_spike_step)) return na_fail(BMTK_E_INVALID, "NULL spike list");
+    if (ring_slots < 1 || n_pad < 1 || target_bits < 1 || target_bits > 29)
+        return na_fail(BMTK_E_INVALID, "bad ring geometry");
+    if (n_spikes > kNoAllocMaxSpikes) {
+        char m[160];
+        snprintf(m, sizeof(m), "%u spikes in one call, the built-in scratch holds at most %u "
+                 "(split the list or use bmtk_propagate_spikes)", n_spikes, kNoAllocMaxSpikes);
+        return na_fail(BMTK_E_INVALID, m);
+    }
+    const uint64_t cells = (uint64_t)ring_slots * kPorts * n_pad;
+    if (cells >= (1ull << 32)) return na_fail(BMTK_E_UNSUPPORTED, "ring has 2^32 cells or more");
+    if (n_spikes == 0) return BMTK_OK;
+
+    // Once per device, with that device current: ask the runtime where the array lives there.
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return na_fail(BMTK_E_CUDA, "cudaGetDevice", ce);
+    if (dev < 0 || dev >= kNaMaxDevices) return na_fail(BMTK_E_UNSUPPORTED, "device ordinal beyond 63");
+    if (!g_noalloc_addr[dev]) {
+        unsigned char* p = nullptr;
+        ce = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (ce != cudaSuccess || !p) return na_fail(BMTK_E_CUDA, "cudaGetSymbolAddress(scratch)", ce);
+        g_noalloc_addr[dev] = p;
+    }
+    unsigned char* base = g_noalloc_addr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+
+    Ctl* ctl = reinterpret_cast<Ctl*>(base + kNaCtl);
+    uint32_t* in_ptr = reinterpret_cast<uint32_t*>(base + kNaInPtr);
+    unsigned long long* item_keys = reinterpret_cast<unsigned long long*>(base + kNaItemKeys);
+    unsigned long long* item_keys2 = reinterpret_cast<unsigned long long*>(base + kNaItemKeys2);
+    uint32_t* row_len = reinterpret_cast<uint32_t*>(base + kNaRowLen);
+    uint32_t* row_off = reinterpret_cast<uint32_t*>(base + kNaRowOff);
+    uint32_t* ev_key = reinterpret_cast<uint32_t*>(base + kNaEvKey);
+    uint32_t* ev_key2 = reinterpret_cast<uint32_t*>(base + kNaEvKey2);
+    float* ev_val = reinterpret_cast<float*>(base + kNaEvVal);
+    float* ev_val2 = reinterpret_cast<float*>(base + kNaEvVal2);
+    void* cub_tmp = base + kNaCub;
+
+    int cell_bits = 1;
+    while (cell_bits < 32 && (cells >> cell_bits) != 0) ++cell_bits;
+
+    // CUB is handed its temporary storage; ask how much each call wants and refuse if the
+    // reserved region were too small (sizes are fixed by the maxima above, so this never trips).
+    size_t t1 = 0, t2 = 0, t3 = 0;
+    cub::DeviceRadixSort::SortKeys(nullptr, t1, item_keys, item_keys2, (int)kNoAllocMaxSpikes, 0, 64, st);
+    cub::DeviceScan::ExclusiveSum(nullptr, t2, row_len, row_off, (int)kNoAllocMaxSpikes, st);
+    cub::DeviceRadixSort::SortPairs(nullptr, t3, ev_key, ev_key2, ev_val, ev_val2, (int)kNoAllocMaxEvents, 0, cell_bits, st);
+    if (t1 > kNoAllocCubBytes || t2 > kNoAllocCubBytes || t3 > kNoAllocCubBytes)
+        return na_fail(BMTK_E_UNSUPPORTED, "sort workspace exceeds the built-in scratch");
+
+    noalloc_setup_kernel<<<1, 1, 0, st>>>(ctl, in_ptr, n_spikes);
+    if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "set-up launch", ce);
+
+    PropArgs a{};
+    a.rowptr = (const unsigned long long*)d_rowptr;
+    a.entries = (const uint2*)d_entries;
+    a.target_bits = target_bits;
+    a.ring = d_ring;
+    a.ring_slots = ring_slots;
+    a.n_pad = n_pad;
+    a.ctl = ctl;
+    a.n_seg = 0;
+    a.in_ptr = in_ptr;
+    a.in_ptr_base = 0;
+    a.in_ptr_len = 2;
+    a.in_step = d_spike_step;
+    a.in_src = d_spike_src;
+    a.window = 1;
+
+    det_collect_kernel<<<1, 256, 0, st>>>(a, item_keys, kNoAllocMaxSpikes);
+    if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "collect launch", ce);
+    size_t tmp = kNoAllocCubBytes;
+    if ((ce = cub::DeviceRadixSort::SortKeys(cub_tmp, tmp, item_keys, item_keys2, (int)n_spikes, 0, 64, st)) != cudaSuccess)
+        return na_fail(BMTK_E_CUDA, "spike sort", ce);
+    det_rowlen_kernel<<<(n_spikes + 255) / 256, 256, 0, st>>>(n_spikes, item_keys2, a.rowptr, row_len);
+    if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "row-length launch", ce);
+    tmp = kNoAllocCubBytes;
+    if ((ce = cub::DeviceScan::ExclusiveSum(cub_tmp, tmp, row_len, row_off, (int)n_spikes, st)) != cudaSuccess)
+        return na_fail(BMTK_E_CUDA, "offset scan", ce);
+    det_total_kernel<<<1, 1, 0, st>>>(n_spikes, row_off, row_len, ctl);
+    if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "total launch", ce);
+    uint32_t n_events = 0;
+    if ((ce = cudaMemcpyAsync(&n_events, &ctl->det_events, 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        return na_fail(BMTK_E_CUDA, "event count read-back", ce);
+    if ((ce = cudaStreamSynchronize(st)) != cudaSuccess) return na_fail(BMTK_E_CUDA, "synchronize", ce);
+    if (n_events > kNoAllocMaxEvents) {
+        char m[200];
+        snprintf(m, sizeof(m), "%u synaptic events in one call, the built-in scratch holds at most %u; "
+                 "nothing was delivered (split the spike list or use bmtk_propagate_spikes)", n_events, kNoAllocMaxEvents);
+        return na_fail(BMTK_E_OVERFLOW, m);
+    }
+    if (n_events) {
+        const uint32_t blocks = n_spikes < 148u * 8u ? n_spikes : 148u * 8u;
+        det_expand_kernel<<<blocks, kDetThreads, 0, st>>>(n_spikes, item_keys2, row_off, a, ev_key, ev_val);
+        if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "expand launch", ce);
+        tmp = kNoAllocCubBytes;
+        if ((ce = cub::DeviceRadixSort::SortPairs(cub_tmp, tmp, ev_key, ev_key2, ev_val, ev_val2, (int)n_events, 0,
+                                                  cell_bits, st)) != cudaSuccess)
+            return na_fail(BMTK_E_CUDA, "event sort", ce);
+        det_reduce_kernel<<<(n_events + 255) / 256, 256, 0, st>>>(n_events, ev_key2, ev_val2, d_ring);
+        if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "reduce launch", ce);
+    }
+    if ((ce = cudaStreamSynchronize(st)) != cudaSuccess) return na_fail(BMTK_E_CUDA, "synchronize", ce);
+    return BMTK_OK;
+}

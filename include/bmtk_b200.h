@@ -172,6 +172,26 @@ int bmtk_propagate_spikes(const uint64_t* d_rowptr, const void* d_entries, uint3
                           uint32_t n_spikes, const uint32_t* d_spike_src, const uint32_t* d_spike_step,
                           float* d_ring, uint32_t ring_slots, uint32_t n_pad, int deterministic, void* stream);
 
+/* The same deterministic delivery as bmtk_propagate_spikes(..., deterministic = 1, ...), for
+ * callers that must not allocate device memory when they call it. (No counterpart in the
+ * reference, which leaves all memory management to NEST.) Such callers exist: a plugin living
+ * inside a host application's fixed memory pool, a latency-bound loop that may not take the
+ * allocator's locks, a process whose network already fills the GPU. This entry point calls no
+ * cudaMalloc/cudaFree and no allocating library routine; its scratch is a fixed array of about
+ * 8.3 MB built into the library, which every GPU that loads the library holds until exit.
+ * Limits per call: at most 4096 spikes and 262 144 synaptic events (sum of the listed rows'
+ * lengths); a longer spike list is refused with BMTK_E_INVALID, more events with
+ * BMTK_E_OVERFLOW, in both cases before the ring is touched.
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call before starting any stream capture. All calls share the one array and it
+ * keeps the previous call's contents (the entry point re-initialises what it needs), so two calls
+ * whose GPU work could overlap - different streams, different host threads - race; serialise them.
+ * Inputs and outputs are the caller's device memory exactly as for bmtk_propagate_spikes; the
+ * call returns after the stream has finished. */
+int bmtk_propagate_spikes_noalloc(const uint64_t* d_rowptr, const void* d_entries, uint32_t target_bits,
+                                  uint32_t n_spikes, const uint32_t* d_spike_src, const uint32_t* d_spike_step,
+                                  float* d_ring, uint32_t ring_slots, uint32_t n_pad, void* stream);
+
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
  * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
  * and returns the device time between two marks. */
