@@ -199,18 +199,23 @@ def main():
         raise SystemExit('bench.py needs a CUDA device: bmtk_b200 has no CPU path')
     torch.cuda.set_device(local_rank)
     dev = torch.device('cuda', local_rank)
-    uid, libnccl = None, None
+    libnccl = None
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=dev)
         libnccl = os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), 'nvidia', 'nccl', 'lib', 'libnccl.so.2')
         if not os.path.exists(libnccl):
             libnccl = None
+
+    def fresh_uid():
+        """A new ncclUniqueId for every engine (an id serves one communicator), made on rank 0."""
+        if world == 1:
+            return None
         buf = torch.zeros(128, dtype=torch.uint8, device=dev)
         if rank == 0:
             buf.copy_(torch.frombuffer(bytearray(nccl_unique_id(libnccl)), dtype=torch.uint8))
         dist.broadcast(buf, 0)
-        uid = bytes(buf.cpu().numpy().tobytes())
+        return bytes(buf.cpu().numpy().tobytes())
 
     def barrier():
         if world > 1:
@@ -234,7 +239,7 @@ def main():
     # ---------------- device-resident run
     t0 = time.time()
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                         options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=uid,
+                         options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
                          libnccl=libnccl)
     t_build = time.time() - t0
     for _ in range(args.warmup):
@@ -294,7 +299,7 @@ def main():
     if not args.no_e2e:
         net.poisson_rate_hz, rates = None, net.poisson_rate_hz.astype(np.float64)
         eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                             options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=uid,
+                             options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
                              libnccl=libnccl)
         rng = np.random.default_rng(99)   # same seed on every rank: virtual cells are replicated
         n_chunks = 1 + args.steps
