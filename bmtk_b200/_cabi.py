@@ -10,6 +10,7 @@ import ctypes as C
 import os
 
 MAX_PORTS = 4
+MODEL_GLIF_PSC, MODEL_IAF_PSC_ALPHA = 0, 1
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'lib', 'libbmtk_b200.so')
 
 OK, E_INVALID, E_CUDA, E_OVERFLOW, E_UNSUPPORTED, E_COMM, E_DELAY = 0, -1, -2, -3, -4, -5, -6
@@ -27,6 +28,7 @@ class GlifParams(C.Structure):
         ('th_voltage_index', C.c_double), ('th_voltage_decay', C.c_double),
         ('n_ports', C.c_int32), ('spike_dependent_threshold', C.c_int32),
         ('after_spike_currents', C.c_int32), ('adapting_threshold', C.c_int32),
+        ('I_e', C.c_double), ('model', C.c_int32), ('reserved', C.c_int32),
     ]
 
 

@@ -33,8 +33,11 @@ struct TypeConsts {
     float th_inf, v_reset, E_L;
     float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction, reset_add;
     float phi, abpara, theta_voltage_decay, inv_G;
+    float i_e, pad_f;
     int32_t n_ref;
-    int32_t flags;  // bit0 spike-dependent threshold, bit1 adapting threshold
+    // bit0 spike-dependent threshold, bit1 adapting threshold, bit2 reset in the spike step
+    // (iaf_psc_alpha), bit3 threshold test is >= (iaf_psc_alpha)
+    int32_t flags;
 };
 static_assert(sizeof(TypeConsts) % 4 == 0, "TypeConsts is copied word-wise");
 
@@ -51,6 +54,8 @@ struct Ctl {
     uint32_t det_items;             // deterministic path: spike rows collected this window
     uint32_t det_events;            // deterministic path: events expanded this window
     uint32_t pad0, pad1;
+    // persistent kernel, option "profile": device-timer totals of the two phases of every window
+    unsigned long long t_update_ns, t_prop_ns, n_windows;
 };
 
 // Neuron state, structure of arrays; every array has n_pad entries (multiple of 4, 16-byte aligned).

@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "csr_build.cuh"
+#include "persistent.cuh"
 #include "propagate_det.cuh"
 
 namespace bmtk {
@@ -49,7 +50,7 @@ static double cross_term(double x) {
 
 static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& c) {
     if (!(p.C_m > 0) || !(p.g > 0)) return fail(BMTK_E_INVALID, "C_m and g must be positive");
-    if (!(p.t_ref > 0)) return fail(BMTK_E_INVALID, "t_ref must be positive");
+    if (!(p.t_ref > 0) && p.model == BMTK_MODEL_GLIF_PSC) return fail(BMTK_E_INVALID, "t_ref must be positive");
     if (p.n_ports < 1 || p.n_ports > kPorts) return fail(BMTK_E_INVALID, "n_ports must be 1..%d", kPorts);
     std::memset(&c, 0, sizeof(c));
     const double tau = p.C_m / p.g;
@@ -98,6 +99,16 @@ static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& 
     } while (r > 0.0 && n < (1 << 30));
     c.n_ref = n;
     c.flags = (p.spike_dependent_threshold ? 1 : 0) | (p.adapting_threshold ? 2 : 0);
+    c.i_e = (float)p.I_e;
+    if (p.model == BMTK_MODEL_IAF_PSC_ALPHA) {
+        if (p.spike_dependent_threshold || p.adapting_threshold || p.after_spike_currents)
+            return fail(BMTK_E_INVALID, "iaf_psc_alpha has no threshold dynamics or after-spike currents");
+        c.flags |= 4 | 8;
+        c.n_ref = (int)std::llround(p.t_ref / h);
+        if (c.n_ref < 1) c.n_ref = 1;  // a spike always costs the step it happens in
+    } else if (p.model != BMTK_MODEL_GLIF_PSC) {
+        return fail(BMTK_E_INVALID, "unknown model %d", p.model);
+    }
     c.theta_spike_decay = (float)std::exp(-p.th_spike_decay * h);
     c.theta_spike_refr = (float)std::exp(-p.th_spike_decay * p.t_ref);
     c.th_spike_add = (float)p.th_spike_add;
@@ -282,6 +293,19 @@ struct bmtk_engine {
     std::vector<std::pair<int, int>> ev_update, ev_prop;  // indices into ev_pool
     double update_ns = 0, prop_ns = 0;
     uint64_t update_launches = 0, prop_launches = 0;
+
+    // persistent stepping (single rank, atomic delivery)
+    bool persistent = true, phase_timers = false;
+    int persist_blocks = 0;
+    bool persist_resident = false;
+    uint32_t *d_send2 = nullptr, *d_virt2 = nullptr;
+    int32_t* d_probe_slot = nullptr;
+    unsigned long long* d_ce_group_step = nullptr;
+    uint32_t* d_ce_group_ptr = nullptr;
+    std::vector<uint64_t> ce_group_step;
+    size_t ce_group_next = 0;
+    double phase_update_ns = 0, phase_prop_ns = 0;
+    uint64_t phase_windows = 0;
 
     DetWorkspace det{};
     cudaEvent_t marks[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -510,6 +534,12 @@ static int drain(bmtk_engine* e) {
     e->events_total = h.n_events;
     e->spikes_total = h.n_spikes;
     e->input_spikes_total = h.n_input_spikes;
+    if (h.n_windows) {
+        e->phase_update_ns += (double)h.t_update_ns;
+        e->phase_prop_ns += (double)h.t_prop_ns;
+        e->phase_windows += h.n_windows;
+        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 24, e->stream));
+    }
     if (h.step_base != e->step)
         return fail(BMTK_E_INVALID, "device clock %llu differs from host clock %llu", (unsigned long long)h.step_base,
                     (unsigned long long)e->step);
@@ -569,6 +599,66 @@ static int drain(bmtk_engine* e) {
     return BMTK_OK;
 }
 
+// One cooperative launch that executes `n` steps (update + delivery of every window inside it).
+static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
+    PersistArgs a{};
+    a.st = e->st;
+    a.types = e->d_types;
+    a.n_types = (int32_t)e->types.size();
+    a.n_local = (uint32_t)e->n_local;
+    a.n_pad = e->n_pad;
+    a.lo = (uint32_t)e->lo;
+    a.n_global = (uint32_t)e->n_global;
+    a.ring = e->ring;
+    a.ring_slots = e->ring_slots;
+    a.ctl = e->d_ctl;
+    a.lists[0] = e->d_send;
+    a.lists[1] = e->d_send2;
+    a.send_cap = e->send_cap;
+    a.log_stamp = e->record_spikes ? e->d_log_stamp : nullptr;
+    a.log_id = e->d_log_id;
+    a.log_cap = (uint32_t)e->log_cap;
+    a.poisson_thr = e->has_poisson ? e->d_poisson_thr : nullptr;
+    a.n_virtual = (uint32_t)e->n_virtual;
+    a.seed = e->seed;
+    a.virts[0] = e->d_virt;
+    a.virts[1] = e->d_virt2;
+    a.virt_cap = e->virt_cap;
+    a.rowptr = e->d_rowptr;
+    a.entries = e->d_entries;
+    a.target_bits = e->target_bits;
+    a.in_ptr = e->d_in_ptr;
+    a.in_ptr_base = e->in_ptr_base;
+    a.in_ptr_len = e->in_ptr_len;
+    a.in_step = e->d_in_step;
+    a.in_src = e->d_in_src;
+    a.n_steps = n;
+    a.window = e->window;
+    a.ce_group_step = e->d_ce_group_step;
+    a.ce_group_ptr = e->d_ce_group_ptr;
+    a.ce_group_begin = (uint32_t)e->ce_group_next;
+    a.ce_group_end = (uint32_t)e->ce_group_step.size();
+    a.ce_target = e->d_ce_target;
+    a.ce_delta = e->d_ce_delta;
+    a.probe_slot = e->probe_ids.empty() ? nullptr : e->d_probe_slot;
+    a.n_probe = (uint32_t)e->probe_ids.size();
+    a.probe_interval = e->probe_interval;
+    a.trace = e->d_trace;
+    a.trace_cap = e->trace_cap;
+    a.profile = e->phase_timers ? 1u : 0u;
+    CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
+    ++e->launches;
+    e->step += n;
+    // lists are empty at rest, whichever path runs next
+    CU(cudaMemsetAsync(e->d_send, 0, 4, e->stream));
+    CU(cudaMemsetAsync(e->d_send2, 0, 4, e->stream));
+    if (e->d_virt) CU(cudaMemsetAsync(e->d_virt, 0, 4, e->stream));
+    if (e->d_virt2) CU(cudaMemsetAsync(e->d_virt2, 0, 4, e->stream));
+    while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step) ++e->ce_group_next;
+    while (e->ce_next < e->ce_step.size() && e->ce_step[e->ce_next] < e->step) ++e->ce_next;
+    return BMTK_OK;
+}
+
 static int run_steps(bmtk_engine* e, uint64_t n_steps) {
     int rc = upload_inputs(e);
     if (rc) return rc;
@@ -581,6 +671,13 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
             chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(room - e->probe_interval + 1, 1));
         }
         uint64_t done = 0;
+        const bool use_persistent = e->persistent && e->n_ranks == 1 && !e->deterministic && !e->profile &&
+                                    e->persist_blocks > 0;
+        if (use_persistent) {
+            rc = run_persistent_chunk(e, (uint32_t)chunk);
+            if (rc) return rc;
+            done = chunk;
+        }
         while (done < chunk) {
             const uint32_t w = (uint32_t)std::min<uint64_t>(e->window, chunk - done);
             bool clamp_in_window = false;
@@ -600,6 +697,8 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
             }
             e->step += w;
             done += w;
+            while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step)
+                ++e->ce_group_next;
         }
         left -= chunk;
         rc = drain(e);
@@ -656,6 +755,8 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_log_stamp); cudaFree(e->d_log_id); cudaFree(e->d_poisson_thr);
     cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
     cudaFree(e->d_ce_target); cudaFree(e->d_ce_delta); cudaFree(e->d_probe_ids); cudaFree(e->d_trace);
+    cudaFree(e->d_send2); cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step);
+    cudaFree(e->d_ce_group_ptr);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return BMTK_OK;
@@ -783,6 +884,8 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     const std::string k(key);
     if (k == "profile") { e->profile = value != 0; return BMTK_OK; }
     if (k == "use_graph") { e->use_graph = value != 0; return BMTK_OK; }
+    if (k == "persistent") { e->persistent = value != 0; return BMTK_OK; }
+    if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "chunk_steps") {
         if (value < 1) return fail(BMTK_E_INVALID, "chunk_steps must be positive");
         e->chunk_steps = (uint64_t)value;
@@ -994,6 +1097,44 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         CU(cudaMalloc(&e->d_probe_ids, 4 * n_ids));
         CU(cudaMemcpy(e->d_probe_ids, e->probe_ids.data(), 4 * n_ids, cudaMemcpyHostToDevice));
         CU(cudaMalloc(&e->d_trace, 4 * n_ids * cap_s));
+    }
+    // persistent stepping: second spike lists, clamp groups, probe map, grid size
+    if (e->n_ranks == 1) {
+        CU(cudaMalloc(&e->d_send2, 4 * seg));
+        CU(cudaMemset(e->d_send2, 0, 4 * seg));
+        if (e->has_poisson) {
+            CU(cudaMalloc(&e->d_virt2, 4 * ((size_t)e->virt_cap + 4)));
+            CU(cudaMemset(e->d_virt2, 0, 4 * ((size_t)e->virt_cap + 4)));
+        }
+        if (e->has_iext) {
+            std::vector<unsigned long long> gs;
+            std::vector<uint32_t> gp;
+            for (size_t i = 0; i < e->ce_step.size(); ++i) {
+                if (i == 0 || e->ce_step[i] != e->ce_step[i - 1]) {
+                    gs.push_back(e->ce_step[i]);
+                    gp.push_back((uint32_t)i);
+                }
+            }
+            gp.push_back((uint32_t)e->ce_step.size());
+            e->ce_group_step.assign(gs.begin(), gs.end());
+            CU(cudaMalloc(&e->d_ce_group_step, 8 * std::max<size_t>(gs.size(), 1)));
+            CU(cudaMalloc(&e->d_ce_group_ptr, 4 * gp.size()));
+            if (!gs.empty()) CU(cudaMemcpy(e->d_ce_group_step, gs.data(), 8 * gs.size(), cudaMemcpyHostToDevice));
+            CU(cudaMemcpy(e->d_ce_group_ptr, gp.data(), 4 * gp.size(), cudaMemcpyHostToDevice));
+        }
+        if (!e->probe_ids.empty()) {
+            std::vector<int32_t> slot(np, -1);
+            for (size_t q = 0; q < e->probe_ids.size(); ++q) slot[e->probe_ids[q]] = (int32_t)q;
+            CU(cudaMalloc(&e->d_probe_slot, 4 * np));
+            CU(cudaMemcpy(e->d_probe_slot, slot.data(), 4 * np, cudaMemcpyHostToDevice));
+        }
+        const size_t smem = persistent_smem((int)nt);
+        const int blocks = persistent_max_blocks(e->device, e->has_theta, e->has_iext, true, smem);
+        e->persist_blocks = blocks;
+        e->persist_resident = blocks > 0 && (uint64_t)(e->n_pad / 4) <= (uint64_t)blocks * persistent_threads_per_block();
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
+        if (!coop) e->persist_blocks = 0;
     }
     if (e->deterministic) {
         cudaError_t ce = det_alloc(e->det, (uint32_t)e->event_cap,
@@ -1221,6 +1362,11 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "update_launches") *out = e->update_launches;
     else if (k == "propagate_launches") *out = e->prop_launches;
     else if (k == "spike_capacity") *out = e->send_cap;
+    else if (k == "phase_update_ns") *out = (uint64_t)e->phase_update_ns;
+    else if (k == "phase_propagate_ns") *out = (uint64_t)e->phase_prop_ns;
+    else if (k == "phase_windows") *out = e->phase_windows;
+    else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
+    else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else return fail(BMTK_E_INVALID, "unknown counter '%s'", name);
     return BMTK_OK;

@@ -1,0 +1,176 @@
+// Register-resident state of four consecutive neurons and one update step on it.
+// Shared by the per-step kernel (state loaded and stored every step) and the persistent kernel
+// (state kept in registers across steps).
+#pragma once
+#include "common.cuh"
+
+namespace bmtk {
+
+constexpr int kNeuronsPerThread = 4;
+
+struct F4 {
+    float v[4];
+};
+__device__ __forceinline__ F4 ld4(const float* p) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    return F4{{t.x, t.y, t.z, t.w}};
+}
+__device__ __forceinline__ void st4(float* p, const F4& a) {
+    *reinterpret_cast<float4*>(p) = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+}
+
+template <bool THETA, bool IEXT>
+struct Neuron4 {
+    F4 U, a0, a1, y1[kPorts], y2[kPorts], ths, thv, iex;
+    int rf[4];
+    uint16_t ty[4];
+
+    __device__ __forceinline__ void load(const StateSoA& st, uint32_t np, uint32_t i0) {
+        U = ld4(st.U + i0);
+        a0 = ld4(st.asc0 + i0);
+        a1 = ld4(st.asc1 + i0);
+#pragma unroll
+        for (int p = 0; p < kPorts; ++p) {
+            y1[p] = ld4(st.y1 + (size_t)p * np + i0);
+            y2[p] = ld4(st.y2 + (size_t)p * np + i0);
+        }
+        const int4 r = *reinterpret_cast<const int4*>(st.refr + i0);
+        rf[0] = r.x; rf[1] = r.y; rf[2] = r.z; rf[3] = r.w;
+        const ushort4 t = *reinterpret_cast<const ushort4*>(st.type + i0);
+        ty[0] = t.x; ty[1] = t.y; ty[2] = t.z; ty[3] = t.w;
+        ths = thv = iex = F4{{0.f, 0.f, 0.f, 0.f}};
+        if (THETA) {
+            ths = ld4(st.th_spike + i0);
+            thv = ld4(st.th_voltage + i0);
+        }
+        if (IEXT) iex = ld4(st.i_ext + i0);
+    }
+
+    __device__ __forceinline__ void store(const StateSoA& st, uint32_t np, uint32_t i0) const {
+        st4(st.U + i0, U);
+        st4(st.asc0 + i0, a0);
+        st4(st.asc1 + i0, a1);
+#pragma unroll
+        for (int p = 0; p < kPorts; ++p) {
+            st4(st.y1 + (size_t)p * np + i0, y1[p]);
+            st4(st.y2 + (size_t)p * np + i0, y2[p]);
+        }
+        *reinterpret_cast<int4*>(st.refr + i0) = make_int4(rf[0], rf[1], rf[2], rf[3]);
+        if (THETA) {
+            st4(st.th_spike + i0, ths);
+            st4(st.th_voltage + i0, thv);
+        }
+    }
+
+    // One step for the four neurons with ring input in[port]. Returns the spike mask (bit j).
+    __device__ __forceinline__ uint32_t step(const TypeConsts* types, const F4 (&in)[kPorts]) {
+        uint32_t mask = 0;
+#pragma unroll
+        for (int j = 0; j < kNeuronsPerThread; ++j) {
+            const TypeConsts& c = types[ty[j]];
+            float u = U.v[j];
+            if (rf[j] > 0) {
+                // refractory: V is held; glif_psc resets on the step the countdown ends
+                if (--rf[j] == 0) {
+                    a0.v[j] = c.asc_amps[0] + a0.v[j] * c.asc_refr[0];
+                    a1.v[j] = c.asc_amps[1] + a1.v[j] * c.asc_refr[1];
+                    if (THETA && (c.flags & 1)) {
+                        u = c.reset_fraction * u + c.reset_add;
+                        ths.v[j] = ths.v[j] * c.theta_spike_refr + c.th_spike_add;
+                    } else {
+                        u = c.v_reset;
+                    }
+                }
+            } else {
+                const float asc_sum = c.asc_coeff[0] * a0.v[j] + c.asc_coeff[1] * a1.v[j];
+                a0.v[j] *= c.asc_decay[0];
+                a1.v[j] *= c.asc_decay[1];
+                if (THETA && (c.flags & 1)) ths.v[j] *= c.theta_spike_decay;
+                const float v_old = u;
+                const float drive = iex.v[j] + c.i_e + asc_sum;
+                u = v_old * c.P33 + drive * c.P30;
+#pragma unroll
+                for (int p = 0; p < kPorts; ++p) u += c.P31[p] * y1[p].v[j] + c.P32[p] * y2[p].v[j];
+                float th = c.th_inf;
+                if (THETA) {
+                    if (c.flags & 2) {
+                        const float beta = drive * c.inv_G;
+                        const float d = c.phi * (v_old - beta);
+                        thv.v[j] = d * c.P33 + c.theta_voltage_decay * (thv.v[j] - d - c.abpara * beta) +
+                                   c.abpara * beta;
+                    }
+                    th += ths.v[j] + thv.v[j];
+                }
+                const bool fire = (c.flags & 8) ? (u >= th) : (u > th);
+                if (fire) {
+                    rf[j] = c.n_ref;
+                    mask |= 1u << j;
+                    if (c.flags & 4) u = c.v_reset;  // iaf_psc_alpha: reset in the spike step
+                }
+            }
+            U.v[j] = u;
+#pragma unroll
+            for (int p = 0; p < kPorts; ++p) {
+                const float y1o = y1[p].v[j];
+                y2[p].v[j] = c.P21[p] * y1o + c.P11[p] * y2[p].v[j];
+                y1[p].v[j] = c.P11[p] * y1o + c.psc_init[p] * in[p].v[j];
+            }
+        }
+        return mask;
+    }
+};
+
+// Reserves `n` consecutive positions for this thread behind a shared counter with one atomic per
+// warp (inclusive warp scan, lane 31 adds the warp total). Returns the thread's first position;
+// *total receives the warp total on every lane. All 32 lanes must call it.
+__device__ __forceinline__ uint32_t warp_reserve(uint32_t* counter, int n, uint32_t* total) {
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    int incl = n;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(full, incl, d);
+        if (lane >= d) incl += t;
+    }
+    uint32_t base = 0;
+    if (lane == 31) base = atomicAdd(counter, (uint32_t)incl);
+    base = __shfl_sync(full, base, 31);
+    *total = (uint32_t)__shfl_sync(full, incl, 31);
+    return base + (uint32_t)(incl - n);
+}
+
+// Appends the fired neurons of this thread (mask over i0..i0+3) to the window spike list and, when
+// recording, to the spike log. Must be called by all lanes of a warp when any lane has a spike.
+__device__ __forceinline__ void emit_spikes(uint32_t spk_mask, uint32_t ent0, uint32_t gid0, uint32_t stamp,
+                                            uint32_t* list, uint32_t cap, Ctl* ctl, uint32_t* log_stamp,
+                                            uint32_t* log_id, uint32_t log_cap) {
+    const int nspk = __popc(spk_mask);
+    uint32_t tot;
+    uint32_t pos = warp_reserve(list, nspk, &tot);
+#pragma unroll
+    for (int j = 0; j < kNeuronsPerThread; ++j) {
+        if (spk_mask >> j & 1u) {
+            if (pos < cap) list[1 + pos] = ent0 + j;
+            else atomicOr(&ctl->error_flags, kErrSpikeListFull);
+            ++pos;
+        }
+    }
+    if ((threadIdx.x & 31) == 31) atomicAdd(&ctl->n_spikes, (unsigned long long)tot);
+    if (log_stamp) {
+        pos = warp_reserve(&ctl->log_count, nspk, &tot);
+#pragma unroll
+        for (int j = 0; j < kNeuronsPerThread; ++j) {
+            if (spk_mask >> j & 1u) {
+                if (pos < log_cap) {
+                    log_stamp[pos] = stamp;
+                    log_id[pos] = gid0 + j;
+                } else {
+                    atomicOr(&ctl->error_flags, kErrLogFull);
+                }
+                ++pos;
+            }
+        }
+    }
+}
+
+}  // namespace bmtk

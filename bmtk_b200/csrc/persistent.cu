@@ -1,0 +1,299 @@
+// Persistent stepping kernel: a whole chunk of simulation steps in ONE cooperative launch.
+//
+// One block per SM stays resident and loops over the steps. A thread owns four neurons; when
+// the network fits (n_pad/4 <= grid threads, e.g. 230 924 neurons on 148 SMs x 512 threads) their
+// state lives in registers for the whole launch and HBM/L2 only sees the ring slots, the spike
+// lists, the CSR rows of spiking sources and the recorders. Steps inside an exchange window
+// need no grid-wide synchronisation at all (a thread touches only its own neurons and ring
+// cells); per window there are two grid barriers: after the window's updates, and after the
+// delivery of its spikes. That replaces w + 1 kernel launches per window.
+//
+// Visibility: ring cells and spike lists are written by other SMs between barriers, so every
+// read of them goes through L2 (__ldcg); CSR rows and type tables are read-only and use the
+// normal path. Spike lists are double buffered by window parity: the list of window k+1 is
+// cleared while window k is being delivered.
+//
+// grid.sync() is the cooperative-groups barrier; the launch is cooperative, so all blocks are
+// co-resident by construction (the launch fails cleanly otherwise) and no hand-written spin exists.
+#include <cooperative_groups.h>
+
+#include "glif_math.cuh"
+#include "persistent.cuh"
+#include "philox.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace bmtk {
+
+constexpr int kPT = 512;         // threads per block, one block per SM
+constexpr int kSub = 128;        // threads that stream one CSR row together
+constexpr int kSmemTypesP = 128;
+
+__device__ __forceinline__ F4 ld4cg(const float* p) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(p));
+    return F4{{t.x, t.y, t.z, t.w}};
+}
+
+__device__ __forceinline__ unsigned long long gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <bool THETA, bool IEXT>
+__device__ __forceinline__ void do_group(const PersistArgs& a, const TypeConsts* types, Neuron4<THETA, IEXT>& nr,
+                                         const int (&pslot)[4], bool valid, uint32_t i0, unsigned long long step,
+                                         uint32_t s_in_win, uint32_t* list, uint32_t sample_base) {
+    uint32_t mask = 0;
+    if (valid) {
+        const uint32_t np = a.n_pad;
+        const uint32_t slot = (uint32_t)(step % a.ring_slots);
+        float* ring = a.ring + (size_t)slot * kPorts * np + i0;
+        F4 in[kPorts];
+#pragma unroll
+        for (int p = 0; p < kPorts; ++p) in[p] = ld4cg(ring + (size_t)p * np);
+        mask = nr.step(types, in);
+        if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
+        const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int p = 0; p < kPorts; ++p) st4(ring + (size_t)p * np, zero);
+        if (a.probe_slot && (step + 1) % a.probe_interval == 0) {
+            const unsigned long long sample = (step + 1) / a.probe_interval - 1ull - sample_base;
+            if (sample < a.trace_cap) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (pslot[j] >= 0) a.trace[(size_t)sample * a.n_probe + pslot[j]] = nr.U.v[j] + types[nr.ty[j]].E_L;
+            }
+        }
+    }
+    if (__any_sync(0xffffffffu, mask != 0))
+        emit_spikes(mask, (s_in_win << kSrcBits) | (a.lo + i0), a.lo + i0, (uint32_t)(step + 1), list, a.send_cap, a.ctl,
+                    a.log_stamp, a.log_id, a.log_cap);
+}
+
+// Delivery of one window: items are the recurrent list, the replayed virtual spikes of the
+// window's steps and the on-line Poisson list; a group of kSub threads streams one row.
+__device__ __forceinline__ void deliver_window(const PersistArgs& a, const uint32_t* list, const uint32_t* virt,
+                                               unsigned long long win_base, uint32_t win_len) {
+    const uint32_t n_rec = min(__ldcg(list), a.send_cap);
+    uint32_t n_in = 0, in_begin = 0;
+    if (a.in_ptr) {
+        unsigned long long lo = win_base > a.in_ptr_base ? win_base - a.in_ptr_base : 0ull;
+        unsigned long long hi = win_base + win_len > a.in_ptr_base ? win_base + win_len - a.in_ptr_base : 0ull;
+        const unsigned long long last = a.in_ptr_len - 1;
+        if (lo > last) lo = last;
+        if (hi > last) hi = last;
+        in_begin = a.in_ptr[lo];
+        n_in = a.in_ptr[hi] - in_begin;
+    }
+    const uint32_t n_virt = virt ? min(__ldcg(virt), a.virt_cap) : 0u;
+    const uint32_t total = n_rec + n_in + n_virt;
+    const uint32_t sub = threadIdx.x / kSub, lane = threadIdx.x % kSub;
+    const uint32_t n_sub = gridDim.x * (kPT / kSub);
+    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
+    const size_t plane = (size_t)a.n_pad;
+    unsigned long long events = 0ull;
+    for (uint32_t idx = blockIdx.x * (kPT / kSub) + sub; idx < total; idx += n_sub) {
+        uint32_t src;
+        unsigned long long step;
+        if (idx < n_rec) {
+            const uint32_t e = __ldcg(list + 1 + idx);
+            src = e & kSrcMask;
+            step = win_base + (e >> kSrcBits);
+        } else if (idx < n_rec + n_in) {
+            src = a.in_src[in_begin + idx - n_rec];
+            step = a.in_step[in_begin + idx - n_rec];
+        } else {
+            const uint32_t e = __ldcg(virt + 1 + idx - n_rec - n_in);
+            src = e & kSrcMask;
+            step = win_base + (e >> kSrcBits);
+        }
+        const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
+        const uint32_t slot0 = (uint32_t)(step % a.ring_slots);
+        if (lane == 0) events += en - b;
+        unsigned long long k = b + lane;
+        for (; k + 3ull * kSub < en; k += 4ull * kSub) {
+            uint2 e[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = __ldg(&a.entries[k + (unsigned long long)u * kSub]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                uint32_t slot = slot0 + (e[u].x >> (tb + 2));
+                if (slot >= a.ring_slots) slot -= a.ring_slots;
+                atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
+                          __uint_as_float(e[u].y));
+            }
+        }
+        for (; k < en; k += kSub) {
+            const uint2 e = __ldg(&a.entries[k]);
+            uint32_t slot = slot0 + (e.x >> (tb + 2));
+            if (slot >= a.ring_slots) slot -= a.ring_slots;
+            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+        }
+    }
+    if (events) atomicAdd(&a.ctl->n_events, events);
+}
+
+template <bool THETA, bool IEXT, bool RESIDENT>
+__global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    cg::grid_group grid = cg::this_grid();
+    TypeConsts* s_types = reinterpret_cast<TypeConsts*>(smem_raw);
+    const bool use_smem = a.n_types <= kSmemTypesP;
+    if (use_smem) {
+        const int words = a.n_types * (int)(sizeof(TypeConsts) / 4);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(a.types);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(s_types);
+        for (int i = threadIdx.x; i < words; i += kPT) dst[i] = src[i];
+        __syncthreads();
+    }
+    const TypeConsts* types = use_smem ? s_types : a.types;
+
+    const uint32_t nthreads = gridDim.x * kPT;
+    const uint32_t gtid = blockIdx.x * kPT + threadIdx.x;
+    const uint32_t n_groups = a.n_pad / kNeuronsPerThread;
+    const unsigned long long step_base = __ldcg(&a.ctl->step_base);
+    const uint32_t sample_base = __ldcg(&a.ctl->sample_base);
+    const bool timer = a.profile && gtid == 0;
+
+    Neuron4<THETA, IEXT> nr;
+    int pslot[4] = {-1, -1, -1, -1};
+    const bool mine = gtid < n_groups;
+    if (RESIDENT && mine) {
+        nr.load(a.st, a.n_pad, gtid * kNeuronsPerThread);
+        if (a.probe_slot) {
+            const int4 q = *reinterpret_cast<const int4*>(a.probe_slot + gtid * kNeuronsPerThread);
+            pslot[0] = q.x; pslot[1] = q.y; pslot[2] = q.z; pslot[3] = q.w;
+        }
+    }
+
+    uint32_t cgi = a.ce_group_begin;       // next clamp group (distinct step with events)
+    uint32_t win = 0, s_in_win = 0;
+    unsigned long long win_base = step_base;
+    unsigned long long t0 = timer ? gtimer() : 0ull;
+
+    for (uint32_t s = 0; s < a.n_steps; ++s) {
+        const unsigned long long step = step_base + s;
+        uint32_t* list = a.lists[win & 1];
+        uint32_t* virt = a.poisson_thr ? a.virts[win & 1] : nullptr;
+
+        if (IEXT) {
+            // clamp changes effective from this step on; the branch is uniform over the grid
+            bool changed = false;
+            while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= step) {
+                const uint32_t b = a.ce_group_ptr[cgi], e = a.ce_group_ptr[cgi + 1];
+                for (uint32_t k = b + gtid; k < e; k += nthreads)
+                    atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
+                ++cgi;
+                changed = true;
+            }
+            if (changed) {
+                grid.sync();
+                if (RESIDENT && mine) nr.iex = ld4cg(a.st.i_ext + gtid * kNeuronsPerThread);
+            }
+        }
+
+        if (RESIDENT) {
+            do_group<THETA, IEXT>(a, types, nr, pslot, mine, gtid * kNeuronsPerThread, step, s_in_win, list, sample_base);
+        } else {
+            for (uint32_t base = 0; base < n_groups; base += nthreads) {
+                const uint32_t g = base + gtid;
+                const bool valid = g < n_groups;
+                const uint32_t i0 = g * kNeuronsPerThread;
+                if (valid) {
+                    nr.load(a.st, a.n_pad, i0);
+                    if (IEXT) nr.iex = ld4cg(a.st.i_ext + i0);
+                    if (a.probe_slot) {
+                        const int4 q = *reinterpret_cast<const int4*>(a.probe_slot + i0);
+                        pslot[0] = q.x; pslot[1] = q.y; pslot[2] = q.z; pslot[3] = q.w;
+                    }
+                }
+                do_group<THETA, IEXT>(a, types, nr, pslot, valid, i0, step, s_in_win, list, sample_base);
+                if (valid) nr.store(a.st, a.n_pad, i0);
+            }
+        }
+
+        if (virt) {
+            for (uint32_t base = 0; base < a.n_virtual; base += nthreads) {
+                const uint32_t v = base + gtid;
+                int k = 0;
+                if (v < a.n_virtual) {
+                    const uint4 thr = a.poisson_thr[v];
+                    const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), 0u, (uint32_t)a.seed,
+                                                     (uint32_t)(a.seed >> 32)).x;
+                    k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
+                }
+                if (__any_sync(0xffffffffu, k > 0)) {
+                    uint32_t tot;
+                    const uint32_t pos = warp_reserve(virt, k, &tot);
+                    const uint32_t e = (s_in_win << kSrcBits) | (a.n_global + v);
+                    for (int j = 0; j < k; ++j) {
+                        if (pos + j < a.virt_cap) virt[1 + pos + j] = e;
+                        else atomicOr(&a.ctl->error_flags, kErrVirtListFull);
+                    }
+                    if ((threadIdx.x & 31) == 31) atomicAdd(&a.ctl->n_input_spikes, (unsigned long long)tot);
+                }
+            }
+        }
+
+        ++s_in_win;
+        if (s_in_win == a.window || s + 1 == a.n_steps) {
+            grid.sync();
+            const unsigned long long t1 = timer ? gtimer() : 0ull;
+            if (gtid == 0) {
+                // the other parity's lists were last read one window ago: clear them for the next window
+                a.lists[(win + 1) & 1][0] = 0u;
+                if (a.poisson_thr) a.virts[(win + 1) & 1][0] = 0u;
+            }
+            deliver_window(a, list, virt, win_base, s_in_win);
+            grid.sync();
+            if (timer) {
+                const unsigned long long t2 = gtimer();
+                a.ctl->t_update_ns += t1 - t0;
+                a.ctl->t_prop_ns += t2 - t1;
+                a.ctl->n_windows += 1ull;
+                t0 = t2;
+            }
+            ++win;
+            win_base += s_in_win;
+            s_in_win = 0;
+        }
+    }
+
+    if (RESIDENT && mine) nr.store(a.st, a.n_pad, gtid * kNeuronsPerThread);
+    if (gtid == 0) a.ctl->step_base = step_base + a.n_steps;
+}
+
+int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem) {
+    int per_sm = 0, sms = 0;
+    const void* f = persistent_kernel_ptr(has_theta, has_iext, resident);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, kPT, smem) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return per_sm > 0 ? sms : 0;   // one block per SM
+}
+
+const void* persistent_kernel_ptr(bool has_theta, bool has_iext, bool resident) {
+#define PK(T, I, R) (const void*)persistent_kernel<T, I, R>
+    if (has_theta) {
+        if (has_iext) return resident ? PK(true, true, true) : PK(true, true, false);
+        return resident ? PK(true, false, true) : PK(true, false, false);
+    }
+    if (has_iext) return resident ? PK(false, true, true) : PK(false, true, false);
+    return resident ? PK(false, false, true) : PK(false, false, false);
+#undef PK
+}
+
+uint32_t persistent_threads_per_block() { return kPT; }
+
+cudaError_t launch_persistent(const PersistArgs& a, bool has_theta, bool has_iext, bool resident, int blocks,
+                              cudaStream_t s) {
+    const size_t smem = a.n_types <= kSmemTypesP ? sizeof(TypeConsts) * (size_t)a.n_types : 0;
+    PersistArgs copy = a;
+    void* args[] = {&copy};
+    return cudaLaunchCooperativeKernel(persistent_kernel_ptr(has_theta, has_iext, resident), dim3(blocks), dim3(kPT), args,
+                                       smem, s);
+}
+
+size_t persistent_smem(int n_types) { return n_types <= kSmemTypesP ? sizeof(TypeConsts) * (size_t)n_types : 0; }
+
+}  // namespace bmtk

@@ -1,0 +1,60 @@
+#pragma once
+#include "common.cuh"
+
+namespace bmtk {
+
+// Arguments of one persistent launch (a chunk of steps on one GPU).
+struct PersistArgs {
+    // neurons
+    StateSoA st;
+    const TypeConsts* types;
+    int32_t n_types;
+    uint32_t n_local, n_pad, lo, n_global;
+    float* ring;
+    uint32_t ring_slots;
+    Ctl* ctl;
+    // spike lists, double buffered by window parity: [0] = count, then entries
+    uint32_t* lists[2];
+    uint32_t send_cap;
+    uint32_t* log_stamp;
+    uint32_t* log_id;
+    uint32_t log_cap;
+    // on-line Poisson cells
+    const uint4* poisson_thr;
+    uint32_t n_virtual;
+    uint64_t seed;
+    uint32_t* virts[2];
+    uint32_t virt_cap;
+    // CSR and replayed inputs
+    const unsigned long long* rowptr;
+    const uint2* entries;
+    uint32_t target_bits;
+    const uint32_t* in_ptr;
+    unsigned long long in_ptr_base;
+    uint32_t in_ptr_len;
+    const uint32_t* in_step;
+    const uint32_t* in_src;
+    // stepping
+    uint32_t n_steps, window;
+    // clamp events grouped by step: group g covers events [ce_group_ptr[g], ce_group_ptr[g+1])
+    const unsigned long long* ce_group_step;
+    const uint32_t* ce_group_ptr;
+    uint32_t ce_group_begin, ce_group_end;
+    const uint32_t* ce_target;
+    const float* ce_delta;
+    // V_m probes: probe_slot[i] = trace column of local neuron i or -1
+    const int32_t* probe_slot;
+    uint32_t n_probe, probe_interval;
+    float* trace;
+    uint32_t trace_cap;
+    uint32_t profile;
+};
+
+const void* persistent_kernel_ptr(bool has_theta, bool has_iext, bool resident);
+int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem);
+uint32_t persistent_threads_per_block();
+size_t persistent_smem(int n_types);
+cudaError_t launch_persistent(const PersistArgs& a, bool has_theta, bool has_iext, bool resident, int blocks,
+                              cudaStream_t s);
+
+}  // namespace bmtk

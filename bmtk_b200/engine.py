@@ -17,13 +17,37 @@ GLIF_PSC_DEFAULTS = dict(
     asc_init=(0.0, 0.0), asc_decay=(0.003, 0.1), asc_amps=(-9.18, -198.94), asc_r=(1.0, 1.0),
     tau_syn=(2.0,), th_spike_add=0.37, th_spike_decay=0.009, voltage_reset_fraction=0.20,
     voltage_reset_add=18.51, th_voltage_index=0.005, th_voltage_decay=0.09,
-    spike_dependent_threshold=False, after_spike_currents=False, adapting_threshold=False)
+    spike_dependent_threshold=False, after_spike_currents=False, adapting_threshold=False, I_e=0.0)
+
+# NEST's iaf_psc_alpha defaults
+IAF_PSC_ALPHA_DEFAULTS = dict(V_m=-70.0, E_L=-70.0, C_m=250.0, tau_m=10.0, t_ref=2.0, V_th=-55.0, V_reset=-70.0,
+                              tau_syn_ex=2.0, tau_syn_in=2.0, I_e=0.0, V_min=None)
+
+
+def iaf_psc_alpha_params(d):
+    """NEST iaf_psc_alpha parameter dict -> GlifParams with model = iaf_psc_alpha: g = C_m/tau_m,
+    receptor ports 0 / 1 carry the excitatory / inhibitory alpha currents."""
+    unknown = set(d) - set(IAF_PSC_ALPHA_DEFAULTS)
+    if unknown:
+        raise ValueError('unknown iaf_psc_alpha parameter(s): %s' % ', '.join(sorted(unknown)))
+    q = dict(IAF_PSC_ALPHA_DEFAULTS)
+    q.update(d)
+    if q['V_min'] is not None and np.isfinite(q['V_min']):
+        raise ValueError('iaf_psc_alpha: a finite V_min is not supported')
+    p = glif_params(dict(V_m=q['V_m'], E_L=q['E_L'], C_m=q['C_m'], g=q['C_m'] / q['tau_m'], t_ref=q['t_ref'],
+                         V_th=q['V_th'], V_reset=q['V_reset'], tau_syn=(q['tau_syn_ex'], q['tau_syn_in']), I_e=q['I_e']))
+    p.model = _cabi.MODEL_IAF_PSC_ALPHA
+    return p
 
 
 def glif_params(d):
-    """NEST-format glif_psc parameter dict -> GlifParams (unknown keys are rejected)."""
+    """NEST-format glif_psc parameter dict -> GlifParams (unknown keys are rejected). A dict with
+    key 'model': 'iaf_psc_alpha' is taken as iaf_psc_alpha parameters."""
     if isinstance(d, GlifParams):
         return d
+    if d.get('model') == 'iaf_psc_alpha':
+        return iaf_psc_alpha_params({k: v for k, v in d.items() if k != 'model'})
+    d = {k: v for k, v in d.items() if k != 'model'}
     unknown = set(d) - set(GLIF_PSC_DEFAULTS)
     if unknown:
         raise ValueError('unknown glif_psc parameter(s): %s' % ', '.join(sorted(unknown)))
@@ -31,7 +55,7 @@ def glif_params(d):
     q.update(d)
     p = GlifParams()
     for k in ('V_m', 'V_th', 'g', 'E_L', 'C_m', 't_ref', 'V_reset', 'th_spike_add', 'th_spike_decay',
-              'voltage_reset_fraction', 'voltage_reset_add', 'th_voltage_index', 'th_voltage_decay'):
+              'voltage_reset_fraction', 'voltage_reset_add', 'th_voltage_index', 'th_voltage_decay', 'I_e'):
         setattr(p, k, float(q[k]))
     for k in ('asc_init', 'asc_decay', 'asc_amps', 'asc_r'):
         v = [float(x) for x in q[k]]

@@ -321,10 +321,12 @@ class PointNetwork(object):
             dp.setdefault('spike_dependent_threshold', r)
             dp.setdefault('after_spike_currents', a)
             dp.setdefault('adapting_threshold', v)
+        elif model == 'iaf_psc_alpha':
+            dp['model'] = 'iaf_psc_alpha'
         elif model != 'glif_psc':
             self.io.log_exception('node type {} of population {}: model_template "{}" is not supported by this '
-                                  'engine (supported: nest:glif_psc and the nest:glif_lif*_psc variants)'.format(
-                                      type_id, pop.name, mt))
+                                  'engine (supported: nest:glif_psc, the nest:glif_lif*_psc variants and '
+                                  'nest:iaf_psc_alpha)'.format(type_id, pop.name, mt))
         dp.pop('type', None)
         return {k: (np.asarray(v).tolist() if isinstance(v, np.ndarray) else v) for k, v in dp.items()}
 
@@ -412,10 +414,18 @@ class PointNetwork(object):
                     float(delay.min()), t, epop.name, self._dt)
                 self.io.log_error(msg)
                 raise BadDelay(msg)
-            yield dict(src=src_lookup(epop.source_node_ids[m]),
-                       trg=self._gid_pool.get_nestids(trg_pop_name, epop.target_node_ids[m]),
-                       weight=weight, delay=delay, port=np.full(n, port, dtype=np.uint8), edge_type_id=int(t),
-                       population=epop.name)
+            trg = self._gid_pool.get_nestids(trg_pop_name, epop.target_node_ids[m])
+            ports = np.full(n, port, dtype=np.uint8)
+            # iaf_psc_alpha targets have no receptor ports: the sign of the weight picks the
+            # excitatory (port 0) or inhibitory (port 1) alpha current
+            iaf = self._type_is_iaf()[self.type_index[trg]] if n else np.zeros(0, dtype=bool)
+            if np.any(iaf):
+                ports = np.where(iaf, (weight < 0).astype(np.uint8), ports).astype(np.uint8)
+            yield dict(src=src_lookup(epop.source_node_ids[m]), trg=trg, weight=weight, delay=delay, port=ports,
+                       edge_type_id=int(t), population=epop.name)
+
+    def _type_is_iaf(self):
+        return np.array([t.get('model') == 'iaf_psc_alpha' for t in self.types], dtype=bool)
 
     def build_recurrent_edges(self):
         """pointnetwork.py:161-173: every edge population between non-virtual populations."""

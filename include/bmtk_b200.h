@@ -50,7 +50,19 @@ typedef struct bmtk_glif_params {
     int32_t spike_dependent_threshold;  /* "R" */
     int32_t after_spike_currents;       /* "ASC" */
     int32_t adapting_threshold;         /* "A" */
+    double I_e;                         /* constant input current, pA */
+    int32_t model;                      /* BMTK_MODEL_GLIF_PSC or BMTK_MODEL_IAF_PSC_ALPHA */
+    int32_t reserved;
 } bmtk_glif_params;
+
+/* `model` selects the conventions that differ between NEST models sharing these dynamics:
+ * glif_psc holds V during refractoriness and resets when it ends, counts the refractory period
+ * down in double precision and fires on V > V_th; iaf_psc_alpha (tau_syn = {tau_syn_ex,
+ * tau_syn_in}, g = C_m / tau_m, no after-spike currents; the caller routes weights >= 0 to port 0
+ * and weights < 0 to port 1) resets V in the spike step, is refractory for round(t_ref/dt) steps
+ * and fires on V >= V_th. */
+#define BMTK_MODEL_GLIF_PSC 0
+#define BMTK_MODEL_IAF_PSC_ALPHA 1
 
 typedef struct bmtk_engine bmtk_engine;
 
@@ -117,7 +129,12 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
  *  "spike_capacity" entries of the per-window spike list, 0 = automatic
  *  "log_capacity"   entries of the device spike log between host drains
  *  "event_capacity" events per window the deterministic path can sort
- *  "use_graph"      0|1 replay each window as a CUDA graph (default 1)
+ *  "persistent"     0|1 run each chunk as ONE cooperative kernel that loops over the steps with the
+ *                   neuron state held in registers (default 1; single rank, atomic delivery; may
+ *                   be changed between runs)
+ *  "phase_timers"   0|1 let the persistent kernel accumulate the device time of its update and
+ *                   delivery phases (counters "phase_update_ns", "phase_propagate_ns", "phase_windows")
+ *  "use_graph"      0|1 replay each window as a CUDA graph when not persistent (default 1)
  *  "chunk_steps"    steps between host drains of the spike log / traces */
 int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
 

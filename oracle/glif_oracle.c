@@ -54,6 +54,9 @@ typedef struct {
     double th_voltage_index, th_voltage_decay;
     int32_t n_ports;
     int32_t spike_dependent_threshold, after_spike_currents, adapting_threshold;
+    double I_e;
+    int32_t model;      /* 0 glif_psc, 1 iaf_psc_alpha */
+    int32_t reserved;
 } orc_glif_params;
 
 /* Per-type constants for one resolution h. */
@@ -69,6 +72,9 @@ typedef struct {
     double E_L;
     int32_t n_ref;                     /* update steps from spike to reset, inclusive */
     int32_t n_ports, has_theta_spike, has_asc, has_theta_voltage;
+    double I_e;
+    int32_t iaf;                       /* iaf_psc_alpha conventions: reset in the spike step, >= test */
+    int32_t pad;
 } orc_glif_consts;
 
 /* x + expm1(-x), accurate for small |x| (the numerator of the alpha-kernel/membrane cross term). */
@@ -136,6 +142,14 @@ void orc_glif_consts_init(const orc_glif_params* p, double h, orc_glif_consts* c
     c->th_inf = p->V_th - p->E_L;
     c->v_reset = p->V_reset - p->E_L;
     c->n_ref = refractory_steps(p->t_ref, h);
+    c->I_e = p->I_e;
+    c->iaf = p->model == 1;
+    if (c->iaf) {
+        /* NEST iaf_psc_alpha: RefractoryCounts = Time(ms(t_ref)).get_steps(); V is set to V_reset in
+         * the spike step and not integrated for that many following steps; spike when V >= V_th. */
+        c->n_ref = (int32_t)llround(p->t_ref / h);
+        if (c->n_ref < 1) c->n_ref = 1;
+    }
     c->theta_spike_decay = exp(-p->th_spike_decay * h);
     c->theta_spike_refr_decay = exp(-p->th_spike_decay * p->t_ref);
     c->th_spike_add = p->th_spike_add;
@@ -284,7 +298,7 @@ int orc_run(orc_run_args* a)
                 }
                 if (c->has_theta_spike) a->th_spike[i] *= c->theta_spike_decay;
                 const double v_old = U;
-                const double I = a->i_ext[i];
+                const double I = a->i_ext[i] + c->I_e;
                 U = v_old * c->P33 + (I + asc_sum) * c->P30;
                 for (int p = 0; p < c->n_ports; ++p)
                     U += c->P31[p] * a->y1[p * N + i] + c->P32[p] * a->y2[p * N + i];
@@ -296,9 +310,10 @@ int orc_run(orc_run_args* a)
                         + c->abpara * beta;
                 }
                 const double th = a->th_spike[i] + a->th_voltage[i] + c->th_inf;
-                if (U > th) {
+                if (c->iaf ? (U >= th) : (U > th)) {
                     a->refr[i] = c->n_ref;
                     spk = 1;
+                    if (c->iaf) U = c->v_reset;
                 }
             }
             a->U[i] = U;

@@ -31,6 +31,7 @@ class GlifParams(C.Structure):
         ('th_voltage_index', C.c_double), ('th_voltage_decay', C.c_double),
         ('n_ports', C.c_int32), ('spike_dependent_threshold', C.c_int32),
         ('after_spike_currents', C.c_int32), ('adapting_threshold', C.c_int32),
+        ('I_e', C.c_double), ('model', C.c_int32), ('reserved', C.c_int32),
     ]
 
 
@@ -49,6 +50,7 @@ class GlifConsts(C.Structure):
         ('G', C.c_double), ('E_L', C.c_double),
         ('n_ref', C.c_int32), ('n_ports', C.c_int32), ('has_theta_spike', C.c_int32),
         ('has_asc', C.c_int32), ('has_theta_voltage', C.c_int32),
+        ('I_e', C.c_double), ('iaf', C.c_int32), ('pad', C.c_int32),
     ]
 
 
@@ -78,16 +80,28 @@ _DEFAULTS = dict(
     asc_init=(0.0, 0.0), asc_decay=(0.003, 0.1), asc_amps=(-9.18, -198.94), asc_r=(1.0, 1.0),
     tau_syn=(2.0,), th_spike_add=0.37, th_spike_decay=0.009, voltage_reset_fraction=0.20,
     voltage_reset_add=18.51, th_voltage_index=0.005, th_voltage_decay=0.09,
-    spike_dependent_threshold=False, after_spike_currents=False, adapting_threshold=False)
+    spike_dependent_threshold=False, after_spike_currents=False, adapting_threshold=False, I_e=0.0)
+
+_IAF_DEFAULTS = dict(V_m=-70.0, E_L=-70.0, C_m=250.0, tau_m=10.0, t_ref=2.0, V_th=-55.0, V_reset=-70.0,
+                     tau_syn_ex=2.0, tau_syn_in=2.0, I_e=0.0)
 
 
 def make_params(d):
-    """dict with NEST glif_psc key names -> GlifParams."""
+    """dict with NEST glif_psc key names -> GlifParams; {'model': 'iaf_psc_alpha', ...} with NEST
+    iaf_psc_alpha names is mapped to g = C_m/tau_m, tau_syn = (tau_syn_ex, tau_syn_in), model = 1."""
+    if d.get('model') == 'iaf_psc_alpha':
+        q = dict(_IAF_DEFAULTS)
+        q.update({k: v for k, v in d.items() if k in _IAF_DEFAULTS})
+        p = make_params(dict(V_m=q['V_m'], E_L=q['E_L'], C_m=q['C_m'], g=q['C_m'] / q['tau_m'], t_ref=q['t_ref'],
+                             V_th=q['V_th'], V_reset=q['V_reset'], tau_syn=(q['tau_syn_ex'], q['tau_syn_in']),
+                             I_e=q['I_e']))
+        p.model = 1
+        return p
     q = dict(_DEFAULTS)
     q.update({k: v for k, v in d.items() if k in _DEFAULTS})
     p = GlifParams()
     for k in ('V_m', 'V_th', 'g', 'E_L', 'C_m', 't_ref', 'V_reset', 'th_spike_add', 'th_spike_decay',
-              'voltage_reset_fraction', 'voltage_reset_add', 'th_voltage_index', 'th_voltage_decay'):
+              'voltage_reset_fraction', 'voltage_reset_add', 'th_voltage_index', 'th_voltage_decay', 'I_e'):
         setattr(p, k, float(q[k]))
     for k in ('asc_init', 'asc_decay', 'asc_amps', 'asc_r'):
         v = [float(x) for x in q[k]]

@@ -28,8 +28,8 @@ def test_library_exports_every_declared_symbol(cabi):
 
 def test_struct_layout_matches_header(cabi):
     from bmtk_b200 import _cabi
-    # 7 + 4*2 + 4 + 6 doubles, 4 int32
-    assert C.sizeof(_cabi.GlifParams) == (7 + 8 + 4 + 6) * 8 + 4 * 4
+    # 7 + 4*2 + 4 + 6 doubles, 4 int32, I_e double, model + reserved int32
+    assert C.sizeof(_cabi.GlifParams) == (7 + 8 + 4 + 6) * 8 + 4 * 4 + 8 + 8
 
 
 def test_argument_errors_do_not_need_a_gpu(cabi):

@@ -230,11 +230,52 @@ def test_graph_replay_equals_plain_launches(cabi):
     """Same kernels, same order: CUDA-graph replay and stream launches must agree bit for bit in
     deterministic bookkeeping (spike lists) when sums are order-independent (no recurrent edges)."""
     net = W.c1(n=3000, t_stop_ms=150.0)
-    a = _run_engine(net, options=dict(use_graph=1))
-    b = _run_engine(net, options=dict(use_graph=0))
+    a = _run_engine(net, options=dict(use_graph=1, persistent=0))
+    b = _run_engine(net, options=dict(use_graph=0, persistent=0))
     assert np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
     assert np.array_equal(a[3].view(np.uint32), b[3].view(np.uint32))
     assert a[0].counter('launches') == b[0].counter('launches')
+
+
+@pytest.mark.parametrize('n', [3000, 700001])
+def test_persistent_kernel_equals_per_step_launches(cabi, n):
+    """The cooperative persistent kernel (state in registers for n = 3000, streamed for n = 700001,
+    which exceeds one group per thread) must reproduce the per-step launches bit for bit where
+    sums are order-independent: unconnected neurons with clamps, probes and the spike log."""
+    net = W.c1(n=n, t_stop_ms=140.0 if n < 10000 else 110.0)
+    a = _run_engine(net, options=dict(persistent=1, chunk_steps=1000))
+    b = _run_engine(net, options=dict(persistent=0))
+    assert a[0].counter('persistent_resident') == (1 if n < 10000 else 0)
+    assert a[0].counter('launches') < 10 and b[0].counter('launches') > 2000
+    assert len(a[1]) > 50
+    assert np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
+    assert np.array_equal(a[3].view(np.uint32), b[3].view(np.uint32))
+    for var in ('U', 'asc0', 'asc1', 'i_ext', 'refr'):
+        assert np.array_equal(a[0].state(var).view(np.uint32), b[0].state(var).view(np.uint32)), var
+
+
+def test_persistent_kernel_network_and_poisson(cabi, oracle):
+    """Persistent kernel on a connected network with on-line Poisson cells: the input spike count is
+    the host Philox count, spikes match the oracle to within one step over the first 100 ms, and
+    a run split into unequal pieces (partial windows at the chunk ends) gives the same event count
+    as one long run of the per-step path."""
+    net = W.c0(t_stop_ms=400.0, poisson_online=True)
+    eng, st, ids, tr = _run_engine(net, options=dict(persistent=1))
+    steps, srcs = oracle.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, net.n_steps)
+    assert eng.counter('input_spikes') == len(steps)
+    r = oracle_from_network(net).run(net.n_steps)
+    ok, bad = _spikes_within_one_step(st, ids, r['spike_step'], r['spike_id'], 1000)
+    assert ok, bad
+    div = _first_divergence(st, ids, r['spike_step'], r['spike_id'])
+    _trace_check(tr, r['trace'], min(div - 1, net.n_steps))
+    e2 = W.build_engine(net, options=dict(persistent=1, chunk_steps=333))
+    for k in (7, 1000, 13, 2980):
+        e2.run(k)
+    s2, i2 = e2.fetch_spikes()
+    d2 = _first_divergence(s2.astype(np.int64), i2.astype(np.int64), st, ids)
+    assert d2 > 1000           # identical until fp32 summation order makes the two runs part
+    if d2 == np.inf:
+        assert e2.counter('events') == eng.counter('events')
 
 
 def test_window_size_does_not_change_results(cabi):

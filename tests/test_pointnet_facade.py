@@ -256,3 +256,51 @@ def test_poisson_generator_rate_and_units():
     psg3 = pointnet.PoissonSpikeGenerator(population='lgn', seed=1)
     psg3.add(node_ids=[0], firing_rate=np.array([0.0, 50.0, 0.0]), times=np.array([0.0, 1.0, 2.0]))
     assert 20 < psg3.n_spikes() < 90
+
+
+@needs_ref
+def test_stock_example_network_expands_to_the_expected_edge_list():
+    """examples/point_450glifs read from the reference tree: per edge weight = nsyns * syn_weight,
+    delay 2.0 ms, port from the synapse JSON (e2e 1, i2e 2, e2i 3, i2i 4, LGN 1; iaf_psc_alpha
+    targets by weight sign) — computed here independently from the raw files."""
+    import pandas as pd
+    from bmtk_b200 import h5io
+    ex = REF + '/examples/point_450glifs'
+    cwd = os.getcwd()
+    os.chdir(ex)
+    try:
+        conf = pointnet.Config.from_json('config.simulation.json')
+        g = pointnet.PointNetwork.from_config(conf)
+        g.dt = conf.run['dt']
+        g.build()
+        g.add_spike_trains(pointnet.SpikeTrains.load(conf.inputs['LGN_spikes']['input_file']), 'lgn')
+    finally:
+        os.chdir(cwd)
+    assert len(g.gid_pool) == 450 and g.n_virtual == 100
+    src, trg, w, d, port = g.edge_arrays()
+    assert len(src) == 28555 + 36035 and np.all(d == 2.0)
+    node_types = pd.read_csv(ex + '/network/v1_node_types.csv', sep=' ').set_index('node_type_id')
+    with h5io.File(ex + '/network/v1_nodes.h5', 'r') as h:
+        ntid = h['/nodes/v1/node_type_id'][()].astype(int)
+    is_iaf_node = np.array([node_types.loc[t, 'model_template'] == 'nest:iaf_psc_alpha' for t in ntid])
+    gid_of_node = g.gid_pool.get_nestids('v1', np.arange(450))
+    exp = []
+    for fname, pop, types_csv, virtual in (('v1_v1_edges.h5', 'v1_to_v1', 'v1_v1_edge_types.csv', False),
+                                           ('lgn_v1_edges.h5', 'lgn_to_v1', 'lgn_v1_edge_types.csv', True)):
+        et = pd.read_csv(ex + '/network/' + types_csv, sep=' ').set_index('edge_type_id')
+        with h5io.File(ex + '/network/' + fname, 'r') as h:
+            p = h['/edges/' + pop]
+            s, t = p['source_node_id'][()].astype(int), p['target_node_id'][()].astype(int)
+            etid, ns = p['edge_type_id'][()].astype(int), p['0/nsyns'][()].astype(float)
+        for k in range(len(s)):
+            row = et.loc[etid[k]]
+            weight = np.float32(ns[k] * row['syn_weight'])
+            dyn = json.load(open(ex + '/../point_components/synaptic_models/' + row['dynamics_params']))
+            prt = int(weight < 0) if is_iaf_node[t[k]] else dyn.get('receptor_type', 1) - 1
+            exp.append((450 + s[k] if virtual else int(gid_of_node[s[k]]), int(gid_of_node[t[k]]), float(weight), prt))
+    got = sorted(zip(src.tolist(), trg.tolist(), w.tolist(), port.tolist()))
+    assert got == sorted(exp)
+    n_in = sum(len(x[0]) for x in g.input_spikes)
+    assert n_in == 3044
+    # the two iaf_psc_alpha types became engine types with that model tag
+    assert sum(t.get('model') == 'iaf_psc_alpha' for t in g.types) == 2
