@@ -267,6 +267,28 @@ def main():
     launches = reduce(eng.counter('launches') - l0, dist.ReduceOp.SUM if world > 1 else None)
     value = events / (dev_ms * 1e-3)
 
+    # ---------------- phase timers of the persistent kernel (device %globaltimer, thread 0)
+    phases = None
+    if eng.counter('persistent_blocks') > 0 and world == 1:
+        eng.set_option('phase_timers', 1)
+        e0 = eng.counter('events')
+        eng.run(steps_per_bench_step)
+        eng.set_option('phase_timers', 0)
+        eng.fetch_spikes()
+        nw = max(1, eng.counter('phase_windows'))
+        pu, pp = eng.counter('phase_update_ns') / nw, eng.counter('phase_propagate_ns') / nw
+        ev_w = (eng.counter('events') - e0) / nw
+        win = eng.counter('window')
+        phases = {
+            'timing': 'in-kernel %globaltimer around the two phases of every window (one cooperative launch per bench step)',
+            'windows': nw, 'steps_per_window': win,
+            'update_phase_us': pu * 1e-3, 'propagate_phase_us': pp * 1e-3,
+            'of_which_barrier_wait_us': [eng.counter('phase_sync1_ns') / nw * 1e-3, eng.counter('phase_sync2_ns') / nw * 1e-3],
+            'update_gbs': BYTES_PER_NEURON_STEP * eng.counter('n_pad') * win / pu,
+            'propagate_gbs': BYTES_PER_EVENT * ev_w / pp, 'events_per_window': ev_w,
+            'resident_state': bool(eng.counter('persistent_resident')),
+        }
+
     # ---------------- profiled pass: per-launch CUDA events around both kernels
     prof_steps = min(steps_per_bench_step, 800)
     eng.set_option('profile', 1)
@@ -290,7 +312,8 @@ def main():
     dom = 'glif_update' if up_ns >= pr_ns else 'propagate'
     roofline = {'kernel': dom, 'bound': 'hbm', 'achieved': kernels[dom]['achieved_gbs'], 'peak': peak, 'unit': 'GB/s',
                 'frac': kernels[dom]['achieved_gbs'] / peak, 'traffic': kernels[dom]['traffic'], 'peak_kind': peak_kind,
-                'kernels': kernels}
+                'timing': 'CUDA events around every launch of the per-step kernels (engine option profile)',
+                'kernels': kernels, 'persistent_phases': phases}
     window = eng.counter('window')
     eng.close()
 

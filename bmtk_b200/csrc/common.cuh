@@ -56,6 +56,7 @@ struct Ctl {
     uint32_t pad0, pad1;
     // persistent kernel, option "profile": device-timer totals of the two phases of every window
     unsigned long long t_update_ns, t_prop_ns, n_windows;
+    unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
 };
 
 // Neuron state, structure of arrays; every array has n_pad entries (multiple of 4, 16-byte aligned).

@@ -304,7 +304,7 @@ struct bmtk_engine {
     uint32_t* d_ce_group_ptr = nullptr;
     std::vector<uint64_t> ce_group_step;
     size_t ce_group_next = 0;
-    double phase_update_ns = 0, phase_prop_ns = 0;
+    double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
     uint64_t phase_windows = 0;
 
     DetWorkspace det{};
@@ -538,7 +538,9 @@ static int drain(bmtk_engine* e) {
         e->phase_update_ns += (double)h.t_update_ns;
         e->phase_prop_ns += (double)h.t_prop_ns;
         e->phase_windows += h.n_windows;
-        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 24, e->stream));
+        e->phase_sync1_ns += (double)h.t_sync1_ns;
+        e->phase_sync2_ns += (double)h.t_sync2_ns;
+        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 40, e->stream));
     }
     if (h.step_base != e->step)
         return fail(BMTK_E_INVALID, "device clock %llu differs from host clock %llu", (unsigned long long)h.step_base,
@@ -1365,6 +1367,8 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "phase_update_ns") *out = (uint64_t)e->phase_update_ns;
     else if (k == "phase_propagate_ns") *out = (uint64_t)e->phase_prop_ns;
     else if (k == "phase_windows") *out = e->phase_windows;
+    else if (k == "phase_sync1_ns") *out = (uint64_t)e->phase_sync1_ns;
+    else if (k == "phase_sync2_ns") *out = (uint64_t)e->phase_sync2_ns;
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;

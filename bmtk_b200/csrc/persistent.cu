@@ -238,6 +238,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
         ++s_in_win;
         if (s_in_win == a.window || s + 1 == a.n_steps) {
+            const unsigned long long t0b = timer ? gtimer() : 0ull;
             grid.sync();
             const unsigned long long t1 = timer ? gtimer() : 0ull;
             if (gtid == 0) {
@@ -246,11 +247,14 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
                 if (a.poisson_thr) a.virts[(win + 1) & 1][0] = 0u;
             }
             deliver_window(a, list, virt, win_base, s_in_win);
+            const unsigned long long t1b = timer ? gtimer() : 0ull;
             grid.sync();
             if (timer) {
                 const unsigned long long t2 = gtimer();
                 a.ctl->t_update_ns += t1 - t0;
                 a.ctl->t_prop_ns += t2 - t1;
+                a.ctl->t_sync1_ns += t1 - t0b;
+                a.ctl->t_sync2_ns += t2 - t1b;
                 a.ctl->n_windows += 1ull;
                 t0 = t2;
             }
