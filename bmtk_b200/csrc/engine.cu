@@ -1133,7 +1133,10 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         const size_t smem = persistent_smem((int)nt);
         const int blocks = persistent_max_blocks(e->device, e->has_theta, e->has_iext, true, smem);
         e->persist_blocks = blocks;
-        e->persist_resident = blocks > 0 && (uint64_t)(e->n_pad / 4) <= (uint64_t)blocks * persistent_threads_per_block();
+        if (blocks > 0) {
+            const uint64_t gpb = (((uint64_t)(e->n_pad / 4) + blocks - 1) / blocks + 31) / 32 * 32;
+            e->persist_resident = gpb <= persistent_threads_per_block();
+        }
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
         if (!coop) e->persist_blocks = 0;

@@ -156,16 +156,23 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
     const uint32_t sample_base = __ldcg(&a.ctl->sample_base);
     const bool timer = a.profile && gtid == 0;
 
+    // Groups of four neurons are dealt out evenly: block b owns groups [b*gpb, (b+1)*gpb), thread t of
+    // the block the t-th of them (and, when gpb > kPT, every kPT-th after it). gpb is a multiple of 32
+    // so that a warp is either all neurons or all idle; idle threads take the Poisson cells first.
+    const uint32_t gpb = ((n_groups + gridDim.x - 1) / gridDim.x + 31u) & ~31u;
+    const uint32_t my_group = blockIdx.x * gpb + threadIdx.x;
     Neuron4<THETA, IEXT> nr;
     int pslot[4] = {-1, -1, -1, -1};
-    const bool mine = gtid < n_groups;
+    const bool mine = threadIdx.x < gpb && my_group < n_groups;
     if (RESIDENT && mine) {
-        nr.load(a.st, a.n_pad, gtid * kNeuronsPerThread);
+        nr.load(a.st, a.n_pad, my_group * kNeuronsPerThread);
         if (a.probe_slot) {
-            const int4 q = *reinterpret_cast<const int4*>(a.probe_slot + gtid * kNeuronsPerThread);
+            const int4 q = *reinterpret_cast<const int4*>(a.probe_slot + my_group * kNeuronsPerThread);
             pslot[0] = q.x; pslot[1] = q.y; pslot[2] = q.z; pslot[3] = q.w;
         }
     }
+    // Poisson cells are numbered from the last thread of every block downwards
+    const uint32_t ptid = (kPT - 1 - threadIdx.x) * gridDim.x + blockIdx.x;
 
     uint32_t cgi = a.ce_group_begin;       // next clamp group (distinct step with events)
     uint32_t win = 0, s_in_win = 0;
@@ -178,8 +185,11 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         uint32_t* virt = a.poisson_thr ? a.virts[win & 1] : nullptr;
 
         if (IEXT) {
-            // clamp changes effective from this step on; the branch is uniform over the grid
+            // Clamp changes effective from this step on; the branch is uniform over the grid. Warps may
+            // run a step ahead of their neighbours inside a window, so the change is fenced on both
+            // sides: nobody may still be reading i_ext for the previous step when it is applied.
             bool changed = false;
+            if (cgi < a.ce_group_end && a.ce_group_step[cgi] <= step) grid.sync();
             while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= step) {
                 const uint32_t b = a.ce_group_ptr[cgi], e = a.ce_group_ptr[cgi + 1];
                 for (uint32_t k = b + gtid; k < e; k += nthreads)
@@ -189,16 +199,16 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
             }
             if (changed) {
                 grid.sync();
-                if (RESIDENT && mine) nr.iex = ld4cg(a.st.i_ext + gtid * kNeuronsPerThread);
+                if (RESIDENT && mine) nr.iex = ld4cg(a.st.i_ext + my_group * kNeuronsPerThread);
             }
         }
 
         if (RESIDENT) {
-            do_group<THETA, IEXT>(a, types, nr, pslot, mine, gtid * kNeuronsPerThread, step, s_in_win, list, sample_base);
+            do_group<THETA, IEXT>(a, types, nr, pslot, mine, my_group * kNeuronsPerThread, step, s_in_win, list, sample_base);
         } else {
-            for (uint32_t base = 0; base < n_groups; base += nthreads) {
-                const uint32_t g = base + gtid;
-                const bool valid = g < n_groups;
+            for (uint32_t t0 = 0; t0 < gpb; t0 += kPT) {
+                const uint32_t g = blockIdx.x * gpb + t0 + threadIdx.x;
+                const bool valid = t0 + threadIdx.x < gpb && g < n_groups;
                 const uint32_t i0 = g * kNeuronsPerThread;
                 if (valid) {
                     nr.load(a.st, a.n_pad, i0);
@@ -215,7 +225,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
         if (virt) {
             for (uint32_t base = 0; base < a.n_virtual; base += nthreads) {
-                const uint32_t v = base + gtid;
+                const uint32_t v = base + ptid;
                 int k = 0;
                 if (v < a.n_virtual) {
                     const uint4 thr = a.poisson_thr[v];
@@ -264,7 +274,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         }
     }
 
-    if (RESIDENT && mine) nr.store(a.st, a.n_pad, gtid * kNeuronsPerThread);
+    if (RESIDENT && mine) nr.store(a.st, a.n_pad, my_group * kNeuronsPerThread);
     if (gtid == 0) a.ctl->step_base = step_base + a.n_steps;
 }
 
