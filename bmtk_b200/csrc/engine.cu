@@ -298,7 +298,9 @@ struct bmtk_engine {
     bool persistent = true, phase_timers = false;
     int persist_blocks = 0;
     bool persist_resident = false;
-    uint32_t *d_send2 = nullptr, *d_virt2 = nullptr;
+    uint32_t* d_virt2 = nullptr;
+    uint4* d_plists[2] = {nullptr, nullptr};
+    uint32_t* d_plist_counts = nullptr;
     int32_t* d_probe_slot = nullptr;
     unsigned long long* d_ce_group_step = nullptr;
     uint32_t* d_ce_group_ptr = nullptr;
@@ -567,7 +569,8 @@ static int drain(bmtk_engine* e) {
         const uint32_t f = h.error_flags;
         CU(cudaMemsetAsync(&e->d_ctl->error_flags, 0, 4, e->stream));
         if (f & kErrSpikeListFull)
-            return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank): raise option spike_capacity",
+            return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank; the persistent kernel also holds "
+                        "at most 4096 spikes per block and window): raise option spike_capacity or set persistent = 0",
                         e->send_cap);
         if (f & kErrVirtListFull)
             return fail(BMTK_E_OVERFLOW, "Poisson spike list full (capacity %u): raise option spike_capacity", e->virt_cap);
@@ -614,12 +617,14 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
     a.ctl = e->d_ctl;
-    a.lists[0] = e->d_send;
-    a.lists[1] = e->d_send2;
+    a.lists[0] = e->d_plists[0];
+    a.lists[1] = e->d_plists[1];
+    a.list_counts = e->d_plist_counts;
     a.send_cap = e->send_cap;
     a.log_stamp = e->record_spikes ? e->d_log_stamp : nullptr;
     a.log_id = e->d_log_id;
     a.log_cap = (uint32_t)e->log_cap;
+    CU(cudaMemsetAsync(e->d_plist_counts, 0, 8, e->stream));
     a.poisson_thr = e->has_poisson ? e->d_poisson_thr : nullptr;
     a.n_virtual = (uint32_t)e->n_virtual;
     a.seed = e->seed;
@@ -652,8 +657,6 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     ++e->launches;
     e->step += n;
     // lists are empty at rest, whichever path runs next
-    CU(cudaMemsetAsync(e->d_send, 0, 4, e->stream));
-    CU(cudaMemsetAsync(e->d_send2, 0, 4, e->stream));
     if (e->d_virt) CU(cudaMemsetAsync(e->d_virt, 0, 4, e->stream));
     if (e->d_virt2) CU(cudaMemsetAsync(e->d_virt2, 0, 4, e->stream));
     while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step) ++e->ce_group_next;
@@ -757,8 +760,8 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_log_stamp); cudaFree(e->d_log_id); cudaFree(e->d_poisson_thr);
     cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
     cudaFree(e->d_ce_target); cudaFree(e->d_ce_delta); cudaFree(e->d_probe_ids); cudaFree(e->d_trace);
-    cudaFree(e->d_send2); cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step);
-    cudaFree(e->d_ce_group_ptr);
+    cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step); cudaFree(e->d_ce_group_ptr);
+    cudaFree(e->d_plists[0]); cudaFree(e->d_plists[1]); cudaFree(e->d_plist_counts);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return BMTK_OK;
@@ -1102,8 +1105,6 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     }
     // persistent stepping: second spike lists, clamp groups, probe map, grid size
     if (e->n_ranks == 1) {
-        CU(cudaMalloc(&e->d_send2, 4 * seg));
-        CU(cudaMemset(e->d_send2, 0, 4 * seg));
         if (e->has_poisson) {
             CU(cudaMalloc(&e->d_virt2, 4 * ((size_t)e->virt_cap + 4)));
             CU(cudaMemset(e->d_virt2, 0, 4 * ((size_t)e->virt_cap + 4)));
@@ -1139,7 +1140,12 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         }
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
-        if (!coop) e->persist_blocks = 0;
+        if (!coop || blocks > 512) e->persist_blocks = 0;
+        if (e->persist_blocks > 0) {
+            for (int q = 0; q < 2; ++q) CU(cudaMalloc(&e->d_plists[q], sizeof(uint4) * (size_t)e->send_cap));
+            CU(cudaMalloc(&e->d_plist_counts, 8));
+            CU(cudaMemset(e->d_plist_counts, 0, 8));
+        }
     }
     if (e->deterministic) {
         cudaError_t ce = det_alloc(e->det, (uint32_t)e->event_cap,

@@ -40,10 +40,88 @@ __device__ __forceinline__ unsigned long long gtimer() {
     return t;
 }
 
+constexpr uint32_t kPend = 4096;   // spikes one block can hold for one window
+
+struct BlockShared {
+    uint32_t pend_count;           // spikes of the current window collected by this block
+    uint32_t base, lbase;          // where this block's spikes go in the global list / log
+    uint32_t pend[kPend];          // step_in_window << kSrcBits | global id
+};
+
+// Records the fired neurons of this thread in the block's shared-memory list (one shared-memory
+// atomic per warp, no global traffic, nothing to wait for).
+__device__ __forceinline__ void emit_block(const PersistArgs& a, BlockShared& sh, uint32_t mask, uint32_t ent0) {
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int n = __popc(mask);
+    int incl = n;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(full, incl, d);
+        if (lane >= d) incl += t;
+    }
+    uint32_t base = 0;
+    if (lane == 31) base = atomicAdd(&sh.pend_count, (uint32_t)incl);
+    base = __shfl_sync(full, base, 31);
+    uint32_t pos = base + (uint32_t)(incl - n);
+#pragma unroll
+    for (int j = 0; j < kNeuronsPerThread; ++j) {
+        if (mask >> j & 1u) {
+            if (pos < kPend) sh.pend[pos] = ent0 + j;
+            else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+            ++pos;
+        }
+    }
+}
+
+// End of a window: the block appends its collected spikes to the global window list (and the spike
+// log) with one atomic each, looks up the CSR row of every spiking source and prefetches the row
+// into L2 so that the delivery phase, one grid barrier later, finds it there.
+__device__ __forceinline__ unsigned long long flush_block(const PersistArgs& a, BlockShared& sh, uint32_t parity,
+                                                          unsigned long long win_base) {
+    __syncthreads();   // every warp of the block has finished the window's updates
+    const uint32_t n = min(sh.pend_count, kPend);
+    if (n == 0) return 0ull;   // uniform over the block
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        sh.base = atomicAdd(a.list_counts + parity, n);
+        if (a.log_stamp) sh.lbase = atomicAdd(&a.ctl->log_count, n);
+    }
+    // while those atomics are in flight: row extents and L2 prefetch, one pending spike per warp
+    for (uint32_t k = warp; k < n; k += kPT / 32) {
+        const uint32_t gid = sh.pend[k] & kSrcMask;
+        const unsigned long long rb = a.rowptr[gid], re = a.rowptr[gid + 1];
+        const char* row = reinterpret_cast<const char*>(a.entries + rb);
+        for (unsigned long long off = (unsigned long long)lane * 128ull; off < (re - rb) * 8ull; off += 32ull * 128ull)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
+    }
+    __syncthreads();   // base / lbase are known
+    for (uint32_t k = threadIdx.x; k < n; k += kPT) {
+        const uint32_t e = sh.pend[k];
+        const uint32_t gid = e & kSrcMask;
+        const unsigned long long rb = a.rowptr[gid], re = a.rowptr[gid + 1];   // L1 hits now
+        const uint32_t pos = sh.base + k;
+        if (pos < a.send_cap) a.lists[parity][pos] = make_uint4(e, (uint32_t)(re - rb), (uint32_t)rb, (uint32_t)(rb >> 32));
+        else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+        if (a.log_stamp) {
+            const uint32_t lpos = sh.lbase + k;
+            if (lpos < a.log_cap) {
+                a.log_stamp[lpos] = (uint32_t)(win_base + (e >> kSrcBits) + 1ull);
+                a.log_id[lpos] = gid;
+            } else {
+                atomicOr(&a.ctl->error_flags, kErrLogFull);
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) sh.pend_count = 0u;
+    return (unsigned long long)n;
+}
+
 template <bool THETA, bool IEXT>
-__device__ __forceinline__ void do_group(const PersistArgs& a, const TypeConsts* types, Neuron4<THETA, IEXT>& nr,
-                                         const int (&pslot)[4], bool valid, uint32_t i0, unsigned long long step,
-                                         uint32_t s_in_win, uint32_t* list, uint32_t sample_base) {
+__device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, const TypeConsts* types,
+                                         Neuron4<THETA, IEXT>& nr, const int (&pslot)[4], bool valid, uint32_t i0,
+                                         unsigned long long step, uint32_t s_in_win, uint32_t sample_base) {
     uint32_t mask = 0;
     if (valid) {
         const uint32_t np = a.n_pad;
@@ -66,16 +144,41 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, const TypeConsts*
             }
         }
     }
-    if (__any_sync(0xffffffffu, mask != 0))
-        emit_spikes(mask, (s_in_win << kSrcBits) | (a.lo + i0), a.lo + i0, (uint32_t)(step + 1), list, a.send_cap, a.ctl,
-                    a.log_stamp, a.log_id, a.log_cap);
+    if (__any_sync(0xffffffffu, mask != 0)) emit_block(a, sh, mask, (s_in_win << kSrcBits) | (a.lo + i0));
 }
 
-// Delivery of one window: items are the recurrent list, the replayed virtual spikes of the
-// window's steps and the on-line Poisson list; a group of kSub threads streams one row.
-__device__ __forceinline__ void deliver_window(const PersistArgs& a, const uint32_t* list, const uint32_t* virt,
+// Streams one CSR row [b, b+len) with a group of kSub threads into the ring.
+__device__ __forceinline__ void stream_row(const PersistArgs& a, unsigned long long b, unsigned long long en, uint32_t slot0,
+                                           uint32_t lane) {
+    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
+    const size_t plane = (size_t)a.n_pad;
+    unsigned long long k = b + lane;
+    for (; k + 3ull * kSub < en; k += 4ull * kSub) {
+        uint2 e[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) e[u] = __ldg(&a.entries[k + (unsigned long long)u * kSub]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            uint32_t slot = slot0 + (e[u].x >> (tb + 2));
+            if (slot >= a.ring_slots) slot -= a.ring_slots;
+            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
+                      __uint_as_float(e[u].y));
+        }
+    }
+    for (; k < en; k += kSub) {
+        const uint2 e = __ldg(&a.entries[k]);
+        uint32_t slot = slot0 + (e.x >> (tb + 2));
+        if (slot >= a.ring_slots) slot -= a.ring_slots;
+        atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+    }
+}
+
+// Delivery of one window: items are the window's spike list (entries carry their row extent), the
+// replayed virtual spikes of the window's steps and the on-line Poisson list; a group of kSub
+// threads streams one row.
+__device__ __forceinline__ void deliver_window(const PersistArgs& a, uint32_t parity, const uint32_t* virt,
                                                unsigned long long win_base, uint32_t win_len) {
-    const uint32_t n_rec = min(__ldcg(list), a.send_cap);
+    const uint32_t n_rec = min(__ldcg(a.list_counts + parity), a.send_cap);
     uint32_t n_in = 0, in_begin = 0;
     if (a.in_ptr) {
         unsigned long long lo = win_base > a.in_ptr_base ? win_base - a.in_ptr_base : 0ull;
@@ -90,45 +193,28 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, const uint3
     const uint32_t total = n_rec + n_in + n_virt;
     const uint32_t sub = threadIdx.x / kSub, lane = threadIdx.x % kSub;
     const uint32_t n_sub = gridDim.x * (kPT / kSub);
-    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
-    const size_t plane = (size_t)a.n_pad;
     unsigned long long events = 0ull;
     for (uint32_t idx = blockIdx.x * (kPT / kSub) + sub; idx < total; idx += n_sub) {
-        uint32_t src;
-        unsigned long long step;
         if (idx < n_rec) {
-            const uint32_t e = __ldcg(list + 1 + idx);
-            src = e & kSrcMask;
-            step = win_base + (e >> kSrcBits);
-        } else if (idx < n_rec + n_in) {
-            src = a.in_src[in_begin + idx - n_rec];
-            step = a.in_step[in_begin + idx - n_rec];
+            const uint4 e = __ldcg(a.lists[parity] + idx);
+            const unsigned long long b = ((unsigned long long)e.w << 32) | e.z;
+            const unsigned long long step = win_base + (e.x >> kSrcBits);
+            if (lane == 0) events += e.y;
+            stream_row(a, b, b + e.y, (uint32_t)(step % a.ring_slots), lane);
         } else {
-            const uint32_t e = __ldcg(virt + 1 + idx - n_rec - n_in);
-            src = e & kSrcMask;
-            step = win_base + (e >> kSrcBits);
-        }
-        const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
-        const uint32_t slot0 = (uint32_t)(step % a.ring_slots);
-        if (lane == 0) events += en - b;
-        unsigned long long k = b + lane;
-        for (; k + 3ull * kSub < en; k += 4ull * kSub) {
-            uint2 e[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) e[u] = __ldg(&a.entries[k + (unsigned long long)u * kSub]);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                uint32_t slot = slot0 + (e[u].x >> (tb + 2));
-                if (slot >= a.ring_slots) slot -= a.ring_slots;
-                atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
-                          __uint_as_float(e[u].y));
+            uint32_t src;
+            unsigned long long step;
+            if (idx < n_rec + n_in) {
+                src = a.in_src[in_begin + idx - n_rec];
+                step = a.in_step[in_begin + idx - n_rec];
+            } else {
+                const uint32_t e = __ldcg(virt + 1 + idx - n_rec - n_in);
+                src = e & kSrcMask;
+                step = win_base + (e >> kSrcBits);
             }
-        }
-        for (; k < en; k += kSub) {
-            const uint2 e = __ldg(&a.entries[k]);
-            uint32_t slot = slot0 + (e.x >> (tb + 2));
-            if (slot >= a.ring_slots) slot -= a.ring_slots;
-            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+            const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
+            if (lane == 0) events += en - b;
+            stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane);
         }
     }
     if (events) atomicAdd(&a.ctl->n_events, events);
@@ -137,8 +223,12 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, const uint3
 template <bool THETA, bool IEXT, bool RESIDENT>
 __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ BlockShared sh;
     cg::grid_group grid = cg::this_grid();
     TypeConsts* s_types = reinterpret_cast<TypeConsts*>(smem_raw);
+    if (threadIdx.x == 0) sh.pend_count = 0u;
+    unsigned long long my_spikes = 0ull;   // block total, kept by thread 0
+    __syncthreads();
     const bool use_smem = a.n_types <= kSmemTypesP;
     if (use_smem) {
         const int words = a.n_types * (int)(sizeof(TypeConsts) / 4);
@@ -181,7 +271,6 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
     for (uint32_t s = 0; s < a.n_steps; ++s) {
         const unsigned long long step = step_base + s;
-        uint32_t* list = a.lists[win & 1];
         uint32_t* virt = a.poisson_thr ? a.virts[win & 1] : nullptr;
 
         if (IEXT) {
@@ -204,7 +293,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         }
 
         if (RESIDENT) {
-            do_group<THETA, IEXT>(a, types, nr, pslot, mine, my_group * kNeuronsPerThread, step, s_in_win, list, sample_base);
+            do_group<THETA, IEXT>(a, sh, types, nr, pslot, mine, my_group * kNeuronsPerThread, step, s_in_win, sample_base);
         } else {
             for (uint32_t t0 = 0; t0 < gpb; t0 += kPT) {
                 const uint32_t g = blockIdx.x * gpb + t0 + threadIdx.x;
@@ -218,7 +307,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
                         pslot[0] = q.x; pslot[1] = q.y; pslot[2] = q.z; pslot[3] = q.w;
                     }
                 }
-                do_group<THETA, IEXT>(a, types, nr, pslot, valid, i0, step, s_in_win, list, sample_base);
+                do_group<THETA, IEXT>(a, sh, types, nr, pslot, valid, i0, step, s_in_win, sample_base);
                 if (valid) nr.store(a.st, a.n_pad, i0);
             }
         }
@@ -248,15 +337,16 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
         ++s_in_win;
         if (s_in_win == a.window || s + 1 == a.n_steps) {
+            my_spikes += flush_block(a, sh, win & 1, win_base);
             const unsigned long long t0b = timer ? gtimer() : 0ull;
             grid.sync();
             const unsigned long long t1 = timer ? gtimer() : 0ull;
+            // the other parity's lists were last read one window ago: clear them for the next window
             if (gtid == 0) {
-                // the other parity's lists were last read one window ago: clear them for the next window
-                a.lists[(win + 1) & 1][0] = 0u;
+                a.list_counts[(win + 1) & 1] = 0u;
                 if (a.poisson_thr) a.virts[(win + 1) & 1][0] = 0u;
             }
-            deliver_window(a, list, virt, win_base, s_in_win);
+            deliver_window(a, win & 1, virt, win_base, s_in_win);
             const unsigned long long t1b = timer ? gtimer() : 0ull;
             grid.sync();
             if (timer) {
@@ -276,6 +366,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
     if (RESIDENT && mine) nr.store(a.st, a.n_pad, my_group * kNeuronsPerThread);
     if (gtid == 0) a.ctl->step_base = step_base + a.n_steps;
+    if (threadIdx.x == 0 && my_spikes) atomicAdd(&a.ctl->n_spikes, my_spikes);
 }
 
 int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem) {

@@ -13,10 +13,13 @@ struct PersistArgs {
     float* ring;
     uint32_t ring_slots;
     Ctl* ctl;
-    // spike lists, double buffered by window parity: [0] = count, then entries
-    uint32_t* lists[2];
+    // Window spike lists, double buffered by window parity. An entry is {step_in_window << kSrcBits |
+    // source, row length, row begin lo, row begin hi}; list_counts[parity] is its fill. Blocks collect
+    // their spikes in shared memory and append them with one atomic per block per window.
+    uint4* lists[2];
+    uint32_t* list_counts;     // [2]
     uint32_t send_cap;
-    uint32_t* log_stamp;
+    uint32_t* log_stamp;       // spike log (nullptr = not recording), fill in ctl->log_count
     uint32_t* log_id;
     uint32_t log_cap;
     // on-line Poisson cells

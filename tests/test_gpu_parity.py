@@ -353,7 +353,7 @@ def test_empty_networks(cabi):
 def test_spike_list_overflow_is_reported_not_fatal(cabi):
     from bmtk_b200._cabi import EngineError
     net = W.c1(n=4096, t_stop_ms=300.0)
-    eng = W.build_engine(net, options=dict(spike_capacity=4, window=16))
+    eng = W.build_engine(net, options=dict(spike_capacity=4, window=16, persistent=0))
     with pytest.raises(EngineError) as ei:
         eng.run(net.n_steps)
     assert 'spike list full' in str(ei.value)
