@@ -26,20 +26,22 @@ enum : uint32_t {
 // Unused ports and disabled mechanisms are neutral values so the update is branch-free:
 // a port that does not exist has P11 = P21 = P31 = P32 = psc_init = 0; a type without
 // after-spike currents has asc_coeff = asc_amps = 0 and asc_decay = asc_refr = 1.
-struct TypeConsts {
-    float P33, P30;
+// Members are grouped in 16-byte blocks so that the shared-memory copy is read with 128-bit loads.
+struct __align__(16) TypeConsts {
     float P11[kPorts], P21[kPorts], P31[kPorts], P32[kPorts], psc_init[kPorts];
-    float asc_decay[2], asc_coeff[2], asc_refr[2], asc_amps[2];
-    float th_inf, v_reset, E_L;
-    float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction, reset_add;
-    float phi, abpara, theta_voltage_decay, inv_G;
-    float i_e, pad_f;
+    float asc_decay[2], asc_coeff[2];
+    float asc_refr[2], asc_amps[2];
+    float P33, P30, th_inf, i_e;
+    float v_reset, E_L, inv_G, pad_f;
+    float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction;
+    float reset_add, phi, abpara, theta_voltage_decay;
     int32_t n_ref;
     // bit0 spike-dependent threshold, bit1 adapting threshold, bit2 reset in the spike step
     // (iaf_psc_alpha), bit3 threshold test is >= (iaf_psc_alpha)
     int32_t flags;
+    int32_t pad_i[2];
 };
-static_assert(sizeof(TypeConsts) % 4 == 0, "TypeConsts is copied word-wise");
+static_assert(sizeof(TypeConsts) % 16 == 0, "TypeConsts is copied word-wise and read with 128-bit loads");
 
 // Device-resident control block: everything a replayed CUDA graph needs to find its place.
 struct Ctl {
