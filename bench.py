@@ -39,7 +39,10 @@ if ROOT not in sys.path:
 BYTES_PER_NEURON_STEP = 128.0
 BYTES_PER_EVENT = 16.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu (see profiles/); None until captured
-NCU_TRAFFIC_BYTES = {'glif_update': None, 'propagate': None, 'persistent': None}
+# per update step for the persistent kernel (profiles/persistent_kernel_c3_phases.md), per launch for the others
+# (profiles/glif_update_2M_neurons_ncu_full.md scaled to this network, profiles/propagate_atomic_c2like_100k_ncu_full.md
+# at 12.4 B per event)
+NCU_TRAFFIC_BYTES = {'glif_update': 102.8 * 230924, 'propagate': None, 'persistent_per_step': 5.97e6}
 
 
 def parse_args():
@@ -315,7 +318,8 @@ def main():
         ach = phases['update_gbs'] if dom_phase == 'update' else phases['propagate_gbs']
         roofline = {
             'kernel': 'persistent_kernel / %s phase' % dom_phase, 'bound': 'hbm', 'achieved': ach, 'peak': peak,
-            'unit': 'GB/s', 'frac': ach / peak, 'traffic': NCU_TRAFFIC_BYTES.get('persistent'), 'peak_kind': peak_kind,
+            'unit': 'GB/s', 'frac': ach / peak, 'traffic': NCU_TRAFFIC_BYTES['persistent_per_step'] * steps_per_bench_step, 'peak_kind': peak_kind,
+            'traffic_note': 'dram bytes of one persistent launch (= one bench step), ncu on a 100-step launch scaled by steps',
             'timing': phases['timing'],
             'note': 'algorithmic bytes = 128 B per neuron-step (update) / 16 B per event (delivery); the persistent '
                     'kernel keeps the 96 B of neuron state in registers, so only the 32 B of ring traffic per neuron-step '

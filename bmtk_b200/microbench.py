@@ -43,7 +43,7 @@ def main():
         net.clamp_step = net.clamp_step[:0]
         net.clamp_target = net.clamp_target[:0]
         net.clamp_delta = net.clamp_delta[:0]
-        eng = W.build_engine(net, record_spikes=False, record_vm=False, options=dict(use_graph=0, window=8))
+        eng = W.build_engine(net, record_spikes=False, record_vm=False, options=dict(use_graph=0, window=8, persistent=0))
     else:
         net = W.c2(n=a.neurons, in_degree=a.in_degree, input_weight=a.input_weight, n_virtual=64, w_scale=0.01)
         rng = np.random.default_rng(5)
@@ -52,7 +52,7 @@ def main():
         net.clamp_target = ids
         net.clamp_delta = rng.uniform(a.drive_pa * 0.6, a.drive_pa * 1.4, size=a.neurons).astype(np.float32)
         eng = W.build_engine(net, record_spikes=False, record_vm=False,
-                             options=dict(use_graph=0, spike_capacity=a.neurons * 2))
+                             options=dict(use_graph=0, persistent=0, spike_capacity=a.neurons * 2))
     eng.run(a.warmup)
     eng.set_option('profile', a.profile)
     e0, s0 = eng.counter('events'), eng.counter('spikes')
