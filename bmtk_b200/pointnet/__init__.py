@@ -12,4 +12,4 @@ from .pointsimulator import PointSimulator
 from .pyfunction_cache import (add_cell_model, add_cell_processor, add_synapse_model, add_weight_function,
                                cell_model, model_processing, synapse_model, synaptic_weight)
 from .spike_trains import PoissonSpikeGenerator, SpikeTrains
-from . import modules
+from . import io_tools, modules

@@ -1,0 +1,84 @@
+"""Full-size and mid-size workloads on the GPU, checked through properties that do not need the
+CPU oracle to simulate them: exact integer bookkeeping of synaptic events, CSR invariants,
+agreement of the deterministic and the atomic delivery, plus a reduced E/I network against the
+oracle."""
+import numpy as np
+import pytest
+
+from bmtk_b200 import workloads as W
+from netutil import oracle_from_network, rates_by_type
+
+pytestmark = pytest.mark.gpu
+
+
+def _first_divergence(st_a, id_a, st_b, id_b):
+    n = min(len(st_a), len(st_b))
+    neq = np.nonzero((st_a[:n] != st_b[:n]) | (id_a[:n] != id_b[:n]))[0]
+    if len(neq):
+        return int(min(st_a[neq[0]], st_b[neq[0]]))
+    return np.inf if len(st_a) == len(st_b) else int((st_a if len(st_a) > n else st_b)[n])
+
+
+def test_c3_full_size_bookkeeping_and_mode_agreement(cabi, oracle):
+    """The benchmark network itself (230 924 neurons, ~70 M synapses, Philox Poisson cells), 100 ms."""
+    net = W.c3()
+    n_steps = 400
+    n = net.n_neurons
+    assert n == 230924 and 69e6 < net.n_edges < 71.5e6
+    eng = W.build_engine(net, record_vm=False)
+    # CSR invariants against the edge list (integer work: exact)
+    rowptr, packed, weight = eng.csr()
+    info = eng.csr_info()
+    tb = info['target_bits']
+    rowptr = rowptr.astype(np.int64)
+    assert rowptr[0] == 0 and rowptr[-1] == net.n_edges and np.all(np.diff(rowptr) >= 0)
+    assert np.array_equal(np.diff(rowptr), np.bincount(net.src, minlength=n + net.n_virtual))
+    row_of = np.repeat(np.arange(n + net.n_virtual), np.diff(rowptr))
+    key = (row_of.astype(np.int64) << 32) | packed
+    assert np.all(np.diff(key) >= 0)                       # rows by source, entries by (delay, port, target)
+    assert np.array_equal(np.bincount(packed & ((1 << tb) - 1), minlength=n), np.bincount(net.trg, minlength=n))
+    assert np.array_equal(np.bincount(packed >> (tb + 2)), np.bincount(net.delay_steps))
+    assert float(weight.astype(np.float64).sum()) == pytest.approx(float(net.weight.astype(np.float64).sum()), rel=1e-12)
+    assert info['min_delay'] == 2 and info['max_delay'] == 16 and eng.counter('window') == 2
+    # atomic delivery (persistent kernel) and deterministic delivery (per-step kernels)
+    eng.run(n_steps)
+    st, ids = eng.fetch_spikes()
+    det = W.build_engine(net, record_vm=False, deterministic=True)
+    det.run(n_steps)
+    st_d, ids_d = det.fetch_spikes()
+    assert len(st) > 50000
+    div = _first_divergence(st.astype(np.int64), ids.astype(np.int64), st_d.astype(np.int64), ids_d.astype(np.int64))
+    assert div > 100                                       # identical spikes until fp32 summation order matters
+    assert abs(len(st) - len(st_d)) <= 0.01 * len(st_d)
+    ra, rd = rates_by_type(net, ids, 100.0), rates_by_type(net, ids_d, 100.0)
+    assert np.all(np.abs(ra - rd) <= 0.02 * rd + 0.2)
+    # events delivered = sum of the row lengths of every spike emitted (neurons and Poisson cells)
+    steps, srcs = oracle.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, n_steps)
+    outdeg = np.diff(rowptr)
+    for e, i in ((eng, ids), (det, ids_d)):
+        assert e.counter('input_spikes') == len(steps)
+        assert e.counter('events') == int(outdeg[i].sum() + outdeg[n + srcs].sum())
+        assert e.counter('spikes') == len(i)
+
+
+@pytest.mark.parametrize('deterministic', [True, False])
+def test_c2_reduced_against_oracle(cabi, deterministic):
+    """The mid-scale E/I configuration at 1/10 size (5000 neurons, in-degree 200, 4 ports, delays
+    0.8-3.0 ms -> window 8) for 400 ms against the fp64 oracle."""
+    net = W.c2(n=5000, in_degree=200, n_virtual=200, t_stop_ms=400.0, input_weight=90.0)
+    eng = W.build_engine(net, deterministic=deterministic)
+    assert eng.counter('window') == 8
+    eng.run(net.n_steps)
+    st, ids = eng.fetch_spikes()
+    st, ids = st.astype(np.int64), ids.astype(np.int64)
+    r = oracle_from_network(net).run(net.n_steps)
+    assert r['n_spikes'] > 2000
+    div = _first_divergence(st, ids, r['spike_step'], r['spike_id'])
+    assert div > 300
+    m_g, m_c = st <= 1000, r['spike_step'] <= 1000
+    a = sorted(zip(ids[m_g].tolist(), st[m_g].tolist()))
+    b = sorted(zip(r['spike_id'][m_c].tolist(), r['spike_step'][m_c].tolist()))
+    assert len(a) == len(b)
+    assert all(x[0] == y[0] and abs(x[1] - y[1]) <= 1 for x, y in zip(a, b))
+    rg, rc = rates_by_type(net, ids, 400.0), rates_by_type(net, r['spike_id'], 400.0)
+    assert np.all(np.abs(rg - rc) <= 0.02 * rc + 0.15), (rg, rc)
