@@ -47,6 +47,27 @@ __global__ void fill_u64_kernel(unsigned long long* p, uint64_t n, unsigned long
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
 }
 
+__global__ void pack_log_kernel(uint32_t n, const uint32_t* stamp, const uint32_t* id, unsigned long long* keys) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) keys[i] = ((unsigned long long)stamp[i] << 32) | id[i];
+}
+
+size_t spike_log_sort_tmp_bytes(uint32_t capacity) {
+    size_t bytes = 0;
+    cub::DeviceRadixSort::SortKeys(nullptr, bytes, (unsigned long long*)nullptr, (unsigned long long*)nullptr,
+                                   (int)capacity);
+    return bytes + 16;
+}
+
+cudaError_t sort_spike_log(uint32_t n, const uint32_t* d_stamp, const uint32_t* d_id, unsigned long long* d_keys,
+                           unsigned long long* d_keys_out, void* tmp, size_t tmp_bytes, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    pack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_stamp, d_id, d_keys);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return cub::DeviceRadixSort::SortKeys(tmp, tmp_bytes, d_keys, d_keys_out, (int)n, 0, 64, stream);
+}
+
 #define CSR_CHECK(x)                      \
     do {                                  \
         cudaError_t e_ = (x);             \

@@ -230,7 +230,7 @@ struct bmtk_engine {
     // options
     bool deterministic = false, use_graph = true, record_spikes = false, profile = false;
     uint32_t window_opt = 0, window = 1;
-    uint64_t spike_cap_opt = 0, log_cap = 1u << 24, event_cap = 1u << 22, chunk_steps = 4096;
+    uint64_t spike_cap_opt = 0, log_cap = 1u << 23, event_cap = 1u << 22, chunk_steps = 4096;
     uint32_t send_cap = 0, virt_cap = 0;
 
     // comm
@@ -256,7 +256,8 @@ struct bmtk_engine {
     uint32_t *d_in_ptr = nullptr, *d_in_step = nullptr, *d_in_src = nullptr;
     uint64_t in_ptr_base = 0;
     uint32_t in_ptr_len = 0;
-    std::vector<uint32_t> pending_in_virt, pending_in_stamp;
+    std::vector<uint32_t> pending_in_virt, pending_in_stamp, h_in_ptr, h_in_step, h_in_src;
+    size_t in_cap = 0, in_ptr_cap = 0;
     bool has_pending_inputs = false;
 
     // clamps
@@ -278,8 +279,13 @@ struct bmtk_engine {
     uint64_t samples_drained = 0;
     std::vector<float> h_trace;
 
-    // host stores
-    std::vector<uint32_t> h_spk_stamp, h_spk_id;
+    // host store of recorded spikes: keys stamp << 32 | id, sorted (every drain appends a later, sorted run)
+    std::vector<unsigned long long> h_spk_keys;
+    unsigned long long *d_log_keys = nullptr, *d_log_keys2 = nullptr;
+    void* d_log_tmp = nullptr;
+    size_t log_tmp_bytes = 0;
+    unsigned long long* h_pinned_keys = nullptr;   // pinned staging for the device-to-host copy
+    size_t h_pinned_cap = 0;
     uint64_t step = 0;
     uint64_t launches = 0;
     uint64_t events_total = 0, spikes_total = 0, input_spikes_total = 0;
@@ -488,40 +494,64 @@ static int upload_inputs(bmtk_engine* e) {
     e->has_pending_inputs = false;
     drop_graph(e);
     const size_t n_in = e->pending_in_virt.size();
-    std::vector<std::pair<uint32_t, uint32_t>> ev;  // (emit step, source row)
-    ev.reserve(n_in);
+    // keep stamps > current step; counting sort by emitting step (= stamp - 1) gives the pointer table
+    const uint64_t base = e->step;
+    uint64_t last = 0;
+    size_t n_keep = 0;
     for (size_t i = 0; i < n_in; ++i) {
         const uint64_t stamp = e->pending_in_stamp[i];
-        if (stamp <= e->step) continue;  // already in the past
-        ev.emplace_back((uint32_t)(stamp - 1), (uint32_t)(e->n_global + e->pending_in_virt[i]));
+        if (stamp <= base) continue;
+        ++n_keep;
+        if (stamp - 1 > last) last = stamp - 1;
     }
-    std::sort(ev.begin(), ev.end());
-    e->pending_in_virt.clear();
-    e->pending_in_stamp.clear();
-    cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
-    e->d_in_ptr = e->d_in_step = e->d_in_src = nullptr;
     e->in_ptr_len = 0;
-    if (ev.empty()) return BMTK_OK;
-    const uint64_t base = e->step;
-    const uint64_t last = ev.back().first;
+    if (n_keep == 0) {
+        e->pending_in_virt.clear();
+        e->pending_in_stamp.clear();
+        cudaFree(e->d_in_ptr); cudaFree(e->d_in_step); cudaFree(e->d_in_src);
+        e->d_in_ptr = e->d_in_step = e->d_in_src = nullptr;
+        e->in_cap = e->in_ptr_cap = 0;
+        return BMTK_OK;
+    }
     const uint64_t len = last - base + 2;  // entries for steps base..last, plus the end
     if (len > (1ull << 31)) return fail(BMTK_E_INVALID, "input spikes span too many steps");
-    std::vector<uint32_t> ptr(len), st(ev.size()), sr(ev.size());
-    size_t k = 0;
-    for (uint64_t i = 0; i < len; ++i) {
-        while (k < ev.size() && ev[k].first < base + i) ++k;
-        ptr[i] = (uint32_t)k;
+    std::vector<uint32_t>& ptr = e->h_in_ptr;
+    ptr.assign(len, 0u);
+    for (size_t i = 0; i < n_in; ++i) {
+        const uint64_t stamp = e->pending_in_stamp[i];
+        if (stamp > base) ++ptr[stamp - 1 - base + 1];
     }
-    for (size_t i = 0; i < ev.size(); ++i) {
-        st[i] = ev[i].first;
-        sr[i] = ev[i].second;
+    for (uint64_t i = 1; i < len; ++i) ptr[i] += ptr[i - 1];
+    std::vector<uint32_t>& st = e->h_in_step;
+    std::vector<uint32_t>& sr = e->h_in_src;
+    st.resize(n_keep);
+    sr.resize(n_keep);
+    std::vector<uint32_t> fill(ptr.begin(), ptr.end() - 1);
+    for (size_t i = 0; i < n_in; ++i) {
+        const uint64_t stamp = e->pending_in_stamp[i];
+        if (stamp <= base) continue;
+        const uint32_t pos = fill[stamp - 1 - base]++;
+        st[pos] = (uint32_t)(stamp - 1);
+        sr[pos] = (uint32_t)(e->n_global + e->pending_in_virt[i]);
     }
-    CU(cudaMalloc(&e->d_in_ptr, 4 * len));
-    CU(cudaMalloc(&e->d_in_step, 4 * ev.size()));
-    CU(cudaMalloc(&e->d_in_src, 4 * ev.size()));
+    e->pending_in_virt.clear();
+    e->pending_in_stamp.clear();
+    if (len > e->in_ptr_cap) {
+        cudaFree(e->d_in_ptr);
+        e->d_in_ptr = nullptr;
+        e->in_ptr_cap = len + len / 2;
+        CU(cudaMalloc(&e->d_in_ptr, 4 * e->in_ptr_cap));
+    }
+    if (n_keep > e->in_cap) {
+        cudaFree(e->d_in_step); cudaFree(e->d_in_src);
+        e->d_in_step = e->d_in_src = nullptr;
+        e->in_cap = n_keep + n_keep / 2;
+        CU(cudaMalloc(&e->d_in_step, 4 * e->in_cap));
+        CU(cudaMalloc(&e->d_in_src, 4 * e->in_cap));
+    }
     CU(cudaMemcpyAsync(e->d_in_ptr, ptr.data(), 4 * len, cudaMemcpyHostToDevice, e->stream));
-    CU(cudaMemcpyAsync(e->d_in_step, st.data(), 4 * ev.size(), cudaMemcpyHostToDevice, e->stream));
-    CU(cudaMemcpyAsync(e->d_in_src, sr.data(), 4 * ev.size(), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_in_step, st.data(), 4 * n_keep, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_in_src, sr.data(), 4 * n_keep, cudaMemcpyHostToDevice, e->stream));
     CU(cudaStreamSynchronize(e->stream));
     e->in_ptr_base = base;
     e->in_ptr_len = (uint32_t)len;
@@ -580,13 +610,23 @@ static int drain(bmtk_engine* e) {
         return fail(BMTK_E_OVERFLOW, "device buffer overflow (flags %u)", f);
     }
     if (e->record_spikes && h.log_count) {
-        const size_t n0 = e->h_spk_stamp.size(), n = h.log_count;
-        e->h_spk_stamp.resize(n0 + n);
-        e->h_spk_id.resize(n0 + n);
-        CU(cudaMemcpyAsync(e->h_spk_stamp.data() + n0, e->d_log_stamp, 4 * n, cudaMemcpyDeviceToHost, e->stream));
-        CU(cudaMemcpyAsync(e->h_spk_id.data() + n0, e->d_log_id, 4 * n, cudaMemcpyDeviceToHost, e->stream));
+        // sort the chunk's spikes by (stamp, id) on the device; chunks are consecutive in time, so the
+        // host store stays sorted by appending
+        const size_t n0 = e->h_spk_keys.size(), n = h.log_count;
+        CU(sort_spike_log((uint32_t)n, e->d_log_stamp, e->d_log_id, e->d_log_keys, e->d_log_keys2, e->d_log_tmp,
+                          e->log_tmp_bytes, e->stream));
+        e->launches += 2;
+        if (e->h_pinned_cap < n) {
+            if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
+            e->h_pinned_keys = nullptr;
+            e->h_pinned_cap = std::max<size_t>(n * 2, 1u << 16);
+            CU(cudaMallocHost(&e->h_pinned_keys, 8 * e->h_pinned_cap));
+        }
+        CU(cudaMemcpyAsync(e->h_pinned_keys, e->d_log_keys2, 8 * n, cudaMemcpyDeviceToHost, e->stream));
         CU(cudaMemsetAsync(&e->d_ctl->log_count, 0, 4, e->stream));
         CU(cudaStreamSynchronize(e->stream));
+        e->h_spk_keys.resize(n0 + n);
+        std::memcpy(e->h_spk_keys.data() + n0, e->h_pinned_keys, 8 * n);
     }
     if (!e->probe_ids.empty()) {
         const uint64_t have = e->step / e->probe_interval;
@@ -762,6 +802,8 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_ce_target); cudaFree(e->d_ce_delta); cudaFree(e->d_probe_ids); cudaFree(e->d_trace);
     cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step); cudaFree(e->d_ce_group_ptr);
     cudaFree(e->d_plists[0]); cudaFree(e->d_plists[1]); cudaFree(e->d_plist_counts);
+    cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
+    if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return BMTK_OK;
@@ -1072,6 +1114,10 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         if (e->log_cap >= (1ull << 32)) return fail(BMTK_E_UNSUPPORTED, "log_capacity too large");
         CU(cudaMalloc(&e->d_log_stamp, 4 * e->log_cap));
         CU(cudaMalloc(&e->d_log_id, 4 * e->log_cap));
+        CU(cudaMalloc(&e->d_log_keys, 8 * e->log_cap));
+        CU(cudaMalloc(&e->d_log_keys2, 8 * e->log_cap));
+        e->log_tmp_bytes = spike_log_sort_tmp_bytes((uint32_t)e->log_cap);
+        CU(cudaMalloc(&e->d_log_tmp, e->log_tmp_bytes));
     }
     // clamps: sort by step
     if (e->has_iext) {
@@ -1166,27 +1212,23 @@ int bmtk_engine_run(bmtk_engine* e, uint64_t n_steps) {
 
 int bmtk_engine_spike_count(bmtk_engine* e, uint64_t* n) {
     if (!e || !n) return fail(BMTK_E_INVALID, "NULL argument");
-    *n = e->h_spk_stamp.size();
+    *n = e->h_spk_keys.size();
     return BMTK_OK;
 }
 
 int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step, uint32_t* id, uint64_t* n_out) {
     if (!e || !n_out) return fail(BMTK_E_INVALID, "NULL argument");
-    const size_t n = e->h_spk_stamp.size();
+    const size_t n = e->h_spk_keys.size();
     if (cap < n) return fail(BMTK_E_INVALID, "fetch_spikes: capacity %llu < %llu spikes", (unsigned long long)cap,
                              (unsigned long long)n);
     if (n && (!stamp_step || !id)) return fail(BMTK_E_INVALID, "fetch_spikes: NULL array");
-    // canonical order (stamp, id): the device appends in no particular order inside a step
-    std::vector<uint64_t> key(n);
-    for (size_t i = 0; i < n; ++i) key[i] = ((uint64_t)e->h_spk_stamp[i] << 32) | e->h_spk_id[i];
-    std::sort(key.begin(), key.end());
+    // already in canonical (stamp, id) order: sorted per chunk on the device, chunks consecutive in time
     for (size_t i = 0; i < n; ++i) {
-        stamp_step[i] = (uint32_t)(key[i] >> 32);
-        id[i] = (uint32_t)key[i];
+        stamp_step[i] = (uint32_t)(e->h_spk_keys[i] >> 32);
+        id[i] = (uint32_t)e->h_spk_keys[i];
     }
     *n_out = n;
-    e->h_spk_stamp.clear();
-    e->h_spk_id.clear();
+    e->h_spk_keys.clear();
     return BMTK_OK;
 }
 
