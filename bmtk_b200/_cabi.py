@@ -72,6 +72,9 @@ _SIGNATURES = {
     'bmtk_engine_get_counter': (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64)]),
     'bmtk_propagate_spikes': (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, _P, _P, _P, C.c_uint32, C.c_uint32, C.c_int, _P]),
     'bmtk_propagate_spikes_noalloc': (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, _P, _P, _P, C.c_uint32, C.c_uint32, _P]),
+    'bmtk_probe_scatter_reductions': (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_int, C.POINTER(C.c_double)]),
+    'bmtk_engine_save_state': (C.c_int, [_P, C.c_char_p]),
+    'bmtk_engine_load_state': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_mark': (C.c_int, [_P, C.c_int]),
     'bmtk_engine_elapsed_ms': (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),
 }

@@ -125,5 +125,6 @@ struct PropArgs {
 cudaError_t launch_glif_update(const UpdateArgs& a, bool has_theta, bool has_iext, cudaStream_t s);
 cudaError_t launch_propagate_atomic(const PropArgs& a, cudaStream_t s);
 int glif_update_blocks(uint32_t n_pad, uint32_t n_virtual);
+cudaError_t launch_scatter_red_probe(float* cells, uint32_t n_cells, unsigned long long n_ops, cudaStream_t s);
 
 }  // namespace bmtk

@@ -1379,6 +1379,130 @@ int bmtk_propagate_spikes(const uint64_t* d_rowptr, const void* d_entries, uint3
     return rc;
 }
 
+int bmtk_probe_scatter_reductions(int device, uint64_t n_cells, uint64_t n_ops, int repeats, double* ms_per_pass) {
+    if (!ms_per_pass || n_cells < 1 || n_cells >= (1ull << 32) || n_ops < 1 || repeats < 1)
+        return fail(BMTK_E_INVALID, "probe_scatter_reductions: bad argument");
+    CU(cudaSetDevice(device));
+    float* cells = nullptr;
+    CU(cudaMalloc(&cells, 4 * n_cells));
+    cudaEvent_t a = nullptr, b = nullptr;
+    int rc = BMTK_OK;
+    do {
+        if (cudaMemset(cells, 0, 4 * n_cells) != cudaSuccess || cudaEventCreate(&a) != cudaSuccess ||
+            cudaEventCreate(&b) != cudaSuccess) { rc = fail(BMTK_E_CUDA, "probe set-up failed"); break; }
+        launch_scatter_red_probe(cells, (uint32_t)n_cells, n_ops, 0);   // warm-up
+        cudaEventRecord(a, 0);
+        for (int r = 0; r < repeats; ++r) launch_scatter_red_probe(cells, (uint32_t)n_cells, n_ops, 0);
+        cudaEventRecord(b, 0);
+        if (cudaEventSynchronize(b) != cudaSuccess) { rc = fail(BMTK_E_CUDA, "probe failed: %s", cudaGetErrorString(cudaGetLastError())); break; }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, a, b);
+        *ms_per_pass = (double)ms / repeats;
+    } while (0);
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    cudaFree(cells);
+    return rc;
+}
+
+// ---- checkpoint / resume: the dynamic state is (step, neuron state arrays, ring buffer); Poisson
+// cells are counter based and need none.
+namespace {
+struct CkptHeader {
+    char magic[8];
+    uint64_t step, n_global, lo, n_local;
+    uint32_t n_pad, ring_slots, has_theta, has_iext;
+    double dt;
+};
+struct CkptArray {
+    void* dev;
+    size_t bytes;
+};
+std::vector<CkptArray> ckpt_arrays(bmtk_engine* e) {
+    const size_t np = e->n_pad;
+    std::vector<CkptArray> v = {
+        {e->st.U, 4 * np}, {e->st.asc0, 4 * np}, {e->st.asc1, 4 * np}, {e->st.y1, 4 * np * kPorts},
+        {e->st.y2, 4 * np * kPorts}, {e->st.refr, 4 * np}, {e->ring, 4 * (size_t)e->ring_slots * kPorts * np}};
+    if (e->has_theta) {
+        v.push_back({e->st.th_spike, 4 * np});
+        v.push_back({e->st.th_voltage, 4 * np});
+    }
+    if (e->has_iext) v.push_back({e->st.i_ext, 4 * np});
+    return v;
+}
+}  // namespace
+
+int bmtk_engine_save_state(bmtk_engine* e, const char* path) {
+    if (!e || !e->finalized || !path) return fail(BMTK_E_INVALID, "save_state: engine missing, not finalized, or NULL path");
+    int rc = set_device(e);
+    if (rc) return rc;
+    CU(cudaStreamSynchronize(e->stream));
+    FILE* f = std::fopen(path, "wb");
+    if (!f) return fail(BMTK_E_INVALID, "save_state: cannot open %s", path);
+    CkptHeader h{};
+    std::memcpy(h.magic, "BMTKB2C1", 8);
+    h.step = e->step; h.n_global = e->n_global; h.lo = e->lo; h.n_local = e->n_local;
+    h.n_pad = e->n_pad; h.ring_slots = e->ring_slots; h.has_theta = e->has_theta; h.has_iext = e->has_iext;
+    h.dt = e->dt;
+    bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1;
+    std::vector<char> buf;
+    for (const CkptArray& a : ckpt_arrays(e)) {
+        if (!ok) break;
+        buf.resize(a.bytes);
+        if (cudaMemcpy(buf.data(), a.dev, a.bytes, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = false; break; }
+        ok = std::fwrite(buf.data(), 1, a.bytes, f) == a.bytes;
+    }
+    std::fclose(f);
+    if (!ok) return fail(BMTK_E_CUDA, "save_state: writing %s failed", path);
+    return BMTK_OK;
+}
+
+int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
+    if (!e || !e->finalized || !path) return fail(BMTK_E_INVALID, "load_state: engine missing, not finalized, or NULL path");
+    int rc = set_device(e);
+    if (rc) return rc;
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return fail(BMTK_E_INVALID, "load_state: cannot open %s", path);
+    CkptHeader h{};
+    if (std::fread(&h, sizeof(h), 1, f) != 1 || std::memcmp(h.magic, "BMTKB2C1", 8) != 0) {
+        std::fclose(f);
+        return fail(BMTK_E_INVALID, "load_state: %s is not a bmtk_b200 checkpoint", path);
+    }
+    if (h.n_global != e->n_global || h.lo != e->lo || h.n_local != e->n_local || h.n_pad != e->n_pad ||
+        h.ring_slots != e->ring_slots || h.has_theta != (uint32_t)e->has_theta || h.has_iext != (uint32_t)e->has_iext ||
+        h.dt != e->dt) {
+        std::fclose(f);
+        return fail(BMTK_E_INVALID, "load_state: checkpoint was written for a different network, partition or dt");
+    }
+    CU(cudaStreamSynchronize(e->stream));
+    std::vector<char> buf;
+    bool ok = true;
+    for (const CkptArray& a : ckpt_arrays(e)) {
+        buf.resize(a.bytes);
+        if (std::fread(buf.data(), 1, a.bytes, f) != a.bytes) { ok = false; break; }
+        if (cudaMemcpy(a.dev, buf.data(), a.bytes, cudaMemcpyHostToDevice) != cudaSuccess) { ok = false; break; }
+    }
+    std::fclose(f);
+    if (!ok) return fail(BMTK_E_CUDA, "load_state: reading %s failed", path);
+    e->step = h.step;
+    const unsigned long long sb = h.step;
+    CU(cudaMemcpy(&e->d_ctl->step_base, &sb, 8, cudaMemcpyHostToDevice));
+    // cursors that follow from the step
+    e->ce_next = 0;
+    while (e->ce_next < e->ce_step.size() && e->ce_step[e->ce_next] < e->step) ++e->ce_next;
+    e->ce_group_next = 0;
+    while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step) ++e->ce_group_next;
+    if (!e->probe_ids.empty()) {
+        e->samples_drained = e->step / e->probe_interval;
+        const uint32_t s32 = (uint32_t)e->samples_drained;
+        CU(cudaMemcpy(&e->d_ctl->sample_base, &s32, 4, cudaMemcpyHostToDevice));
+    }
+    e->h_spk_keys.clear();
+    e->h_trace.clear();
+    // replayed inputs handed over before the load are re-indexed from the restored step
+    return BMTK_OK;
+}
+
 int bmtk_engine_mark(bmtk_engine* e, int slot) {
     if (!e || slot < 0 || slot >= 8) return fail(BMTK_E_INVALID, "mark: slot must be 0..7");
     int rc = set_device(e);

@@ -162,6 +162,23 @@ __global__ void __launch_bounds__(kPropThreads) propagate_atomic_kernel(const Pr
     }
 }
 
+// Ceiling probe for the delivery kernels: `n_ops` fp32 reductions into pseudo-random cells of a
+// buffer of `n_cells` floats, nothing else (the address comes from a multiplicative hash of the
+// thread's running index, no loads). What this sustains is the most any delivery scheme that ends
+// in one scattered reduction per synaptic event can reach on the device.
+__global__ void scatter_red_probe_kernel(float* cells, uint32_t n_cells, unsigned long long n_ops) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_ops; i += stride) {
+        const uint32_t h = (uint32_t)((i * 0x9E3779B97F4A7C15ull) >> 32);
+        atomicAdd(cells + (uint32_t)(((unsigned long long)h * n_cells) >> 32), 1.0f);
+    }
+}
+
+cudaError_t launch_scatter_red_probe(float* cells, uint32_t n_cells, unsigned long long n_ops, cudaStream_t s) {
+    scatter_red_probe_kernel<<<148 * 8, 256, 0, s>>>(cells, n_cells, n_ops);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_propagate_atomic(const PropArgs& a, cudaStream_t s) {
     if (a.n_seg > kMaxSeg) return cudaErrorInvalidValue;
     int dev = 0, sms = 148;

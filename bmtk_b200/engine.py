@@ -217,6 +217,14 @@ class Engine(object):
         check(self._lib.bmtk_engine_get_csr(self._h, _ptr(rowptr), _ptr(packed), _ptr(weight)))
         return rowptr, packed, weight
 
+    def save_state(self, path):
+        """Checkpoint: step counter, neuron state and ring buffer."""
+        check(self._lib.bmtk_engine_save_state(self._h, str(path).encode()))
+
+    def load_state(self, path):
+        """Resume from a checkpoint written for the same network, partition and dt."""
+        check(self._lib.bmtk_engine_load_state(self._h, str(path).encode()))
+
     def mark(self, slot):
         """Records a CUDA event on the engine's stream in slot 0..7."""
         check(self._lib.bmtk_engine_mark(self._h, int(slot)))
@@ -237,3 +245,11 @@ def nccl_unique_id(libnccl=None):
     buf = (C.c_char * 128)()
     check(_cabi.load().bmtk_comm_unique_id(buf, libnccl.encode() if libnccl else None))
     return bytes(buf)
+
+
+def scatter_reduction_rate(n_cells, n_ops, repeats=5, device=0):
+    """Reductions per second the device sustains for one fp32 `red` per op into random cells of a
+    buffer of n_cells floats (the ceiling of atomic spike delivery)."""
+    ms = C.c_double()
+    check(_cabi.load().bmtk_probe_scatter_reductions(int(device), int(n_cells), int(n_ops), int(repeats), C.byref(ms)))
+    return n_ops / (ms.value * 1e-3)

@@ -61,6 +61,11 @@ def main():
     ev, sp = eng.counter('events') - e0, eng.counter('spikes') - s0
     peak, kind = _peak()
     out = dict(kernel=a.kernel, neurons=a.neurons, steps=a.steps, events=ev, spikes=sp, peak_gbs=peak, peak_kind=kind)
+    if a.kernel == 'propagate':
+        from .engine import scatter_reduction_rate
+        cells = eng.csr_info()['ring_slots'] * 4 * eng.counter('n_pad')
+        out['scatter_red_ceiling_per_s'] = scatter_reduction_rate(cells, 8 * 1024 * 1024)
+        out['ring_cells'] = cells
     if a.profile:
         un, pn = max(1, eng.counter('update_launches')), max(1, eng.counter('propagate_launches'))
         ut, pt = eng.counter('update_ns') / un, eng.counter('propagate_ns') / pn
@@ -68,7 +73,10 @@ def main():
         pb = 16.0 * ev / pn
         out.update(update=dict(launches=un, avg_us=ut * 1e-3, bytes_per_launch=ub, gbs=ub / ut, frac=ub / ut / peak),
                    propagate=dict(launches=pn, avg_us=pt * 1e-3, bytes_per_launch=pb, gbs=pb / max(pt, 1e-9),
-                                  frac=pb / max(pt, 1e-9) / peak, events_per_launch=ev / pn))
+                                  frac=pb / max(pt, 1e-9) / peak, events_per_launch=ev / pn,
+                                  events_per_s=ev / pn / max(pt, 1e-9) * 1e9))
+        if 'scatter_red_ceiling_per_s' in out:
+            out['propagate']['frac_of_scatter_red_ceiling'] = out['propagate']['events_per_s'] / out['scatter_red_ceiling_per_s']
     print(json.dumps(out))
 
 

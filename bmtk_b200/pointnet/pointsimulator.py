@@ -222,14 +222,37 @@ class PointSimulator(object):
         io.barrier()
         self._build_engine()
         io.log_info('Starting Simulation')
+        import time
+        t0 = time.time()
         self._engine.run(self.n_steps)
         io.barrier()
+        wall = time.time() - t0
         io.log_info('Simulation finished, finalizing results.')
         self._collect()
         for mod in self._mods:
             mod.finalize(self)
+        self._write_metrics(wall)
         io.barrier()
         io.log_info('Done.')
+
+    def _write_metrics(self, wall_s):
+        """<output_dir>/metrics.json on rank 0: what ran and how fast (this rank's counters)."""
+        import json
+        eng = self._engine
+        m = {
+            'n_neurons': len(self._graph.gid_pool), 'n_virtual': self._graph.n_virtual, 'dt_ms': self._dt,
+            'n_steps': self.n_steps, 'sim_ms': self.n_steps * self._dt, 'wall_s': wall_s,
+            'sim_ms_per_wall_ms': self.n_steps * self._dt / max(wall_s * 1e3, 1e-9),
+            'ranks': io.mpi_size, 'rank_block': list(self._block),
+            'spikes': eng.counter('spikes'), 'synaptic_events': eng.counter('events'),
+            'events_per_s': eng.counter('events') / max(wall_s, 1e-9), 'kernel_launches': eng.counter('launches'),
+            'window_steps': eng.counter('window'), 'persistent_kernel': bool(eng.counter('persistent_blocks')) and
+            io.mpi_size == 1 and not self._engine_options.get('deterministic', 0),
+        }
+        self.metrics = m
+        if io.mpi_rank == 0 and os.path.isdir(self._output_dir):
+            with open(os.path.join(self._output_dir, 'metrics.json'), 'w') as f:
+                json.dump(m, f, indent=1)
 
     @classmethod
     def from_config(cls, configure, graph, n_thread=None):

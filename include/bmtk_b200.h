@@ -209,6 +209,20 @@ int bmtk_propagate_spikes_noalloc(const uint64_t* d_rowptr, const void* d_entrie
                                   uint32_t n_spikes, const uint32_t* d_spike_src, const uint32_t* d_spike_step,
                                   float* d_ring, uint32_t ring_slots, uint32_t n_pad, void* stream);
 
+/* Checkpoint / resume (the reference has none; its block_run keys are dead code,
+ * bmtk/simulator/pointnet/pointsimulator.py:118-132,215-218). save_state writes the step counter, the
+ * neuron state arrays and the ring buffer of this engine to a file; load_state restores them into an
+ * engine that was built and finalized from the same network, partition and dt. Recorder stores are
+ * emptied by a load; replayed input spikes must be handed over again after it. */
+int bmtk_engine_save_state(bmtk_engine* e, const char* path);
+int bmtk_engine_load_state(bmtk_engine* e, const char* path);
+
+/* Measures the device's rate of scattered fp32 reductions (no counterpart in the reference): n_ops
+ * `red.global.add.f32` into pseudo-random cells of a zeroed buffer of n_cells floats, `repeats` times,
+ * timed with CUDA events. This is the ceiling of any delivery that ends in one reduction per synaptic
+ * event; bench and microbench report the delivery kernels against it. */
+int bmtk_probe_scatter_reductions(int device, uint64_t n_cells, uint64_t n_ops, int repeats, double* ms_per_pass);
+
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
  * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
  * and returns the device time between two marks. */

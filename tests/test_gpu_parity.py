@@ -444,3 +444,37 @@ def test_iaf_psc_alpha_cells(cabi):
             neq = np.nonzero(a != b)[0]
             upto = (min(a[neq[0]], b[neq[0]]) - 1) if len(neq) else net.n_steps
             _trace_check(tr[:, q:q + 1], r['trace'][:, q:q + 1], upto)
+
+
+@pytest.mark.parametrize('deterministic', [True, False])
+def test_checkpoint_resume(cabi, tmp_path, deterministic):
+    """run(a); save; run(b)  ==  fresh engine; load; run(b): bit for bit in deterministic mode, and for
+    the atomic path up to the first divergence caused by summation order."""
+    net = W.c0(t_stop_ms=300.0, poisson_online=True)
+    a, b = 1234, 1766
+    e1 = W.build_engine(net, deterministic=deterministic)
+    e1.run(a)
+    e1.fetch_spikes(); e1.fetch_trace()
+    ck = str(tmp_path / 'state.ckpt')
+    e1.save_state(ck)
+    e1.run(b)
+    s1, i1 = e1.fetch_spikes()
+    t1 = e1.fetch_trace()
+    e2 = W.build_engine(net, deterministic=deterministic)
+    e2.load_state(ck)
+    assert e2.counter('steps') == a
+    e2.run(b)
+    s2, i2 = e2.fetch_spikes()
+    t2 = e2.fetch_trace()
+    assert len(s1) > 200 and s1.min() > a
+    if deterministic:
+        assert np.array_equal(s1, s2) and np.array_equal(i1, i2)
+        assert np.array_equal(t1.view(np.uint32), t2.view(np.uint32))
+        for var in ('U', 'asc0', 'y1_0', 'y2_3', 'refr'):
+            assert np.array_equal(e1.state(var).view(np.uint32), e2.state(var).view(np.uint32))
+    else:
+        div = _first_divergence(s1.astype(np.int64), i1.astype(np.int64), s2.astype(np.int64), i2.astype(np.int64))
+        assert div > a + 500
+    other = W.build_engine(W.c0(t_stop_ms=300.0, poisson_online=True, dt=0.2))
+    with pytest.raises(Exception):
+        other.load_state(ck)

@@ -304,3 +304,44 @@ def test_stock_example_network_expands_to_the_expected_edge_list():
     assert n_in == 3044
     # the two iaf_psc_alpha types became engine types with that model tag
     assert sum(t.get('model') == 'iaf_psc_alpha' for t in g.types) == 2
+
+
+def test_weight_function_is_called_per_edge_type(project, tmp_path):
+    """sonata_adaptors.py:319-335: a `weight_function` column replaces nsyns*syn_weight; the function
+    gets (edges, source nodes, target nodes) data frames of one edge type and returns one weight per edge."""
+    import shutil
+    net, info = project
+    root = tmp_path / 'proj'
+    shutil.copytree(os.path.dirname(info['config']), str(root))
+    tf = root / 'network' / 'v1_v1_edge_types.csv'
+    lines = tf.read_text().splitlines()
+    lines[0] += ' weight_function'
+    lines[1:] = [ln + (' scaled_by_target' if ln.startswith('100 ') else ' NONE') for ln in lines[1:]]
+    tf.write_text('\n'.join(lines) + '\n')
+    calls = []
+
+    @pointnet.synaptic_weight
+    def scaled_by_target(edges, src_nodes, trg_nodes):
+        calls.append((len(edges), len(src_nodes), len(trg_nodes), sorted(set(edges['edge_type_id']))))
+        assert list(trg_nodes['node_id'].values) == list(edges['target_node_id'].values)
+        return edges['syn_weight'].values * edges['nsyns'].values * np.where(trg_nodes['ei'].values == 'i', 2.0, 0.5)
+
+    conf = pointnet.Config.from_json(str(root / 'config.simulation.json'))
+    g = pointnet.PointNetwork.from_config(conf)
+    g.build()
+    assert len(calls) == 1 and calls[0][0] == calls[0][1] == calls[0][2] and calls[0][3] == [100]
+    g0 = pointnet.PointNetwork.from_config(pointnet.Config.from_json(info['config']))
+    g0.build()
+    b1 = [b for b in g.edge_batches if b['edge_type_id'] == 100][0]
+    b0 = [b for b in g0.edge_batches if b['edge_type_id'] == 100][0]
+    inh = np.array([t.get('V_th') is not None for t in g.types])   # placeholder to keep shapes explicit
+    node_ids, _ = g.gid_pool.get_node_ids(b1['trg'])
+    ei = g.get_node_population('v1').to_dataframe().loc[node_ids, 'ei'].values
+    assert np.allclose(b1['weight'], b0['weight'] * np.where(ei == 'i', 2.0, 0.5))
+    others1 = [b for b in g.edge_batches if b['edge_type_id'] != 100]
+    others0 = [b for b in g0.edge_batches if b['edge_type_id'] != 100]
+    assert all(np.array_equal(x['weight'], y['weight']) for x, y in zip(others1, others0))
+    with pytest.raises(Exception):
+        lines[1] = lines[1].replace('scaled_by_target', 'not_registered')
+        tf.write_text('\n'.join(lines) + '\n')
+        pointnet.PointNetwork.from_config(conf).build()
