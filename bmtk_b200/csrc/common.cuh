@@ -20,6 +20,7 @@ enum : uint32_t {
     kErrLogFull = 2u,
     kErrVirtListFull = 4u,
     kErrEventsFull = 8u,
+    kErrExchangeTimeout = 16u,
 };
 
 // Per node type constants for one resolution, fp32 copies of fp64 host values.

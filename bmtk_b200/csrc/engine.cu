@@ -307,6 +307,11 @@ struct bmtk_engine {
     uint32_t* d_virt2 = nullptr;
     uint4* d_plists[2] = {nullptr, nullptr};
     uint32_t* d_plist_counts = nullptr;
+    // spike exchange over peer memory (several ranks, persistent kernel)
+    uint32_t* d_xchg = nullptr;                 // this rank's exchange buffer
+    uint32_t* xchg_peers[kXRanks] = {};         // every rank's buffer as mapped here
+    bool p2p_ready = false;
+    uint32_t xchg_seq = 0;                      // windows exchanged so far
     int32_t* d_probe_slot = nullptr;
     unsigned long long* d_ce_group_step = nullptr;
     uint32_t* d_ce_group_ptr = nullptr;
@@ -602,6 +607,9 @@ static int drain(bmtk_engine* e) {
             return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank; the persistent kernel also holds "
                         "at most 4096 spikes per block and window): raise option spike_capacity or set persistent = 0",
                         e->send_cap);
+        if (f & kErrExchangeTimeout)
+            return fail(BMTK_E_COMM, "spike exchange timed out: a rank did not publish its window within ~1 s "
+                        "(rank %d of %d); the results of this run are invalid", e->rank, e->n_ranks);
         if (f & kErrVirtListFull)
             return fail(BMTK_E_OVERFLOW, "Poisson spike list full (capacity %u): raise option spike_capacity", e->virt_cap);
         if (f & kErrLogFull)
@@ -693,9 +701,15 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.trace = e->d_trace;
     a.trace_cap = e->trace_cap;
     a.profile = e->phase_timers ? 1u : 0u;
+    a.n_ranks = (uint32_t)e->n_ranks;
+    a.rank = (uint32_t)e->rank;
+    a.xchg_cap = e->send_cap;
+    a.seq0 = e->xchg_seq;
+    for (int r = 0; r < e->n_ranks; ++r) a.peers[r] = e->xchg_peers[r];
     CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
     ++e->launches;
     e->step += n;
+    e->xchg_seq += (n + e->window - 1) / e->window;
     // lists are empty at rest, whichever path runs next
     if (e->d_virt) CU(cudaMemsetAsync(e->d_virt, 0, 4, e->stream));
     if (e->d_virt2) CU(cudaMemsetAsync(e->d_virt2, 0, 4, e->stream));
@@ -716,8 +730,8 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
             chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(room - e->probe_interval + 1, 1));
         }
         uint64_t done = 0;
-        const bool use_persistent = e->persistent && e->n_ranks == 1 && !e->deterministic && !e->profile &&
-                                    e->persist_blocks > 0;
+        const bool use_persistent = e->persistent && (e->n_ranks == 1 || e->p2p_ready) && !e->deterministic &&
+                                    !e->profile && e->persist_blocks > 0;
         if (use_persistent) {
             rc = run_persistent_chunk(e, (uint32_t)chunk);
             if (rc) return rc;
@@ -802,6 +816,9 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_ce_target); cudaFree(e->d_ce_delta); cudaFree(e->d_probe_ids); cudaFree(e->d_trace);
     cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step); cudaFree(e->d_ce_group_ptr);
     cudaFree(e->d_plists[0]); cudaFree(e->d_plists[1]); cudaFree(e->d_plist_counts);
+    for (int r = 0; r < e->n_ranks && r < (int)kXRanks; ++r)
+        if (e->xchg_peers[r] && r != e->rank) cudaIpcCloseMemHandle(e->xchg_peers[r]);
+    cudaFree(e->d_xchg);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -1150,7 +1167,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         CU(cudaMalloc(&e->d_trace, 4 * n_ids * cap_s));
     }
     // persistent stepping: second spike lists, clamp groups, probe map, grid size
-    if (e->n_ranks == 1) {
+    {
         if (e->has_poisson) {
             CU(cudaMalloc(&e->d_virt2, 4 * ((size_t)e->virt_cap + 4)));
             CU(cudaMemset(e->d_virt2, 0, 4 * ((size_t)e->virt_cap + 4)));
@@ -1191,6 +1208,11 @@ int bmtk_engine_finalize(bmtk_engine* e) {
             for (int q = 0; q < 2; ++q) CU(cudaMalloc(&e->d_plists[q], sizeof(uint4) * (size_t)e->send_cap));
             CU(cudaMalloc(&e->d_plist_counts, 8));
             CU(cudaMemset(e->d_plist_counts, 0, 8));
+            if (e->n_ranks > 1) {
+                const size_t words = xchg_words((uint32_t)e->n_ranks, e->send_cap);
+                CU(cudaMalloc(&e->d_xchg, 4 * words));
+                CU(cudaMemset(e->d_xchg, 0, 4 * words));
+            }
         }
     }
     if (e->deterministic) {
@@ -1431,6 +1453,40 @@ std::vector<CkptArray> ckpt_arrays(bmtk_engine* e) {
     return v;
 }
 }  // namespace
+
+int bmtk_engine_p2p_handle(bmtk_engine* e, void* handle64) {
+    if (!e || !e->finalized || !handle64) return fail(BMTK_E_INVALID, "p2p_handle: engine missing, not finalized, or NULL");
+    if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_handle: no exchange buffer (one rank, or cooperative launch unavailable)");
+    int rc = set_device(e);
+    if (rc) return rc;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    CU(cudaIpcGetMemHandle(&h, e->d_xchg));
+    std::memcpy(handle64, &h, 64);
+    return BMTK_OK;
+}
+
+int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
+    if (!e || !e->finalized || !handles) return fail(BMTK_E_INVALID, "p2p_connect: engine missing, not finalized, or NULL");
+    if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_connect: no exchange buffer");
+    int rc = set_device(e);
+    if (rc) return rc;
+    for (int r = 0; r < e->n_ranks; ++r) {
+        if (r == e->rank) {
+            e->xchg_peers[r] = e->d_xchg;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, (const char*)handles + 64 * r, 64);
+        void* p = nullptr;
+        cudaError_t ce = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (ce != cudaSuccess)
+            return fail(BMTK_E_COMM, "p2p_connect: cannot map the exchange buffer of rank %d: %s", r, cudaGetErrorString(ce));
+        e->xchg_peers[r] = (uint32_t*)p;
+    }
+    e->p2p_ready = true;
+    return BMTK_OK;
+}
 
 int bmtk_engine_save_state(bmtk_engine* e, const char* path) {
     if (!e || !e->finalized || !path) return fail(BMTK_E_INVALID, "save_state: engine missing, not finalized, or NULL path");

@@ -147,6 +147,78 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, 
     if (__any_sync(0xffffffffu, mask != 0)) emit_block(a, sh, mask, (s_in_win << kSrcBits) | (a.lo + i0));
 }
 
+// ---- several ranks: the exchange is part of this kernel, over peer memory (NVLink / NVSwitch)
+
+__device__ __forceinline__ uint32_t* x_counts(uint32_t* x, uint32_t parity) { return x + kXRanks + parity * kXRanks; }
+__device__ __forceinline__ uint32_t* x_inbox(const PersistArgs& a, uint32_t* x, uint32_t parity, uint32_t src_rank) {
+    return x + 3 * kXRanks + ((size_t)parity * a.n_ranks + src_rank) * a.xchg_cap;
+}
+
+// End of a window with several ranks: the block reserves a range behind this rank's window counter
+// and stores its spikes (step_in_window << kSrcBits | global id) into inbox[parity][rank] of every
+// rank, its own included, with plain peer stores; then the spike log, locally.
+__device__ __forceinline__ unsigned long long flush_block_multi(const PersistArgs& a, BlockShared& sh, uint32_t parity,
+                                                                unsigned long long win_base) {
+    __syncthreads();
+    const uint32_t n = min(sh.pend_count, kPend);
+    if (n == 0) return 0ull;
+    if (threadIdx.x == 0) {
+        sh.base = atomicAdd(a.list_counts + parity, n);
+        if (a.log_stamp) sh.lbase = atomicAdd(&a.ctl->log_count, n);
+    }
+    __syncthreads();
+    for (uint32_t k = threadIdx.x; k < n; k += kPT) {
+        const uint32_t e = sh.pend[k];
+        const uint32_t pos = sh.base + k;
+        if (pos < a.xchg_cap) {
+            for (uint32_t r = 0; r < a.n_ranks; ++r) x_inbox(a, a.peers[r], parity, a.rank)[pos] = e;
+        } else {
+            atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+        }
+        if (a.log_stamp) {
+            const uint32_t lpos = sh.lbase + k;
+            if (lpos < a.log_cap) {
+                a.log_stamp[lpos] = (uint32_t)(win_base + (e >> kSrcBits) + 1ull);
+                a.log_id[lpos] = e & kSrcMask;
+            } else {
+                atomicOr(&a.ctl->error_flags, kErrLogFull);
+            }
+        }
+    }
+    __threadfence_system();   // the peer stores are ordered before whatever this thread signals later
+    __syncthreads();
+    if (threadIdx.x == 0) sh.pend_count = 0u;
+    return (unsigned long long)n;
+}
+
+// After the grid barrier that follows the flush: thread 0 publishes this rank's count and sequence
+// number to every rank; the first n_ranks threads of block 0 then wait (bounded) until every rank
+// has published the same window. On a time-out the sticky error bit is set and all later waits are
+// skipped, so the launch still ends; the host turns the bit into BMTK_E_COMM.
+__device__ __forceinline__ void publish_and_wait(const PersistArgs& a, uint32_t parity, uint32_t seq) {
+    if (blockIdx.x != 0) return;
+    if (threadIdx.x == 0) {
+        const uint32_t n = min(__ldcg(a.list_counts + parity), a.xchg_cap);
+        for (uint32_t r = 0; r < a.n_ranks; ++r) x_counts(a.peers[r], parity)[a.rank] = n;
+        __threadfence_system();
+        for (uint32_t r = 0; r < a.n_ranks; ++r) *reinterpret_cast<volatile uint32_t*>(a.peers[r] + a.rank) = seq;
+    }
+    if (threadIdx.x < a.n_ranks) {
+        volatile uint32_t* flag = reinterpret_cast<volatile uint32_t*>(a.peers[a.rank] + threadIdx.x);
+        if (!(__ldcg(&a.ctl->error_flags) & kErrExchangeTimeout)) {
+            unsigned int spins = 0;
+            while ((int)(*flag - seq) < 0) {
+                if (++spins > 4000000u) {   // ~1 s
+                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+        __threadfence_system();
+    }
+}
+
 // Streams one CSR row [b, b+len) with a group of kSub threads into the ring.
 __device__ __forceinline__ void stream_row(const PersistArgs& a, unsigned long long b, unsigned long long en, uint32_t slot0,
                                            uint32_t lane) {
@@ -216,6 +288,55 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, uint32_t pa
             if (lane == 0) events += en - b;
             stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane);
         }
+    }
+    if (events) atomicAdd(&a.ctl->n_events, events);
+}
+
+// Delivery with several ranks: the window's spikes of every rank sit in the local inbox; rows are
+// looked up in this rank's CSR (it holds a row for every source of the network).
+__device__ __forceinline__ void deliver_window_multi(const PersistArgs& a, uint32_t parity, const uint32_t* virt,
+                                                     unsigned long long win_base, uint32_t win_len) {
+    uint32_t* x = a.peers[a.rank];
+    uint32_t off[kXRanks + 1];
+    off[0] = 0;
+    for (uint32_t r = 0; r < a.n_ranks; ++r)
+        off[r + 1] = off[r] + min(*reinterpret_cast<volatile uint32_t*>(x_counts(x, parity) + r), a.xchg_cap);
+    const uint32_t n_rec = off[a.n_ranks];
+    uint32_t n_in = 0, in_begin = 0;
+    if (a.in_ptr) {
+        unsigned long long lo = win_base > a.in_ptr_base ? win_base - a.in_ptr_base : 0ull;
+        unsigned long long hi = win_base + win_len > a.in_ptr_base ? win_base + win_len - a.in_ptr_base : 0ull;
+        const unsigned long long last = a.in_ptr_len - 1;
+        if (lo > last) lo = last;
+        if (hi > last) hi = last;
+        in_begin = a.in_ptr[lo];
+        n_in = a.in_ptr[hi] - in_begin;
+    }
+    const uint32_t n_virt = virt ? min(__ldcg(virt), a.virt_cap) : 0u;
+    const uint32_t total = n_rec + n_in + n_virt;
+    const uint32_t sub = threadIdx.x / kSub, lane = threadIdx.x % kSub;
+    const uint32_t n_sub = gridDim.x * (kPT / kSub);
+    unsigned long long events = 0ull;
+    for (uint32_t idx = blockIdx.x * (kPT / kSub) + sub; idx < total; idx += n_sub) {
+        uint32_t src;
+        unsigned long long step;
+        if (idx < n_rec) {
+            uint32_t r = 0;
+            while (idx >= off[r + 1]) ++r;
+            const uint32_t e = __ldcv(x_inbox(a, x, parity, r) + (idx - off[r]));
+            src = e & kSrcMask;
+            step = win_base + (e >> kSrcBits);
+        } else if (idx < n_rec + n_in) {
+            src = a.in_src[in_begin + idx - n_rec];
+            step = a.in_step[in_begin + idx - n_rec];
+        } else {
+            const uint32_t e = __ldcg(virt + 1 + idx - n_rec - n_in);
+            src = e & kSrcMask;
+            step = win_base + (e >> kSrcBits);
+        }
+        const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
+        if (lane == 0) events += en - b;
+        stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane);
     }
     if (events) atomicAdd(&a.ctl->n_events, events);
 }
@@ -337,16 +458,24 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 
         ++s_in_win;
         if (s_in_win == a.window || s + 1 == a.n_steps) {
-            my_spikes += flush_block(a, sh, win & 1, win_base);
+            const bool multi = a.n_ranks > 1;
+            const uint32_t seq = a.seq0 + win + 1u;
+            const uint32_t par = multi ? (seq & 1u) : (win & 1u);
+            my_spikes += multi ? flush_block_multi(a, sh, par, win_base) : flush_block(a, sh, par, win_base);
             const unsigned long long t0b = timer ? gtimer() : 0ull;
             grid.sync();
+            if (multi) {
+                publish_and_wait(a, par, seq);
+                grid.sync();
+            }
             const unsigned long long t1 = timer ? gtimer() : 0ull;
             // the other parity's lists were last read one window ago: clear them for the next window
             if (gtid == 0) {
-                a.list_counts[(win + 1) & 1] = 0u;
+                a.list_counts[par ^ 1u] = 0u;
                 if (a.poisson_thr) a.virts[(win + 1) & 1][0] = 0u;
             }
-            deliver_window(a, win & 1, virt, win_base, s_in_win);
+            if (multi) deliver_window_multi(a, par, virt, win_base, s_in_win);
+            else deliver_window(a, par, virt, win_base, s_in_win);
             const unsigned long long t1b = timer ? gtimer() : 0ull;
             grid.sync();
             if (timer) {

@@ -3,6 +3,8 @@
 
 namespace bmtk {
 
+constexpr uint32_t kXRanks = 16;   // most ranks an exchange buffer is laid out for
+
 // Arguments of one persistent launch (a chunk of steps on one GPU).
 struct PersistArgs {
     // neurons
@@ -51,7 +53,18 @@ struct PersistArgs {
     float* trace;
     uint32_t trace_cap;
     uint32_t profile;
+    // Spike exchange between ranks over peer memory (n_ranks > 1). Every rank owns an exchange
+    // buffer of u32 words laid out as  flags[kXRanks] | counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
+    // peers[r] is rank r's buffer as mapped into this process (peers[rank] is the local one).
+    // Window `seq` uses parity seq & 1; rank r publishes its spikes of the window into
+    // inbox[parity][r] of EVERY rank, then counts[parity][r], then flags[r] = seq.
+    uint32_t n_ranks, rank;
+    uint32_t* peers[kXRanks];
+    uint32_t xchg_cap;
+    uint32_t seq0;             // windows completed before this launch
 };
+
+constexpr uint32_t xchg_words(uint32_t n_ranks, uint32_t cap) { return kXRanks + 2 * kXRanks + 2 * n_ranks * cap; }
 
 const void* persistent_kernel_ptr(bool has_theta, bool has_iext, bool resident);
 int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem);

@@ -172,6 +172,27 @@ class Engine(object):
     def finalize(self):
         check(self._lib.bmtk_engine_finalize(self._h))
 
+    def p2p_handle(self):
+        """64-byte handle of this rank's spike-exchange buffer (after finalize, several ranks)."""
+        buf = (C.c_char * 64)()
+        check(self._lib.bmtk_engine_p2p_handle(self._h, buf))
+        return bytes(buf)
+
+    def p2p_connect(self, handles):
+        """Maps the exchange buffers of all ranks (list of 64-byte handles in rank order): the stepping
+        kernel then exchanges spikes over peer memory instead of NCCL."""
+        blob = b''.join(bytes(h) for h in handles)
+        buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+        check(self._lib.bmtk_engine_p2p_connect(self._h, buf))
+
+    def connect_peers(self):
+        """Exchanges the handles over torch.distributed (any backend) and connects."""
+        import torch.distributed as dist
+        handles = [None] * dist.get_world_size()
+        dist.all_gather_object(handles, self.p2p_handle())
+        self.p2p_connect(handles)
+        dist.barrier()
+
     # ---- simulation
     def run(self, n_steps):
         check(self._lib.bmtk_engine_run(self._h, int(n_steps)))

@@ -372,7 +372,7 @@ def c3(n=230924, mean_in_degree=330.0, t_stop_ms=1000.0, dt=0.25, seed=1237, n_v
 
 
 def build_engine(net, device=0, deterministic=False, record_spikes=True, record_vm=True, options=None,
-                 rank=0, n_ranks=1, nccl_uid=None, libnccl=None):
+                 rank=0, n_ranks=1, nccl_uid=None, libnccl=None, p2p=False):
     """Creates and finalizes an Engine for `net` (whose edges must cover [net.lo, net.hi))."""
     from .engine import Engine
     e = Engine(net.dt, device=device)
@@ -396,4 +396,6 @@ def build_engine(net, device=0, deterministic=False, record_spikes=True, record_
     if n_ranks > 1:
         e.comm_init(nccl_uid, rank, n_ranks, libnccl)
     e.finalize()
+    if n_ranks > 1 and p2p and not deterministic:
+        e.connect_peers()       # spike exchange over peer memory inside the persistent kernel
     return e

@@ -144,6 +144,17 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
 int bmtk_comm_unique_id(void* uid128, const char* libnccl);
 int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ranks, const char* libnccl);
 
+/* Spike exchange inside the stepping kernel, over peer memory (NVLink / NVSwitch) instead of one
+ * NCCL all-gather per window: after finalize every rank exports the handle of its exchange buffer
+ * (a 64-byte cudaIpcMemHandle_t), the caller distributes the handles, and p2p_connect maps all
+ * n_ranks of them (handles = n_ranks x 64 bytes, in rank order). From then on the persistent kernel
+ * of every rank stores its window's spike ids straight into every rank's inbox and waits, with a
+ * bound of about one second, for the other ranks' windows; a time-out ends the run with
+ * BMTK_E_COMM. Ranks are separate processes on separate GPUs and must call run() with the same
+ * step counts. Without p2p_connect several ranks use the per-step kernels and NCCL. */
+int bmtk_engine_p2p_handle(bmtk_engine* e, void* handle64);
+int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles);
+
 /* Builds the delay-bucketed CSR on the device, allocates state and ring buffers, initialises
  * V = V_m, ASC = asc_init. Must precede run. */
 int bmtk_engine_finalize(bmtk_engine* e);

@@ -25,7 +25,9 @@ def main():
     libnccl = libnccl if os.path.exists(libnccl) else None
     uid = [nccl_unique_id(libnccl) if rank == 0 else None]
     dist.broadcast_object_list(uid, 0)
-    poisson = len(sys.argv) > 2 and sys.argv[2] == 'poisson'
+    mode = sys.argv[2] if len(sys.argv) > 2 else 'replay'
+    poisson = mode in ('poisson', 'p2p')
+    p2p = mode == 'p2p'
     net = W.c0(t_stop_ms=300.0, poisson_online=poisson)
     n = net.n_neurons
     bounds = np.linspace(0, n, world + 1).astype(int)
@@ -35,8 +37,8 @@ def main():
     part.lo, part.hi = lo, hi
     for k in ('src', 'trg', 'weight', 'delay_steps', 'port'):
         setattr(part, k, getattr(net, k)[m])
-    eng = W.build_engine(part, device=local, deterministic=True, rank=rank, n_ranks=world, nccl_uid=uid[0],
-                         libnccl=libnccl)
+    eng = W.build_engine(part, device=local, deterministic=not p2p, rank=rank, n_ranks=world, nccl_uid=uid[0],
+                         libnccl=libnccl, p2p=p2p, options=dict(chunk_steps=700) if p2p else None)
     eng.run(net.n_steps)
     st, ids = eng.fetch_spikes()
     tr = eng.fetch_trace()
@@ -46,19 +48,37 @@ def main():
     ok = True
     msg = ''
     if rank == 0:
-        ref = W.build_engine(net, device=local, deterministic=True)
+        ref = W.build_engine(net, device=local, deterministic=not p2p)
         ref.run(net.n_steps)
         rst, rids = ref.fetch_spikes()
         rtr = ref.fetch_trace()
         ast = np.concatenate([g[0] for g in gathered]); aids = np.concatenate([g[1] for g in gathered])
         o = np.lexsort((aids, ast))
-        ok &= bool(np.array_equal(ast[o], rst) and np.array_equal(aids[o], rids))
+        ast, aids = ast[o], aids[o]
         atr = np.concatenate([g[2] for g in gathered], axis=1)
         aprobe = np.concatenate([g[3] for g in gathered])
         ok &= bool(np.array_equal(aprobe, net.probe_ids))
-        ok &= bool(np.array_equal(atr.view(np.uint32), rtr.view(np.uint32)))
-        ok &= sum(g[4] for g in gathered) == ref.counter('events')
-        msg = 'spikes %d ref %d events %d ref %d' % (len(ast), len(rst), sum(g[4] for g in gathered), ref.counter('events'))
+        events = sum(g[4] for g in gathered)
+        if not p2p:
+            ok &= bool(np.array_equal(ast, rst) and np.array_equal(aids, rids))
+            ok &= bool(np.array_equal(atr.view(np.uint32), rtr.view(np.uint32)))
+            ok &= events == ref.counter('events')
+        else:
+            # atomic sums: identical spikes until fp32 summation order makes the runs part, and exact
+            # integer bookkeeping: every spike of every rank was delivered exactly once on every rank
+            k = min(len(ast), len(rst))
+            neq = np.nonzero((ast[:k] != rst[:k]) | (aids[:k] != rids[:k]))[0]
+            div = int(ast[neq[0]]) if len(neq) else net.n_steps
+            ok &= div > 800 and abs(len(ast) - len(rst)) <= 0.03 * len(rst) and eng.counter('launches') < 20
+            rowptr = ref.csr()[0].astype(np.int64)
+            outdeg = np.diff(rowptr)
+            sys.path.insert(0, os.path.join(ROOT, 'tests'))
+            from oracle import glif_oracle as O
+            steps, srcs = O.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, net.n_steps)
+            expect = int(outdeg[aids].sum() + outdeg[n + srcs].sum())
+            ok &= events == expect
+            msg = 'p2p: first divergence %d, events %d expected %d; ' % (div, events, expect)
+        msg += 'spikes %d ref %d events %d ref %d' % (len(ast), len(rst), events, ref.counter('events'))
         with open(sys.argv[1], 'w') as f:
             json.dump(dict(ok=bool(ok), msg=msg), f)
     dist.barrier()

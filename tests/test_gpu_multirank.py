@@ -1,5 +1,7 @@
-"""Two ranks on two GPUs: neuron blocks + one NCCL all-gather of spike ids per min-delay window
-must reproduce the single-GPU result bit for bit (deterministic delivery). Skipped on a box with
+"""Two ranks on two GPUs: neuron blocks + one exchange of spike ids per min-delay window must
+reproduce the single-GPU result — bit for bit with deterministic delivery over NCCL ('replay',
+'poisson'), and with exact event bookkeeping for the persistent kernel that exchanges over peer
+memory ('p2p'). Skipped on a box with
 one GPU; the CPU side of the partition logic is covered by test_partition_gloo.py."""
 import json
 import os
@@ -12,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize('mode', ['replay', 'poisson'])
+@pytest.mark.parametrize('mode', ['replay', 'poisson', 'p2p'])
 def test_two_ranks_equal_one(cabi, tmp_path, mode):
     import torch
     if torch.cuda.device_count() < 2:
