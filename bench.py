@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument('--no-cpu', action='store_true')
     ap.add_argument('--cpu-slice-ms', type=float, default=250.0)
     ap.add_argument('--step-ms', type=float, default=1000.0, help='simulated ms per bench step (1000 = the configuration)')
+    ap.add_argument('--exchange', default='p2p', choices=['p2p', 'nccl'],
+                    help='several ranks: spike exchange inside the persistent kernel over peer memory, or one NCCL '
+                         'all-gather per window around the per-step kernels')
     return ap.parse_args()
 
 
@@ -189,6 +192,11 @@ def main():
     STEP_MS = args.step_ms
     if args.impl == 'reference':
         return reference_arm(args)
+    # Only the JSON line may reach stdout: libraries (NCCL prints its version there) write to fd 1,
+    # so fd 1 is pointed at stderr for the duration and the line goes to the saved descriptor.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
     import torch.distributed as dist
@@ -243,7 +251,7 @@ def main():
     t0 = time.time()
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
                          options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
-                         libnccl=libnccl)
+                         libnccl=libnccl, p2p=args.exchange == 'p2p')
     t_build = time.time() - t0
     for _ in range(args.warmup):
         eng.run(steps_per_bench_step)
@@ -272,7 +280,7 @@ def main():
 
     # ---------------- phase timers of the persistent kernel (device %globaltimer, thread 0)
     phases = None
-    if eng.counter('persistent_blocks') > 0 and world == 1:
+    if eng.counter('persistent_blocks') > 0 and (world == 1 or args.exchange == 'p2p'):
         eng.set_option('phase_timers', 1)
         e0 = eng.counter('events')
         eng.run(steps_per_bench_step)
@@ -308,7 +316,7 @@ def main():
     pr_bytes = BYTES_PER_EVENT * prof_events / pr_n
     kernels = {
         'glif_update': {'launches': up_n, 'avg_us': up_ns / up_n * 1e-3, 'bytes_per_launch': up_bytes,
-                        'achieved_gbs': up_bytes / (up_ns / up_n), 'traffic': NCU_TRAFFIC_BYTES['glif_update']},
+                        'achieved_gbs': up_bytes / (up_ns / up_n), 'traffic': 102.8 * n_pad},
         'propagate': {'launches': pr_n, 'avg_us': pr_ns / pr_n * 1e-3, 'bytes_per_launch': pr_bytes,
                       'achieved_gbs': pr_bytes / (pr_ns / pr_n), 'traffic': NCU_TRAFFIC_BYTES['propagate']},
     }
@@ -344,7 +352,7 @@ def main():
         net.poisson_rate_hz, rates = None, net.poisson_rate_hz.astype(np.float64)
         eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
                              options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
-                             libnccl=libnccl)
+                             libnccl=libnccl, p2p=args.exchange == 'p2p')
         rng = np.random.default_rng(99)   # same seed on every rank: virtual cells are replicated
         n_chunks = 1 + args.steps
         cap = int(rates.sum() * STEP_MS * 1e-3 * 1.2) + 4096
@@ -408,14 +416,16 @@ def main():
                                    % (n_total, int(reduce_edges(net, world, dist, dev)), '' if world == 1 else ' (all ranks)',
                                       net.n_virtual),
                        'step': '%g ms of simulated time = %d update steps' % (STEP_MS, steps_per_bench_step),
-                       'partition': 'neurons in %d contiguous blocks, one NCCL all-gather of spike ids per %d-step window'
-                                    % (world, window) if world > 1 else 'single GPU',
+                       'partition': ('neurons in %d contiguous blocks, spike ids of every %d-step window exchanged %s'
+                                     % (world, window, 'inside the persistent kernel over peer memory (NVLink)'
+                                        if args.exchange == 'p2p' else 'with one NCCL all-gather'))
+                       if world > 1 else 'single GPU',
                        'l2': 'state + ring (~80 MB) are re-read every step; the 560 MB CSR exceeds L2',
                        'mean_rate_hz': spikes / n_total / (STEP_MS * 1e-3 * args.steps)},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline, 'cpu_baseline': cpu,
             'wall_ms_per_step': wall_ms / args.steps, 'setup_s': {'generate': t_gen, 'build_engine': t_build},
         }
-        print(json.dumps(line))
+        os.write(json_fd, (json.dumps(line) + '\n').encode())
     else:
         reduce_edges(net, world, dist, dev)
     if world > 1:

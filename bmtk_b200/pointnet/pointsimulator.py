@@ -181,6 +181,8 @@ class PointSimulator(object):
             dist.broadcast_object_list(uid, 0)
             eng.comm_init(uid[0], rank, world, lib)
         eng.finalize()
+        if world > 1 and not self._engine_options.get('deterministic', 0) and self._engine_options.get('persistent', 1):
+            eng.connect_peers()      # spike exchange inside the stepping kernel over peer memory
         self._engine = eng
 
     def _collect(self):
