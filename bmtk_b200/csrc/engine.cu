@@ -308,8 +308,8 @@ struct bmtk_engine {
     uint4* d_plists[2] = {nullptr, nullptr};
     uint32_t* d_plist_counts = nullptr;
     // spike exchange over peer memory (several ranks, persistent kernel)
-    uint32_t* d_xchg = nullptr;                 // this rank's exchange buffer
-    uint32_t* xchg_peers[kXRanks] = {};         // every rank's buffer as mapped here
+    unsigned long long* d_xchg = nullptr;             // this rank's exchange buffer
+    unsigned long long* xchg_peers[kXRanks] = {};     // every rank's buffer as mapped here
     bool p2p_ready = false;
     uint32_t xchg_seq = 0;                      // windows exchanged so far
     int32_t* d_probe_slot = nullptr;
@@ -1210,8 +1210,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
             CU(cudaMemset(e->d_plist_counts, 0, 8));
             if (e->n_ranks > 1) {
                 const size_t words = xchg_words((uint32_t)e->n_ranks, e->send_cap);
-                CU(cudaMalloc(&e->d_xchg, 4 * words));
-                CU(cudaMemset(e->d_xchg, 0, 4 * words));
+                CU(cudaMalloc(&e->d_xchg, 8 * words));
+                CU(cudaMemset(e->d_xchg, 0, 8 * words));
             }
         }
     }
@@ -1482,7 +1482,7 @@ int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
         cudaError_t ce = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
         if (ce != cudaSuccess)
             return fail(BMTK_E_COMM, "p2p_connect: cannot map the exchange buffer of rank %d: %s", r, cudaGetErrorString(ce));
-        e->xchg_peers[r] = (uint32_t*)p;
+        e->xchg_peers[r] = (unsigned long long*)p;
     }
     e->p2p_ready = true;
     return BMTK_OK;

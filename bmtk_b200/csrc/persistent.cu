@@ -149,16 +149,22 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, 
 
 // ---- several ranks: the exchange is part of this kernel, over peer memory (NVLink / NVSwitch)
 
-__device__ __forceinline__ uint32_t* x_counts(uint32_t* x, uint32_t parity) { return x + kXRanks + parity * kXRanks; }
-__device__ __forceinline__ uint32_t* x_inbox(const PersistArgs& a, uint32_t* x, uint32_t parity, uint32_t src_rank) {
-    return x + 3 * kXRanks + ((size_t)parity * a.n_ranks + src_rank) * a.xchg_cap;
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64* x_counts(u64* x, uint32_t parity) { return x + parity * kXRanks; }
+__device__ __forceinline__ u64* x_inbox(const PersistArgs& a, u64* x, uint32_t parity, uint32_t src_rank) {
+    return x + 2 * kXRanks + ((size_t)parity * a.n_ranks + src_rank) * a.xchg_cap;
 }
+__device__ __forceinline__ void st_word(u64* p, uint32_t seq, uint32_t payload) {
+    *reinterpret_cast<volatile u64*>(p) = ((u64)seq << 32) | payload;
+}
+__device__ __forceinline__ u64 ld_word(const u64* p) { return *reinterpret_cast<const volatile u64*>(p); }
 
 // End of a window with several ranks: the block reserves a range behind this rank's window counter
-// and stores its spikes (step_in_window << kSrcBits | global id) into inbox[parity][rank] of every
-// rank, its own included, with plain peer stores; then the spike log, locally.
+// and stores its spikes, tagged with the window's sequence number, into inbox[parity][rank] of every
+// rank (its own included) with plain 8-byte peer stores; then the spike log, locally.
 __device__ __forceinline__ unsigned long long flush_block_multi(const PersistArgs& a, BlockShared& sh, uint32_t parity,
-                                                                unsigned long long win_base) {
+                                                                uint32_t seq, unsigned long long win_base) {
     __syncthreads();
     const uint32_t n = min(sh.pend_count, kPend);
     if (n == 0) return 0ull;
@@ -171,7 +177,7 @@ __device__ __forceinline__ unsigned long long flush_block_multi(const PersistArg
         const uint32_t e = sh.pend[k];
         const uint32_t pos = sh.base + k;
         if (pos < a.xchg_cap) {
-            for (uint32_t r = 0; r < a.n_ranks; ++r) x_inbox(a, a.peers[r], parity, a.rank)[pos] = e;
+            for (uint32_t r = 0; r < a.n_ranks; ++r) st_word(x_inbox(a, a.peers[r], parity, a.rank) + pos, seq, e);
         } else {
             atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
         }
@@ -185,37 +191,33 @@ __device__ __forceinline__ unsigned long long flush_block_multi(const PersistArg
             }
         }
     }
-    __threadfence_system();   // the peer stores are ordered before whatever this thread signals later
     __syncthreads();
     if (threadIdx.x == 0) sh.pend_count = 0u;
     return (unsigned long long)n;
 }
 
-// After the grid barrier that follows the flush: thread 0 publishes this rank's count and sequence
-// number to every rank; the first n_ranks threads of block 0 then wait (bounded) until every rank
-// has published the same window. On a time-out the sticky error bit is set and all later waits are
+// After the grid barrier that follows the flush: thread 0 stores this rank's tagged count to every
+// rank; the first n_ranks threads of block 0 then wait (bounded) until the count word of every rank
+// carries this window's tag. On a time-out the sticky error bit is set and all later waits are
 // skipped, so the launch still ends; the host turns the bit into BMTK_E_COMM.
+constexpr unsigned int kWaitSpins = 4000000u;   // x (load + 100 ns sleep): about a second
+
 __device__ __forceinline__ void publish_and_wait(const PersistArgs& a, uint32_t parity, uint32_t seq) {
     if (blockIdx.x != 0) return;
     if (threadIdx.x == 0) {
         const uint32_t n = min(__ldcg(a.list_counts + parity), a.xchg_cap);
-        for (uint32_t r = 0; r < a.n_ranks; ++r) x_counts(a.peers[r], parity)[a.rank] = n;
-        __threadfence_system();
-        for (uint32_t r = 0; r < a.n_ranks; ++r) *reinterpret_cast<volatile uint32_t*>(a.peers[r] + a.rank) = seq;
+        for (uint32_t r = 0; r < a.n_ranks; ++r) st_word(x_counts(a.peers[r], parity) + a.rank, seq, n);
     }
-    if (threadIdx.x < a.n_ranks) {
-        volatile uint32_t* flag = reinterpret_cast<volatile uint32_t*>(a.peers[a.rank] + threadIdx.x);
-        if (!(__ldcg(&a.ctl->error_flags) & kErrExchangeTimeout)) {
-            unsigned int spins = 0;
-            while ((int)(*flag - seq) < 0) {
-                if (++spins > 4000000u) {   // ~1 s
-                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
-                    break;
-                }
-                __nanosleep(200);
+    if (threadIdx.x < a.n_ranks && !(__ldcg(&a.ctl->error_flags) & kErrExchangeTimeout)) {
+        const u64* w = x_counts(a.peers[a.rank], parity) + threadIdx.x;
+        unsigned int spins = 0;
+        while ((uint32_t)(ld_word(w) >> 32) != seq) {
+            if (++spins > kWaitSpins) {
+                atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                break;
             }
+            __nanosleep(100);
         }
-        __threadfence_system();
     }
 }
 
@@ -292,15 +294,19 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, uint32_t pa
     if (events) atomicAdd(&a.ctl->n_events, events);
 }
 
-// Delivery with several ranks: the window's spikes of every rank sit in the local inbox; rows are
-// looked up in this rank's CSR (it holds a row for every source of the network).
-__device__ __forceinline__ void deliver_window_multi(const PersistArgs& a, uint32_t parity, const uint32_t* virt,
-                                                     unsigned long long win_base, uint32_t win_len) {
-    uint32_t* x = a.peers[a.rank];
+// Delivery with several ranks: the window's spikes of every rank arrive in the local inbox; an entry
+// is valid once its tag is this window's (its 8-byte store may land after the count word did, so
+// the reader waits for the tag, bounded). Rows are looked up in this rank's CSR, which holds a row
+// for every source of the network.
+__device__ __forceinline__ void deliver_window_multi(const PersistArgs& a, uint32_t parity, uint32_t seq,
+                                                     const uint32_t* virt, unsigned long long win_base, uint32_t win_len) {
+    u64* x = a.peers[a.rank];
     uint32_t off[kXRanks + 1];
     off[0] = 0;
-    for (uint32_t r = 0; r < a.n_ranks; ++r)
-        off[r + 1] = off[r] + min(*reinterpret_cast<volatile uint32_t*>(x_counts(x, parity) + r), a.xchg_cap);
+    for (uint32_t r = 0; r < a.n_ranks; ++r) {
+        const u64 w = ld_word(x_counts(x, parity) + r);
+        off[r + 1] = off[r] + ((uint32_t)(w >> 32) == seq ? min((uint32_t)w, a.xchg_cap) : 0u);
+    }
     const uint32_t n_rec = off[a.n_ranks];
     uint32_t n_in = 0, in_begin = 0;
     if (a.in_ptr) {
@@ -323,9 +329,20 @@ __device__ __forceinline__ void deliver_window_multi(const PersistArgs& a, uint3
         if (idx < n_rec) {
             uint32_t r = 0;
             while (idx >= off[r + 1]) ++r;
-            const uint32_t e = __ldcv(x_inbox(a, x, parity, r) + (idx - off[r]));
-            src = e & kSrcMask;
-            step = win_base + (e >> kSrcBits);
+            const u64* p = x_inbox(a, x, parity, r) + (idx - off[r]);
+            u64 w = ld_word(p);
+            unsigned int spins = 0;
+            while ((uint32_t)(w >> 32) != seq) {
+                if (++spins > kWaitSpins) {
+                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                    break;
+                }
+                __nanosleep(100);
+                w = ld_word(p);
+            }
+            if ((uint32_t)(w >> 32) != seq) continue;   // uniform over the group: every lane read the same word
+            src = (uint32_t)w & kSrcMask;
+            step = win_base + ((uint32_t)w >> kSrcBits);
         } else if (idx < n_rec + n_in) {
             src = a.in_src[in_begin + idx - n_rec];
             step = a.in_step[in_begin + idx - n_rec];
@@ -461,7 +478,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
             const bool multi = a.n_ranks > 1;
             const uint32_t seq = a.seq0 + win + 1u;
             const uint32_t par = multi ? (seq & 1u) : (win & 1u);
-            my_spikes += multi ? flush_block_multi(a, sh, par, win_base) : flush_block(a, sh, par, win_base);
+            my_spikes += multi ? flush_block_multi(a, sh, par, seq, win_base) : flush_block(a, sh, par, win_base);
             const unsigned long long t0b = timer ? gtimer() : 0ull;
             grid.sync();
             if (multi) {
@@ -474,7 +491,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
                 a.list_counts[par ^ 1u] = 0u;
                 if (a.poisson_thr) a.virts[(win + 1) & 1][0] = 0u;
             }
-            if (multi) deliver_window_multi(a, par, virt, win_base, s_in_win);
+            if (multi) deliver_window_multi(a, par, seq, virt, win_base, s_in_win);
             else deliver_window(a, par, virt, win_base, s_in_win);
             const unsigned long long t1b = timer ? gtimer() : 0ull;
             grid.sync();

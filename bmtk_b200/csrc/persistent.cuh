@@ -54,17 +54,20 @@ struct PersistArgs {
     uint32_t trace_cap;
     uint32_t profile;
     // Spike exchange between ranks over peer memory (n_ranks > 1). Every rank owns an exchange
-    // buffer of u32 words laid out as  flags[kXRanks] | counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
+    // buffer of 64-bit words laid out as  counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
     // peers[r] is rank r's buffer as mapped into this process (peers[rank] is the local one).
-    // Window `seq` uses parity seq & 1; rank r publishes its spikes of the window into
-    // inbox[parity][r] of EVERY rank, then counts[parity][r], then flags[r] = seq.
+    // Every word is {window sequence number : 32 | payload : 32} written with ONE 8-byte store, so a
+    // reader knows a word belongs to the window it is waiting for by its tag alone and no
+    // system-wide fence is needed (the payload of a count word is the number of spikes, of an inbox
+    // word a spike entry). Window `seq` uses parity seq & 1; rank r stores its spikes of the window
+    // into inbox[parity][r] of EVERY rank and then its count into counts[parity][r] of every rank.
     uint32_t n_ranks, rank;
-    uint32_t* peers[kXRanks];
+    unsigned long long* peers[kXRanks];
     uint32_t xchg_cap;
     uint32_t seq0;             // windows completed before this launch
 };
 
-constexpr uint32_t xchg_words(uint32_t n_ranks, uint32_t cap) { return kXRanks + 2 * kXRanks + 2 * n_ranks * cap; }
+constexpr size_t xchg_words(uint32_t n_ranks, uint32_t cap) { return 2 * (size_t)kXRanks + 2 * (size_t)n_ranks * cap; }
 
 const void* persistent_kernel_ptr(bool has_theta, bool has_iext, bool resident);
 int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem);
