@@ -301,7 +301,7 @@ struct bmtk_engine {
     uint64_t update_launches = 0, prop_launches = 0;
 
     // persistent stepping (single rank, atomic delivery)
-    bool persistent = true, phase_timers = false;
+    bool persistent = true, phase_timers = false, ring_prefetch = false;
     int persist_blocks = 0;
     bool persist_resident = false;
     uint32_t* d_virt2 = nullptr;
@@ -701,6 +701,7 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.trace = e->d_trace;
     a.trace_cap = e->trace_cap;
     a.profile = e->phase_timers ? 1u : 0u;
+    a.ring_prefetch = e->ring_prefetch ? 1u : 0u;
     a.n_ranks = (uint32_t)e->n_ranks;
     a.rank = (uint32_t)e->rank;
     a.xchg_cap = e->send_cap;
@@ -950,6 +951,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     if (k == "use_graph") { e->use_graph = value != 0; return BMTK_OK; }
     if (k == "persistent") { e->persistent = value != 0; return BMTK_OK; }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
+    if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
     if (k == "chunk_steps") {
         if (value < 1) return fail(BMTK_E_INVALID, "chunk_steps must be positive");
         e->chunk_steps = (uint64_t)value;

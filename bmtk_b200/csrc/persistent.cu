@@ -34,6 +34,14 @@ __device__ __forceinline__ F4 ld4cg(const float* p) {
     return F4{{t.x, t.y, t.z, t.w}};
 }
 
+// 16-byte asynchronous copy global -> shared that caches in L2 only (the ring is written by other SMs)
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ unsigned long long gtimer() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -121,15 +129,25 @@ __device__ __forceinline__ unsigned long long flush_block(const PersistArgs& a, 
 template <bool THETA, bool IEXT>
 __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, const TypeConsts* types,
                                          Neuron4<THETA, IEXT>& nr, const int (&pslot)[4], bool valid, uint32_t i0,
-                                         unsigned long long step, uint32_t s_in_win, uint32_t sample_base) {
+                                         unsigned long long step, uint32_t s_in_win, uint32_t sample_base,
+                                         const float4* staged = nullptr) {
     uint32_t mask = 0;
     if (valid) {
         const uint32_t np = a.n_pad;
         const uint32_t slot = (uint32_t)(step % a.ring_slots);
         float* ring = a.ring + (size_t)slot * kPorts * np + i0;
         F4 in[kPorts];
+        if (staged) {
+            // this step's ring slot was copied to shared memory asynchronously (this thread's 4 x 16 B)
 #pragma unroll
-        for (int p = 0; p < kPorts; ++p) in[p] = ld4cg(ring + (size_t)p * np);
+            for (int p = 0; p < kPorts; ++p) {
+                const float4 t = staged[p * kPT];
+                in[p] = F4{{t.x, t.y, t.z, t.w}};
+            }
+        } else {
+#pragma unroll
+            for (int p = 0; p < kPorts; ++p) in[p] = ld4cg(ring + (size_t)p * np);
+        }
         mask = nr.step(types, in);
         if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
         const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
@@ -376,6 +394,9 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         __syncthreads();
     }
     const TypeConsts* types = use_smem ? s_types : a.types;
+    // RESIDENT: two stage buffers [kPorts][kPT] float4 behind the type table; while step s is computed the
+    // ring slot of step s+1 (final inside a window: deliveries happen only at its end) is already on its way
+    float4* stage = reinterpret_cast<float4*>(smem_raw + (use_smem ? (sizeof(TypeConsts) * a.n_types + 15) / 16 * 16 : 0));
 
     const uint32_t nthreads = gridDim.x * kPT;
     const uint32_t gtid = blockIdx.x * kPT + threadIdx.x;
@@ -431,7 +452,25 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         }
 
         if (RESIDENT) {
-            do_group<THETA, IEXT>(a, sh, types, nr, pslot, mine, my_group * kNeuronsPerThread, step, s_in_win, sample_base);
+            const uint32_t i0 = my_group * kNeuronsPerThread;
+            float4* cur = stage + (size_t)(s & 1u) * kPorts * kPT + threadIdx.x;
+            if (mine && a.ring_prefetch) {
+                if (s_in_win == 0) {
+                    const float* r0 = a.ring + (size_t)(step % a.ring_slots) * kPorts * a.n_pad + i0;
+#pragma unroll
+                    for (int p = 0; p < kPorts; ++p) cp_async16(cur + p * kPT, r0 + (size_t)p * a.n_pad);
+                    cp_async_commit();
+                }
+                cp_async_wait_all();
+                if (s_in_win + 1 < a.window && s + 1 < a.n_steps) {
+                    float4* nxt = stage + (size_t)((s + 1) & 1u) * kPorts * kPT + threadIdx.x;
+                    const float* r1 = a.ring + (size_t)((step + 1) % a.ring_slots) * kPorts * a.n_pad + i0;
+#pragma unroll
+                    for (int p = 0; p < kPorts; ++p) cp_async16(nxt + p * kPT, r1 + (size_t)p * a.n_pad);
+                    cp_async_commit();
+                }
+            }
+            do_group<THETA, IEXT>(a, sh, types, nr, pslot, mine, i0, step, s_in_win, sample_base, a.ring_prefetch ? cur : nullptr);
         } else {
             for (uint32_t t0 = 0; t0 < gpb; t0 += kPT) {
                 const uint32_t g = blockIdx.x * gpb + t0 + threadIdx.x;
@@ -518,6 +557,7 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
 int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem) {
     int per_sm = 0, sms = 0;
     const void* f = persistent_kernel_ptr(has_theta, has_iext, resident);
+    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, kPT, smem) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
     return per_sm > 0 ? sms : 0;   // one block per SM
@@ -538,13 +578,18 @@ uint32_t persistent_threads_per_block() { return kPT; }
 
 cudaError_t launch_persistent(const PersistArgs& a, bool has_theta, bool has_iext, bool resident, int blocks,
                               cudaStream_t s) {
-    const size_t smem = a.n_types <= kSmemTypesP ? sizeof(TypeConsts) * (size_t)a.n_types : 0;
+    const size_t smem = persistent_smem(a.n_types);
+    const void* f = persistent_kernel_ptr(has_theta, has_iext, resident);
+    cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
     PersistArgs copy = a;
     void* args[] = {&copy};
-    return cudaLaunchCooperativeKernel(persistent_kernel_ptr(has_theta, has_iext, resident), dim3(blocks), dim3(kPT), args,
-                                       smem, s);
+    return cudaLaunchCooperativeKernel(f, dim3(blocks), dim3(kPT), args, smem, s);
 }
 
-size_t persistent_smem(int n_types) { return n_types <= kSmemTypesP ? sizeof(TypeConsts) * (size_t)n_types : 0; }
+size_t persistent_smem(int n_types) {
+    const size_t t = n_types <= kSmemTypesP ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0;
+    return t + 2 * kPorts * kPT * sizeof(float4);   // type table + two ring stage buffers
+}
 
 }  // namespace bmtk

@@ -53,6 +53,7 @@ struct PersistArgs {
     float* trace;
     uint32_t trace_cap;
     uint32_t profile;
+    uint32_t ring_prefetch;    // RESIDENT: copy the next step's ring slot to shared memory while this step computes
     // Spike exchange between ranks over peer memory (n_ranks > 1). Every rank owns an exchange
     // buffer of 64-bit words laid out as  counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
     // peers[r] is rank r's buffer as mapped into this process (peers[rank] is the local one).

@@ -132,6 +132,9 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
  *  "persistent"     0|1 run each chunk as ONE cooperative kernel that loops over the steps with the
  *                   neuron state held in registers (default 1; single rank, atomic delivery; may
  *                   be changed between runs)
+ *  "ring_prefetch"  0|1 persistent kernel with resident state: fetch the next step's ring slot into shared
+ *                   memory with cp.async while the current step computes (default 0: on the 2-step
+ *                   windows of the benchmark network it measured 3 % slower than plain L2 loads)
  *  "phase_timers"   0|1 let the persistent kernel accumulate the device time of its update and
  *                   delivery phases (counters "phase_update_ns", "phase_propagate_ns", "phase_windows")
  *  "use_graph"      0|1 replay each window as a CUDA graph when not persistent (default 1)

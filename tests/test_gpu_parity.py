@@ -245,6 +245,11 @@ def test_persistent_kernel_equals_per_step_launches(cabi, n):
     net = W.c1(n=n, t_stop_ms=140.0 if n < 10000 else 110.0)
     a = _run_engine(net, options=dict(persistent=1, chunk_steps=1000))
     b = _run_engine(net, options=dict(persistent=0))
+    if n < 10000:
+        # the cp.async ring prefetch variant must give the same bits
+        c = _run_engine(net, options=dict(persistent=1, ring_prefetch=1, chunk_steps=777))
+        assert np.array_equal(a[1], c[1]) and np.array_equal(a[2], c[2])
+        assert np.array_equal(a[3].view(np.uint32), c[3].view(np.uint32))
     assert a[0].counter('persistent_resident') == (1 if n < 10000 else 0)
     assert a[0].counter('launches') < 10 and b[0].counter('launches') > 2000
     assert len(a[1]) > 50
