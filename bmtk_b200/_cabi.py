@@ -63,6 +63,8 @@ _SIGNATURES = {
     'bmtk_engine_finalize': (C.c_int, [_P]),
     'bmtk_engine_p2p_handle': (C.c_int, [_P, _P]),
     'bmtk_engine_p2p_connect': (C.c_int, [_P, _P]),
+    'bmtk_engine_p2p_buffer': (C.c_int, [_P, C.POINTER(_P)]),
+    'bmtk_engine_p2p_connect_pointers': (C.c_int, [_P, C.POINTER(_P)]),
     'bmtk_engine_run': (C.c_int, [_P, C.c_uint64]),
     'bmtk_engine_spike_count': (C.c_int, [_P, C.POINTER(C.c_uint64)]),
     'bmtk_engine_fetch_spikes': (C.c_int, [_P, C.c_uint64, _P, _P, C.POINTER(C.c_uint64)]),

@@ -310,7 +310,7 @@ struct bmtk_engine {
     // spike exchange over peer memory (several ranks, persistent kernel)
     unsigned long long* d_xchg = nullptr;             // this rank's exchange buffer
     unsigned long long* xchg_peers[kXRanks] = {};     // every rank's buffer as mapped here
-    bool p2p_ready = false;
+    bool p2p_ready = false, p2p_by_pointer = false;
     uint32_t xchg_seq = 0;                      // windows exchanged so far
     int32_t* d_probe_slot = nullptr;
     unsigned long long* d_ce_group_step = nullptr;
@@ -432,6 +432,8 @@ static int enqueue_window(bmtk_engine* e, uint32_t w, bool capturing) {
         }
     }
     if (e->n_ranks > 1) {
+        if (!e->comm) return fail(BMTK_E_COMM, "several ranks without an NCCL communicator: connect the peer-memory exchange "
+                                  "(p2p_connect) or pass an id to comm_init");
         const int rc = g_nccl.AllGather(e->d_send, e->d_gathered, (size_t)e->send_cap + 4, kNcclUint32, e->comm,
                                         e->stream);
         if (rc != 0)
@@ -818,7 +820,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step); cudaFree(e->d_ce_group_ptr);
     cudaFree(e->d_plists[0]); cudaFree(e->d_plists[1]); cudaFree(e->d_plist_counts);
     for (int r = 0; r < e->n_ranks && r < (int)kXRanks; ++r)
-        if (e->xchg_peers[r] && r != e->rank) cudaIpcCloseMemHandle(e->xchg_peers[r]);
+        if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r]);
     cudaFree(e->d_xchg);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
@@ -987,7 +989,7 @@ int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ra
     e->rank = rank;
     e->n_ranks = n_ranks;
     if (n_ranks == 1) return BMTK_OK;
-    if (!uid128) return fail(BMTK_E_INVALID, "comm_init: uid128 is NULL");
+    if (!uid128) return BMTK_OK;   // no NCCL communicator: only the peer-memory exchange can be used
     int rc = load_nccl(libnccl);
     if (rc) return rc;
     rc = set_device(e);
@@ -1487,6 +1489,25 @@ int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
         e->xchg_peers[r] = (unsigned long long*)p;
     }
     e->p2p_ready = true;
+    return BMTK_OK;
+}
+
+int bmtk_engine_p2p_buffer(bmtk_engine* e, void** d_buffer) {
+    if (!e || !e->finalized || !d_buffer) return fail(BMTK_E_INVALID, "p2p_buffer: engine missing, not finalized, or NULL");
+    if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_buffer: no exchange buffer (one rank, or cooperative launch unavailable)");
+    *d_buffer = e->d_xchg;
+    return BMTK_OK;
+}
+
+int bmtk_engine_p2p_connect_pointers(bmtk_engine* e, void* const* d_buffers) {
+    if (!e || !e->finalized || !d_buffers) return fail(BMTK_E_INVALID, "p2p_connect_pointers: engine missing, not finalized, or NULL");
+    if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_connect_pointers: no exchange buffer");
+    for (int r = 0; r < e->n_ranks; ++r) {
+        if (r != e->rank && !d_buffers[r]) return fail(BMTK_E_INVALID, "p2p_connect_pointers: buffer of rank %d is NULL", r);
+        e->xchg_peers[r] = r == e->rank ? e->d_xchg : (unsigned long long*)d_buffers[r];
+    }
+    e->p2p_ready = true;
+    e->p2p_by_pointer = true;
     return BMTK_OK;
 }
 

@@ -185,6 +185,16 @@ class Engine(object):
         buf = (C.c_char * len(blob)).from_buffer_copy(blob)
         check(self._lib.bmtk_engine_p2p_connect(self._h, buf))
 
+    def p2p_buffer(self):
+        """Device pointer of this engine's exchange buffer (ranks living in one process)."""
+        p = C.c_void_p()
+        check(self._lib.bmtk_engine_p2p_buffer(self._h, C.byref(p)))
+        return p.value
+
+    def p2p_connect_pointers(self, pointers):
+        arr = (C.c_void_p * len(pointers))(*[C.c_void_p(p) for p in pointers])
+        check(self._lib.bmtk_engine_p2p_connect_pointers(self._h, arr))
+
     def connect_peers(self):
         """Exchanges the handles over torch.distributed (any backend) and connects."""
         import torch.distributed as dist

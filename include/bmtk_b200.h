@@ -143,7 +143,8 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
 
 /* Multi-GPU spike exchange: replaces NEST's MPI exchange inside nest.Simulate. uid is the
  * 128-byte ncclUniqueId made by bmtk_comm_unique_id on rank 0 and distributed by the caller;
- * libnccl is the path of the NCCL shared object to use (NULL = "libnccl.so.2"). */
+ * libnccl is the path of the NCCL shared object to use (NULL = "libnccl.so.2"). A NULL uid creates no
+ * communicator (for ranks that only use the peer-memory exchange below). */
 int bmtk_comm_unique_id(void* uid128, const char* libnccl);
 int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ranks, const char* libnccl);
 
@@ -157,6 +158,12 @@ int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ra
  * step counts. Without p2p_connect several ranks use the per-step kernels and NCCL. */
 int bmtk_engine_p2p_handle(bmtk_engine* e, void* handle64);
 int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles);
+/* The same for ranks that live in ONE process (one engine per GPU, peer access enabled by the
+ * caller): p2p_buffer returns the device pointer of an engine's exchange buffer, and
+ * p2p_connect_pointers takes the n_ranks pointers in rank order. comm_init may then be given a
+ * NULL id (no NCCL communicator is created). */
+int bmtk_engine_p2p_buffer(bmtk_engine* e, void** d_buffer);
+int bmtk_engine_p2p_connect_pointers(bmtk_engine* e, void* const* d_buffers);
 
 /* Builds the delay-bucketed CSR on the device, allocates state and ring buffers, initialises
  * V = V_m, ASC = asc_init. Must precede run. */

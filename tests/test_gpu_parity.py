@@ -483,3 +483,34 @@ def test_checkpoint_resume(cabi, tmp_path, deterministic):
     other = W.build_engine(W.c0(t_stop_ms=300.0, poisson_online=True, dt=0.2))
     with pytest.raises(Exception):
         other.load_state(ck)
+
+
+def test_exchange_timeout_is_an_error_not_a_hang(cabi):
+    """Failure detection without a GPU fault: rank 0 of two is connected to the exchange buffer of a
+    rank that never runs, so the bounded wait for that rank's window runs out (about a second); the
+    launch still ends, run() reports BMTK_E_COMM, and the device stays usable."""
+    import time
+    from bmtk_b200._cabi import EngineError, E_COMM
+    net = W.c0(t_stop_ms=50.0)
+    half = net.n_neurons // 2
+
+    def part(lo, hi):
+        p = W.c0(t_stop_ms=50.0)
+        m = (net.trg >= lo) & (net.trg < hi)
+        p.lo, p.hi = lo, hi
+        for k in ('src', 'trg', 'weight', 'delay_steps', 'port'):
+            setattr(p, k, getattr(net, k)[m])
+        return p
+    e0 = W.build_engine(part(0, half), rank=0, n_ranks=2)
+    e1 = W.build_engine(part(half, net.n_neurons), rank=1, n_ranks=2)      # built, never run
+    bufs = [e0.p2p_buffer(), e1.p2p_buffer()]
+    e0.p2p_connect_pointers(bufs)
+    t0 = time.time()
+    with pytest.raises(EngineError) as ei:
+        e0.run(net.n_steps)
+    assert ei.value.code == E_COMM and 'timed out' in str(ei.value)
+    assert time.time() - t0 < 30.0
+    # the context is intact: an ordinary engine still runs and agrees with itself
+    a = _run_engine(W.c0(t_stop_ms=50.0), deterministic=True)
+    b = _run_engine(W.c0(t_stop_ms=50.0), deterministic=True)
+    assert len(a[1]) > 20 and np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
