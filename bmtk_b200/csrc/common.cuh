@@ -62,6 +62,25 @@ struct Ctl {
     unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
 };
 
+// Trial batching: T independent copies ("trials") of one network share its CSR. Cell c of trial t has
+// index t*n_pad1 + c in every state array and ring plane (n_pad1 = cells per trial, padded to 4);
+// Poisson cell v of trial t has source id n_cells_all + t*n_virtual + v and draws from its own Philox
+// stream. With one trial n_cells_all = n_pad1 = n_global (ids are global neuron ids, trial 0).
+struct IdSpace {
+    uint32_t n_pad1, n_cells_all, n_virtual, n_global;
+};
+// source id -> CSR row and trial
+__device__ __forceinline__ void split_source(const IdSpace& s, uint32_t id, uint32_t& row, uint32_t& trial) {
+    if (id < s.n_cells_all) {
+        trial = id / s.n_pad1;
+        row = id - trial * s.n_pad1;
+    } else {
+        const uint32_t v = id - s.n_cells_all;
+        trial = v / s.n_virtual;
+        row = s.n_global + (v - trial * s.n_virtual);
+    }
+}
+
 // Neuron state, structure of arrays; every array has n_pad entries (multiple of 4, 16-byte aligned).
 struct StateSoA {
     float* U;        // membrane potential relative to E_L
@@ -80,7 +99,9 @@ struct UpdateArgs {
     StateSoA st;
     const TypeConsts* types;
     int32_t n_types;
-    uint32_t n_local, n_pad;
+    uint32_t n_local, n_pad;  // n_pad covers all trials
+    uint32_t n_pad1;          // padded cells of ONE trial held here (= n_pad with one trial)
+    IdSpace ids;
     uint32_t lo;              // global id of local neuron 0
     float* ring;              // [slots][kPorts][n_pad]
     uint32_t ring_slots;
@@ -93,7 +114,7 @@ struct UpdateArgs {
     uint32_t log_cap;
     // on-line Poisson sources (nullptr = none)
     const uint4* poisson_thr; // per virtual source: CDF thresholds of k = 0..3
-    uint32_t n_virtual, n_global;
+    uint32_t n_virtual, n_global, n_trials;
     uint64_t seed;
     uint32_t* virt;           // [0] = count, then entries, same packing as `send`
     uint32_t virt_cap;
@@ -105,6 +126,8 @@ struct PropArgs {
     uint32_t target_bits;
     float* ring;
     uint32_t ring_slots, n_pad;
+    uint32_t n_pad1;                   // local cells per trial (offset of a trial inside a ring plane)
+    IdSpace ids;
     Ctl* ctl;
     // recurrent spikes: n_seg segments of seg_stride words, word 0 = count
     const uint32_t* gathered;

@@ -214,7 +214,7 @@ struct bmtk_engine {
 
     // nodes
     uint64_t n_global = 0, lo = 0, n_local = 0, n_virtual = 0;
-    uint32_t n_pad = 0;
+    uint32_t n_pad = 0, n_pad1 = 0, n_trials = 1;
     std::vector<uint16_t> type_index;
     std::vector<bmtk_glif_params> types;
     bool has_theta = false;
@@ -331,6 +331,20 @@ static int set_device(bmtk_engine* e) {
     return BMTK_OK;
 }
 
+static IdSpace make_ids(bmtk_engine* e) {
+    IdSpace s{};
+    s.n_virtual = e->n_virtual ? (uint32_t)e->n_virtual : 1u;
+    s.n_global = (uint32_t)e->n_global;
+    if (e->n_trials > 1) {
+        s.n_pad1 = e->n_pad1;
+        s.n_cells_all = e->n_pad;
+    } else {
+        s.n_pad1 = (uint32_t)std::max<uint64_t>(e->n_global, 1);
+        s.n_cells_all = (uint32_t)e->n_global;
+    }
+    return s;
+}
+
 static UpdateArgs make_update_args(bmtk_engine* e, uint32_t s) {
     UpdateArgs a{};
     a.st = e->st;
@@ -338,6 +352,9 @@ static UpdateArgs make_update_args(bmtk_engine* e, uint32_t s) {
     a.n_types = (int32_t)e->types.size();
     a.n_local = (uint32_t)e->n_local;
     a.n_pad = e->n_pad;
+    a.n_pad1 = e->n_pad1;
+    a.ids = make_ids(e);
+    a.n_trials = e->n_trials;
     a.lo = (uint32_t)e->lo;
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
@@ -365,6 +382,8 @@ static PropArgs make_prop_args(bmtk_engine* e, uint32_t w) {
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
     a.n_pad = e->n_pad;
+    a.n_pad1 = e->n_pad1;
+    a.ids = make_ids(e);
     a.ctl = e->d_ctl;
     a.gathered = e->n_ranks > 1 ? e->d_gathered : e->d_send;
     a.n_seg = (uint32_t)e->n_ranks;
@@ -664,6 +683,9 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.n_pad = e->n_pad;
     a.lo = (uint32_t)e->lo;
     a.n_global = (uint32_t)e->n_global;
+    a.n_pad1 = e->n_pad1;
+    a.n_trials = e->n_trials;
+    a.ids = make_ids(e);
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
     a.ctl = e->d_ctl;
@@ -888,6 +910,7 @@ int bmtk_engine_add_edges(bmtk_engine* e, uint64_t n, const uint32_t* src, const
 int bmtk_engine_set_input_spikes(bmtk_engine* e, uint64_t n, const uint32_t* virt_index, const uint32_t* stamp_step) {
     if (!e) return fail(BMTK_E_INVALID, "engine is NULL");
     if (n && (!virt_index || !stamp_step)) return fail(BMTK_E_INVALID, "set_input_spikes: NULL array");
+    if (e->finalized && e->n_trials > 1) return fail(BMTK_E_UNSUPPORTED, "trials > 1 take Poisson cells only");
     for (uint64_t i = 0; i < n; ++i) {
         if (virt_index[i] >= e->n_virtual)
             return fail(BMTK_E_INVALID, "input spike %llu: virtual cell %u out of range", (unsigned long long)i, virt_index[i]);
@@ -937,8 +960,9 @@ int bmtk_engine_record_spikes(bmtk_engine* e, int enable) {
 int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps) {
     if (!e || e->finalized) return fail(BMTK_E_INVALID, "record_vm: engine missing or already finalized");
     if (interval_steps < 1) return fail(BMTK_E_INVALID, "record_vm: interval must be at least one step");
+    const uint64_t span = e->n_trials > 1 ? (uint64_t)e->n_trials * ((e->n_local + 3) / 4 * 4) : e->n_local;
     for (uint64_t i = 0; i < n_ids; ++i)
-        if (ids[i] < e->lo || ids[i] >= e->lo + e->n_local)
+        if (ids[i] < e->lo || ids[i] >= e->lo + span)
             return fail(BMTK_E_INVALID, "record_vm: id %u outside this engine's block", ids[i]);
     e->probe_ids.resize(n_ids);
     for (uint64_t i = 0; i < n_ids; ++i) e->probe_ids[i] = ids[i] - (uint32_t)e->lo;
@@ -962,6 +986,10 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     if (e->finalized) return fail(BMTK_E_INVALID, "option '%s' must be set before finalize", key);
     if (value < 0) return fail(BMTK_E_INVALID, "option '%s' must not be negative", key);
     if (k == "deterministic") e->deterministic = value != 0;
+    else if (k == "trials") {
+        if (value < 1 || value > 4096) return fail(BMTK_E_INVALID, "trials must be 1..4096");
+        e->n_trials = (uint32_t)value;
+    }
     else if (k == "window") e->window_opt = (uint32_t)value;
     else if (k == "spike_capacity") e->spike_cap_opt = (uint64_t)value;
     else if (k == "log_capacity") e->log_cap = std::max<uint64_t>(1024, (uint64_t)value);
@@ -1008,8 +1036,18 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     if (rc) return rc;
     const uint64_t n_rows = e->n_global + e->n_virtual;
     e->n_edges = e->e_src.size();
-    e->n_pad = (uint32_t)((e->n_local + 3) / 4 * 4);
-    if (e->n_pad == 0) e->n_pad = 4;
+    e->n_pad1 = (uint32_t)((e->n_local + 3) / 4 * 4);
+    if (e->n_pad1 == 0) e->n_pad1 = 4;
+    if (e->n_trials > 1) {
+        if (e->n_ranks > 1 || e->lo != 0 || e->n_local != e->n_global)
+            return fail(BMTK_E_UNSUPPORTED, "trials > 1 need the whole network on one rank (shard the trials over ranks instead)");
+        if (e->deterministic) return fail(BMTK_E_UNSUPPORTED, "trials > 1 are not available with deterministic delivery");
+        if (e->has_pending_inputs || !e->ce_step_in.empty())
+            return fail(BMTK_E_UNSUPPORTED, "trials > 1 take Poisson cells only (no replayed spikes, no clamps)");
+        if ((uint64_t)e->n_trials * (e->n_pad1 + e->n_virtual) >= (1ull << kSrcBits))
+            return fail(BMTK_E_UNSUPPORTED, "trials x (neurons + virtual cells) exceeds 2^%d source ids", kSrcBits);
+    }
+    e->n_pad = e->n_pad1 * e->n_trials;
 
     // delays and the bit layout of a CSR entry
     uint32_t dmax = 1, dmin = 0xffffffffu;
@@ -1021,7 +1059,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     e->max_delay = dmax;
     e->min_delay = dmin;
     uint32_t tb = 1;
-    while ((1ull << tb) < e->n_pad) ++tb;
+    while ((1ull << tb) < e->n_pad1) ++tb;
     uint32_t db = 1;
     while ((1u << db) <= dmax) ++db;
     if (tb + 2 + db > 32)
@@ -1069,7 +1107,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     CU(cudaMalloc(&e->d_type, 2 * np));
     {
         std::vector<uint16_t> ty(np, 0);
-        std::copy(e->type_index.begin(), e->type_index.end(), ty.begin());
+        for (uint32_t t = 0; t < e->n_trials; ++t)      // every trial has the same cells
+            std::copy(e->type_index.begin(), e->type_index.end(), ty.begin() + (size_t)t * e->n_pad1);
         CU(cudaMemcpy(e->d_type, ty.data(), 2 * np, cudaMemcpyHostToDevice));
     }
     e->st.type = e->d_type;
@@ -1098,8 +1137,9 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     cudaFree(d_init);
 
     // spike lists. Automatic capacity: every local neuron may fire in 1 of 8 steps of a window.
-    uint64_t cap = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, (uint64_t)e->n_local * w / 8);
-    cap = std::min<uint64_t>(cap, (uint64_t)e->n_local * w + 4);
+    const uint64_t n_cells = (uint64_t)e->n_local * e->n_trials;
+    uint64_t cap = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, n_cells * w / 8);
+    cap = std::min<uint64_t>(cap, n_cells * w + 4);
     cap = (cap + 3) / 4 * 4;
     if (cap + 4 >= (1ull << 31)) return fail(BMTK_E_UNSUPPORTED, "spike_capacity too large");
     e->send_cap = (uint32_t)cap;
@@ -1111,7 +1151,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         CU(cudaMemset(e->d_gathered, 0, 4 * seg * e->n_ranks));
     }
     if (e->has_poisson) {
-        uint64_t vc = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, e->n_virtual * w / 4);
+        uint64_t vc = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, e->n_virtual * e->n_trials * w / 4);
         e->virt_cap = (uint32_t)vc;
         CU(cudaMalloc(&e->d_virt, 4 * ((size_t)e->virt_cap + 4)));
         CU(cudaMemset(e->d_virt, 0, 4 * ((size_t)e->virt_cap + 4)));
@@ -1280,7 +1320,8 @@ int bmtk_engine_get_state(bmtk_engine* e, const char* var, float* out) {
     int rc = set_device(e);
     if (rc) return rc;
     const std::string v(var);
-    const size_t n = e->n_local, np = e->n_pad;
+    // one trial: n_local values; several trials: all n_trials * n_pad1 cells (trial-major, padded)
+    const size_t n = e->n_trials > 1 ? (size_t)e->n_pad : e->n_local, np = e->n_pad;
     const float* src = nullptr;
     if (v == "U" || v == "V_m") src = e->st.U;
     else if (v == "asc0") src = e->st.asc0;
@@ -1304,7 +1345,10 @@ int bmtk_engine_get_state(bmtk_engine* e, const char* var, float* out) {
     CU(cudaStreamSynchronize(e->stream));
     CU(cudaMemcpy(out, src, 4 * n, cudaMemcpyDeviceToHost));
     if (v == "V_m")
-        for (size_t i = 0; i < n; ++i) out[i] += (float)e->types[e->type_index[i]].E_L;
+        for (size_t i = 0; i < n; ++i) {
+            const size_t c = i % e->n_pad1;
+            if (c < e->n_local) out[i] += (float)e->types[e->type_index[c]].E_L;
+        }
     return BMTK_OK;
 }
 
@@ -1626,6 +1670,8 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
+    else if (k == "n_pad1") *out = e->n_pad1;
+    else if (k == "trials") *out = e->n_trials;
     else return fail(BMTK_E_INVALID, "unknown counter '%s'", name);
     return BMTK_OK;
 }

@@ -33,12 +33,13 @@ __global__ void __launch_bounds__(kUpdateThreads) glif_update_kernel(const Updat
         const uint32_t v = (blockIdx.x - neuron_blocks) * kUpdateThreads + threadIdx.x;
         int k = 0;
         uint32_t e = 0;
-        if (v < a.n_virtual) {
-            const uint4 thr = a.poisson_thr[v];
-            const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), 0u, (uint32_t)a.seed,
+        if (v < a.n_virtual * a.n_trials) {
+            const uint32_t trial = v / a.n_virtual, cell = v - trial * a.n_virtual;
+            const uint4 thr = a.poisson_thr[cell];
+            const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), trial, (uint32_t)a.seed,
                                              (uint32_t)(a.seed >> 32)).x;
             k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
-            e = (a.step_in_window << kSrcBits) | (a.n_global + v);
+            e = (a.step_in_window << kSrcBits) | (a.ids.n_cells_all + v);
         }
         if (__any_sync(0xffffffffu, k > 0)) {
             uint32_t tot;
@@ -74,8 +75,9 @@ __global__ void __launch_bounds__(kUpdateThreads) glif_update_kernel(const Updat
 #pragma unroll
         for (int p = 0; p < kPorts; ++p) in[p] = ld4(ring + (size_t)p * np);
         spk_mask = nr.step(types, in);
-        // neurons beyond n_local are padding
-        if (i0 + kNeuronsPerThread > a.n_local) spk_mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
+        // cells beyond n_local inside a trial are padding
+        const uint32_t li0 = i0 % a.n_pad1;
+        if (li0 + kNeuronsPerThread > a.n_local) spk_mask &= (1u << (a.n_local > li0 ? a.n_local - li0 : 0)) - 1u;
         nr.store(a.st, np, i0);
         const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -94,7 +96,7 @@ int glif_update_blocks(uint32_t n_pad, uint32_t n_virtual_poisson) {
 }
 
 cudaError_t launch_glif_update(const UpdateArgs& a, bool has_theta, bool has_iext, cudaStream_t s) {
-    const int blocks = glif_update_blocks(a.n_pad, a.poisson_thr ? a.n_virtual : 0);
+    const int blocks = glif_update_blocks(a.n_pad, a.poisson_thr ? a.n_virtual * a.n_trials : 0);
     if (blocks == 0) return cudaSuccess;
     const size_t smem = a.n_types <= kSmemTypes ? sizeof(TypeConsts) * (size_t)a.n_types : 0;
     if (has_theta) {

@@ -97,7 +97,8 @@ __device__ __forceinline__ unsigned long long flush_block(const PersistArgs& a, 
     }
     // while those atomics are in flight: row extents and L2 prefetch, one pending spike per warp
     for (uint32_t k = warp; k < n; k += kPT / 32) {
-        const uint32_t gid = sh.pend[k] & kSrcMask;
+        uint32_t gid, trial;
+        split_source(a.ids, sh.pend[k] & kSrcMask, gid, trial);
         const unsigned long long rb = a.rowptr[gid], re = a.rowptr[gid + 1];
         const char* row = reinterpret_cast<const char*>(a.entries + rb);
         for (unsigned long long off = (unsigned long long)lane * 128ull; off < (re - rb) * 8ull; off += 32ull * 128ull)
@@ -106,8 +107,10 @@ __device__ __forceinline__ unsigned long long flush_block(const PersistArgs& a, 
     __syncthreads();   // base / lbase are known
     for (uint32_t k = threadIdx.x; k < n; k += kPT) {
         const uint32_t e = sh.pend[k];
-        const uint32_t gid = e & kSrcMask;
-        const unsigned long long rb = a.rowptr[gid], re = a.rowptr[gid + 1];   // L1 hits now
+        const uint32_t gid = e & kSrcMask;   // id in the log: trial * n_pad1 + cell with several trials
+        uint32_t row, trial;
+        split_source(a.ids, gid, row, trial);
+        const unsigned long long rb = a.rowptr[row], re = a.rowptr[row + 1];   // L1 hits now
         const uint32_t pos = sh.base + k;
         if (pos < a.send_cap) a.lists[parity][pos] = make_uint4(e, (uint32_t)(re - rb), (uint32_t)rb, (uint32_t)(rb >> 32));
         else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
@@ -149,7 +152,8 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, 
             for (int p = 0; p < kPorts; ++p) in[p] = ld4cg(ring + (size_t)p * np);
         }
         mask = nr.step(types, in);
-        if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
+        const uint32_t li0 = i0 % a.n_pad1;   // cells beyond n_local inside a trial are padding
+        if (li0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > li0 ? a.n_local - li0 : 0)) - 1u;
         const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int p = 0; p < kPorts; ++p) st4(ring + (size_t)p * np, zero);
@@ -241,9 +245,10 @@ __device__ __forceinline__ void publish_and_wait(const PersistArgs& a, uint32_t 
 
 // Streams one CSR row [b, b+len) with a group of kSub threads into the ring.
 __device__ __forceinline__ void stream_row(const PersistArgs& a, unsigned long long b, unsigned long long en, uint32_t slot0,
-                                           uint32_t lane) {
+                                           uint32_t lane, uint32_t cell0) {
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
+    float* const ring = a.ring + cell0;
     unsigned long long k = b + lane;
     for (; k + 3ull * kSub < en; k += 4ull * kSub) {
         uint2 e[4];
@@ -253,7 +258,7 @@ __device__ __forceinline__ void stream_row(const PersistArgs& a, unsigned long l
         for (int u = 0; u < 4; ++u) {
             uint32_t slot = slot0 + (e[u].x >> (tb + 2));
             if (slot >= a.ring_slots) slot -= a.ring_slots;
-            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
+            atomicAdd(ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
                       __uint_as_float(e[u].y));
         }
     }
@@ -261,7 +266,7 @@ __device__ __forceinline__ void stream_row(const PersistArgs& a, unsigned long l
         const uint2 e = __ldg(&a.entries[k]);
         uint32_t slot = slot0 + (e.x >> (tb + 2));
         if (slot >= a.ring_slots) slot -= a.ring_slots;
-        atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+        atomicAdd(ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
     }
 }
 
@@ -291,10 +296,12 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, uint32_t pa
             const uint4 e = __ldcg(a.lists[parity] + idx);
             const unsigned long long b = ((unsigned long long)e.w << 32) | e.z;
             const unsigned long long step = win_base + (e.x >> kSrcBits);
+            uint32_t row, trial;
+            split_source(a.ids, e.x & kSrcMask, row, trial);
             if (lane == 0) events += e.y;
-            stream_row(a, b, b + e.y, (uint32_t)(step % a.ring_slots), lane);
+            stream_row(a, b, b + e.y, (uint32_t)(step % a.ring_slots), lane, trial * a.n_pad1);
         } else {
-            uint32_t src;
+            uint32_t src, row, trial;
             unsigned long long step;
             if (idx < n_rec + n_in) {
                 src = a.in_src[in_begin + idx - n_rec];
@@ -304,9 +311,10 @@ __device__ __forceinline__ void deliver_window(const PersistArgs& a, uint32_t pa
                 src = e & kSrcMask;
                 step = win_base + (e >> kSrcBits);
             }
-            const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
+            split_source(a.ids, src, row, trial);
+            const unsigned long long b = a.rowptr[row], en = a.rowptr[row + 1];
             if (lane == 0) events += en - b;
-            stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane);
+            stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane, trial * a.n_pad1);
         }
     }
     if (events) atomicAdd(&a.ctl->n_events, events);
@@ -371,7 +379,7 @@ __device__ __forceinline__ void deliver_window_multi(const PersistArgs& a, uint3
         }
         const unsigned long long b = a.rowptr[src], en = a.rowptr[src + 1];
         if (lane == 0) events += en - b;
-        stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane);
+        stream_row(a, b, en, (uint32_t)(step % a.ring_slots), lane, 0u);   // several ranks: one trial
     }
     if (events) atomicAdd(&a.ctl->n_events, events);
 }
@@ -490,19 +498,21 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
         }
 
         if (virt) {
-            for (uint32_t base = 0; base < a.n_virtual; base += nthreads) {
+            const uint32_t n_virt_all = a.n_virtual * a.n_trials;
+            for (uint32_t base = 0; base < n_virt_all; base += nthreads) {
                 const uint32_t v = base + ptid;
                 int k = 0;
-                if (v < a.n_virtual) {
-                    const uint4 thr = a.poisson_thr[v];
-                    const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), 0u, (uint32_t)a.seed,
+                if (v < n_virt_all) {
+                    const uint32_t trial = v / a.n_virtual, cell = v - trial * a.n_virtual;
+                    const uint4 thr = a.poisson_thr[cell];
+                    const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), trial, (uint32_t)a.seed,
                                                      (uint32_t)(a.seed >> 32)).x;
                     k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
                 }
                 if (__any_sync(0xffffffffu, k > 0)) {
                     uint32_t tot;
                     const uint32_t pos = warp_reserve(virt, k, &tot);
-                    const uint32_t e = (s_in_win << kSrcBits) | (a.n_global + v);
+                    const uint32_t e = (s_in_win << kSrcBits) | (a.ids.n_cells_all + v);
                     for (int j = 0; j < k; ++j) {
                         if (pos + j < a.virt_cap) virt[1 + pos + j] = e;
                         else atomicOr(&a.ctl->error_flags, kErrVirtListFull);

@@ -12,6 +12,8 @@ struct PersistArgs {
     const TypeConsts* types;
     int32_t n_types;
     uint32_t n_local, n_pad, lo, n_global;
+    uint32_t n_pad1, n_trials;   // cells per trial (padded) and number of trials sharing the CSR
+    IdSpace ids;
     float* ring;
     uint32_t ring_slots;
     Ctl* ctl;

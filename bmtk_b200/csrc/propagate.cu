@@ -23,6 +23,7 @@ constexpr int kMaxSeg = 16;
 struct Item {
     unsigned long long begin, end;
     uint32_t slot0;
+    uint32_t cell0;   // first cell of the spike's trial inside a ring plane
 };
 
 // Resolves work item `idx` (0 <= idx < total) to (source row, emitting step).
@@ -98,14 +99,16 @@ __global__ void __launch_bounds__(kPropThreads) propagate_atomic_kernel(const Pr
         // stage up to kStage items of this block
         if (threadIdx.x < kStage) {
             const uint32_t idx = first + threadIdx.x * gridDim.x;
-            Item it = {0ull, 0ull, 0u};
+            Item it = {0ull, 0ull, 0u, 0u};
             if (idx < total) {
-                uint32_t src;
+                uint32_t src, row, trial;
                 unsigned long long step;
                 resolve(a, s_map, step_base, idx, src, step);
-                it.begin = a.rowptr[src];
-                it.end = a.rowptr[src + 1];
+                split_source(a.ids, src, row, trial);
+                it.begin = a.rowptr[row];
+                it.end = a.rowptr[row + 1];
                 it.slot0 = (uint32_t)(step % a.ring_slots);
+                it.cell0 = trial * a.n_pad1;
             }
             s_items[threadIdx.x] = it;
         }
@@ -119,7 +122,7 @@ __global__ void __launch_bounds__(kPropThreads) propagate_atomic_kernel(const Pr
                 continue;
             }
             if (threadIdx.x == 0) my_events += it.end - it.begin;
-            float* ring0 = a.ring;
+            float* ring0 = a.ring + it.cell0;
             unsigned long long k = it.begin + threadIdx.x;
             // four independent loads in flight per thread
             for (; k + 3ull * kPropThreads < it.end; k += 4ull * kPropThreads) {

@@ -227,7 +227,9 @@ class Engine(object):
         return tr[:out.value]
 
     def state(self, var):
-        out = np.empty(self.n_local, dtype=np.float32)
+        """One trial: n_local values. Several trials: n_trials * n_pad1 values, trial-major."""
+        t = self.counter('trials')
+        out = np.empty(self.n_local if t == 1 else self.counter('n_pad'), dtype=np.float32)
         check(self._lib.bmtk_engine_get_state(self._h, var.encode(), _ptr(out)))
         return out
 

@@ -125,6 +125,10 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
 
 /* Options (before finalize unless noted):
  *  "deterministic"  0|1  sorted segmented reduction instead of atomics in spike delivery
+ *  "trials"         T >= 1 independent copies of the network that share the CSR (one rank, atomic
+ *                   delivery, Poisson cells only): cell c of trial t is id t*n_pad1 + c in spike records,
+ *                   probes and get_state (n_pad1 = counter "n_pad1" = n_local rounded up to 4), and Poisson
+ *                   cell v of trial t draws from Philox counter (v, step, t)
  *  "window"         steps per exchange window, 0 = min delay (default)
  *  "spike_capacity" entries of the per-window spike list, 0 = automatic
  *  "log_capacity"   entries of the device spike log between host drains

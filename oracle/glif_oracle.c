@@ -411,6 +411,18 @@ void orc_poisson_thresholds(double lambda, uint32_t thr[4])
     }
 }
 
+int32_t orc_poisson_count_stream(uint32_t source, uint64_t step, uint32_t stream, uint64_t seed, const uint32_t thr[4])
+{
+    /* counter = (source, step lo, step hi, stream): stream is the trial of a trial-batched run */
+    const uint32_t ctr[4] = { source, (uint32_t)step, (uint32_t)(step >> 32), stream };
+    const uint32_t key[2] = { (uint32_t)seed, (uint32_t)(seed >> 32) };
+    uint32_t out[4];
+    orc_philox4x32_10(ctr, key, out);
+    int32_t k = 0;
+    for (int j = 0; j < 4; ++j) k += out[0] >= thr[j];
+    return k;
+}
+
 int32_t orc_poisson_count(uint32_t source, uint64_t step, uint64_t seed, const uint32_t thr[4])
 {
     const uint32_t ctr[4] = { source, (uint32_t)step, (uint32_t)(step >> 32), 0u };
@@ -425,6 +437,25 @@ int32_t orc_poisson_count(uint32_t source, uint64_t step, uint64_t seed, const u
 /* All Poisson spikes of steps [step0, step0+n_steps) for n_virtual sources with per-source
  * thresholds thr[4*v..4*v+3], ordered by (step, source); a count of k gives k entries.
  * Returns the number of spikes (entries beyond cap are counted, not stored). */
+int64_t orc_poisson_fill_stream(int64_t n_virtual, const uint32_t* thr, uint64_t seed, uint32_t stream, int64_t step0,
+                                int64_t n_steps, int64_t cap, int64_t* emit_step, int32_t* source)
+{
+    int64_t n = 0;
+    for (int64_t s = step0; s < step0 + n_steps; ++s) {
+        for (int64_t v = 0; v < n_virtual; ++v) {
+            const int32_t k = orc_poisson_count_stream((uint32_t)v, (uint64_t)s, stream, seed, thr + 4 * v);
+            for (int32_t j = 0; j < k; ++j) {
+                if (n < cap) {
+                    emit_step[n] = s;
+                    source[n] = (int32_t)v;
+                }
+                ++n;
+            }
+        }
+    }
+    return n;
+}
+
 int64_t orc_poisson_fill(int64_t n_virtual, const uint32_t* thr, uint64_t seed, int64_t step0, int64_t n_steps,
                          int64_t cap, int64_t* emit_step, int32_t* source)
 {

@@ -148,6 +148,9 @@ def lib():
         _lib.orc_poisson_fill.argtypes = [C.c_int64, C.c_void_p, C.c_uint64, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_void_p, C.c_void_p]
         _lib.orc_poisson_fill.restype = C.c_int64
+        _lib.orc_poisson_fill_stream.argtypes = [C.c_int64, C.c_void_p, C.c_uint64, C.c_uint32, C.c_int64, C.c_int64,
+                                                 C.c_int64, C.c_void_p, C.c_void_p]
+        _lib.orc_poisson_fill_stream.restype = C.c_int64
         _lib.orc_csr_by_source.argtypes = [C.c_int64, C.c_int64] + [C.c_void_p] * 10
         _lib.orc_csr_by_source.restype = None
     return _lib
@@ -174,11 +177,11 @@ def poisson_thresholds(lam):
     return np.array(list(o), dtype=np.uint32)
 
 
-def poisson_spikes(rates_hz, dt, seed, step0, n_steps):
+def poisson_spikes(rates_hz, dt, seed, step0, n_steps, stream=0):
     """Host statement of the on-line Poisson sources: for every step n in [step0, step0+n_steps)
     and every source v, count = poisson_count(v, n, seed, thresholds(rate_v*dt/1000)); a source with
-    count k contributes k entries. Returns (emit_step int64[], source int32[]) ordered by
-    (step, source)."""
+    count k contributes k entries. `stream` is the fourth word of the Philox counter (the trial of a
+    trial-batched run; 0 otherwise). Returns (emit_step int64[], source int32[]) ordered by (step, source)."""
     L = lib()
     rates_hz = np.asarray(rates_hz, dtype=np.float64)
     thr = np.ascontiguousarray(np.concatenate([poisson_thresholds(r * dt * 1e-3) for r in rates_hz])
@@ -187,8 +190,8 @@ def poisson_spikes(rates_hz, dt, seed, step0, n_steps):
     while True:
         steps = np.zeros(cap, dtype=np.int64)
         srcs = np.zeros(cap, dtype=np.int32)
-        n = L.orc_poisson_fill(len(rates_hz), _ptr(thr), int(seed), int(step0), int(n_steps), cap,
-                               _ptr(steps), _ptr(srcs))
+        n = L.orc_poisson_fill_stream(len(rates_hz), _ptr(thr), int(seed), int(stream), int(step0), int(n_steps), cap,
+                                      _ptr(steps), _ptr(srcs))
         if n <= cap:
             return steps[:n].copy(), srcs[:n].copy()
         cap = int(n)

@@ -82,3 +82,49 @@ def test_c2_reduced_against_oracle(cabi, deterministic):
     assert all(x[0] == y[0] and abs(x[1] - y[1]) <= 1 for x, y in zip(a, b))
     rg, rc = rates_by_type(net, ids, 400.0), rates_by_type(net, r['spike_id'], 400.0)
     assert np.all(np.abs(rg - rc) <= 0.02 * rc + 0.15), (rg, rc)
+
+
+def test_trial_batching_shares_the_csr(cabi, oracle):
+    """Option "trials": T independent copies of a network over ONE CSR, each with its own Philox stream
+    (counter word 3 = trial). Every trial must reproduce the oracle run of that trial's input stream
+    (spikes within one step over the first 100 ms, then until the first divergence), the trials must
+    differ from each other, and events / input spikes must add up exactly over the trials."""
+    T = 5
+    net = W.c2(n=3000, in_degree=150, n_virtual=150, t_stop_ms=300.0, input_weight=90.0)
+    eng = W.build_engine(net, record_vm=False, options=dict(trials=T))
+    assert eng.counter('trials') == T and eng.csr_info()['n_edges'] == net.n_edges
+    eng.run(net.n_steps)
+    st, ids = eng.fetch_spikes()
+    st, ids = st.astype(np.int64), ids.astype(np.int64)
+    n_pad1 = eng.counter('n_pad1')
+    trial, cell = ids // n_pad1, ids % n_pad1
+    assert cell.max() < net.n_neurons and set(np.unique(trial)) == set(range(T))
+    rowptr = eng.csr()[0].astype(np.int64)
+    outdeg = np.diff(rowptr)
+    n_inputs, events = 0, 0
+    trains = []
+    for t in range(T):
+        steps, srcs = oracle.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, net.n_steps, stream=t)
+        n_inputs += len(steps)
+        m = trial == t
+        events += int(outdeg[cell[m]].sum() + outdeg[net.n_neurons + srcs].sum())
+        sim = oracle_from_network(net)
+        sim.set_input_spikes(steps, srcs)
+        r = sim.run(net.n_steps)
+        div = _first_divergence(st[m], cell[m], r['spike_step'], r['spike_id'])
+        assert div > 300, (t, div)
+        a = sorted(zip(cell[m][st[m] <= 1000].tolist(), st[m][st[m] <= 1000].tolist()))
+        b = sorted(zip(r['spike_id'][r['spike_step'] <= 1000].tolist(), r['spike_step'][r['spike_step'] <= 1000].tolist()))
+        assert len(a) == len(b) and all(x[0] == y[0] and abs(x[1] - y[1]) <= 1 for x, y in zip(a, b))
+        trains.append((st[m], cell[m]))
+    assert eng.counter('input_spikes') == n_inputs
+    assert eng.counter('events') == events
+    assert not (len(trains[0][0]) == len(trains[1][0]) and np.array_equal(trains[0][0], trains[1][0]))
+    # per-step kernels give the same early spikes as the persistent kernel
+    e2 = W.build_engine(net, record_vm=False, options=dict(trials=T, persistent=0))
+    e2.run(1200)
+    s2, i2 = e2.fetch_spikes()
+    m = st <= 1200
+    assert _first_divergence(st[m], ids[m], s2.astype(np.int64), i2.astype(np.int64)) > 300
+    U = eng.state('U')
+    assert U.shape == (T * n_pad1,)
