@@ -56,6 +56,10 @@ def parse_args():
     ap.add_argument('--no-cpu', action='store_true')
     ap.add_argument('--cpu-slice-ms', type=float, default=250.0)
     ap.add_argument('--step-ms', type=float, default=1000.0, help='simulated ms per bench step (1000 = the configuration)')
+    ap.add_argument('--workload', default='c3', choices=['c3', 'c4'],
+                    help='c3: the V1-scale network (the headline line). c4: trial sweep, the 50 000-neuron E/I network as 64 '
+                         'independent trials over one CSR, trials sharded over the ranks, one step = 500 ms')
+    ap.add_argument('--trials', type=int, default=64)
     ap.add_argument('--exchange', default='p2p', choices=['p2p', 'nccl'],
                     help='several ranks: spike exchange inside the persistent kernel over peer memory, or one NCCL '
                          'all-gather per window around the per-step kernels')
@@ -239,6 +243,11 @@ def main():
         dist.all_reduce(t, op=op)
         return float(t.item())
 
+    if args.workload == 'c4':
+        trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, reduce, json_fd)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     n_total = int(round(230924 * args.scale))
     bounds = np.linspace(0, n_total, world + 1).astype(np.int64)
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
@@ -430,6 +439,85 @@ def main():
         reduce_edges(net, world, dist, dev)
     if world > 1:
         dist.destroy_process_group()
+
+
+def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, reduce, json_fd):
+    """Workload c4. Every rank holds the whole CSR and runs trials [rank*T/N, (rank+1)*T/N) of the sweep:
+    independent replicas, no collective on the data path (strong scaling: the sweep is fixed)."""
+    T = args.trials
+    if T % world:
+        raise SystemExit('--trials must be a multiple of the number of ranks')
+    t_loc = T // world
+    step_ms = 500.0 if args.step_ms == 1000.0 else args.step_ms
+    n = int(round(50000 * args.scale))
+    net = W.c4(n=n, in_degree=min(1000, n // 4), n_virtual=max(8, int(round(2000 * args.scale))), t_stop_ms=step_ms)
+    n_steps = int(round(step_ms / net.dt))
+    eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
+                         options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000))
+    MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
+    for _ in range(args.warmup):
+        eng.run(n_steps)
+        eng.fetch_spikes()
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, sp0, l0 = eng.counter('events'), eng.counter('spikes'), eng.counter('launches')
+    eng.mark(0)
+    for _ in range(args.steps):
+        eng.run(n_steps)
+    eng.mark(1)
+    dev_ms = eng.elapsed_ms(0, 1)
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    eng.fetch_spikes()
+    dev_ms = reduce(dev_ms, MAX)
+    events = reduce(eng.counter('events') - ev0, SUM)
+    spikes = reduce(eng.counter('spikes') - sp0, SUM)
+    launches = reduce(eng.counter('launches') - l0, SUM)
+    # end to end: the Poisson cells live on the device, so a step's host traffic is its spike list
+    torch.cuda.synchronize()
+    barrier()
+    e0, d2h = eng.counter('events'), 0
+    t0 = time.time()
+    for _ in range(args.steps):
+        eng.run(n_steps)
+        st, ids = eng.fetch_spikes()
+        d2h += 8 * len(st)
+    torch.cuda.synchronize()
+    barrier()
+    wall = reduce(time.time() - t0, MAX)
+    e2e_events = reduce(eng.counter('events') - e0, SUM)
+    n_pad, window = eng.counter('n_pad'), eng.counter('window')
+    eng.close()
+    peak, peak_kind = peaks()
+    alg_bytes = BYTES_PER_NEURON_STEP * n_pad * world * n_steps * args.steps + BYTES_PER_EVENT * events
+    if rank == 0:
+        line = {
+            'metric': 'synaptic_events_per_sec', 'value': events / (dev_ms * 1e-3), 'unit': 'events/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dev_ms / args.steps, 'higher_is_better': True,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'sim_ms_per_wall_ms': step_ms * T * args.steps / dev_ms,
+            'config': {'workload': 'c4: %d trials of the %d-neuron E/I network (%d synapses, one CSR per GPU), %d Poisson '
+                                   'cells per trial on their own Philox streams, dt 0.1 ms' % (T, n, net.n_edges, net.n_virtual),
+                       'step': '%g ms of simulated time in every trial = %d update steps' % (step_ms, n_steps),
+                       'partition': '%d trials per GPU, no exchange between GPUs' % t_loc,
+                       'l2': 'state + ring of %d trials exceed L2' % t_loc, 'window_steps': window,
+                       'mean_rate_hz': spikes / (n * T) / (step_ms * 1e-3 * args.steps)},
+            'clocks': clocks,
+            'e2e': {'value': e2e_events / wall, 'unit': 'events/s', 'h2d_bytes_per_step': 0,
+                    'd2h_bytes_per_step': int(reduce(d2h, SUM) / args.steps),
+                    'timing': 'wall clock; inputs are device-generated Poisson cells, every step reads its spike list back'},
+            'gpu_launches': int(launches),
+            'roofline': {'kernel': 'persistent_kernel (update + delivery)', 'bound': 'hbm',
+                         'achieved': alg_bytes / world / (dev_ms * 1e6), 'peak': peak, 'unit': 'GB/s',
+                         'frac': alg_bytes / world / (dev_ms * 1e6) / peak, 'traffic': None, 'peak_kind': peak_kind,
+                         'note': 'algorithmic bytes per GPU = 128 B per neuron-step + 16 B per event, over the whole timed region'},
+            'cpu_baseline': None,
+        }
+        os.write(json_fd, (json.dumps(line) + '\n').encode())
+    else:
+        reduce(d2h, SUM)
 
 
 def reduce_edges(net, world, dist, dev):

@@ -115,6 +115,7 @@ struct UpdateArgs {
     // on-line Poisson sources (nullptr = none)
     const uint4* poisson_thr; // per virtual source: CDF thresholds of k = 0..3
     uint32_t n_virtual, n_global, n_trials;
+    uint32_t trial_base;      // Philox stream of local trial 0 (trials sharded over engines)
     uint64_t seed;
     uint32_t* virt;           // [0] = count, then entries, same packing as `send`
     uint32_t virt_cap;

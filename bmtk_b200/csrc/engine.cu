@@ -214,7 +214,7 @@ struct bmtk_engine {
 
     // nodes
     uint64_t n_global = 0, lo = 0, n_local = 0, n_virtual = 0;
-    uint32_t n_pad = 0, n_pad1 = 0, n_trials = 1;
+    uint32_t n_pad = 0, n_pad1 = 0, n_trials = 1, trial_base = 0;
     std::vector<uint16_t> type_index;
     std::vector<bmtk_glif_params> types;
     bool has_theta = false;
@@ -355,6 +355,7 @@ static UpdateArgs make_update_args(bmtk_engine* e, uint32_t s) {
     a.n_pad1 = e->n_pad1;
     a.ids = make_ids(e);
     a.n_trials = e->n_trials;
+    a.trial_base = e->trial_base;
     a.lo = (uint32_t)e->lo;
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
@@ -685,6 +686,7 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.n_global = (uint32_t)e->n_global;
     a.n_pad1 = e->n_pad1;
     a.n_trials = e->n_trials;
+    a.trial_base = e->trial_base;
     a.ids = make_ids(e);
     a.ring = e->ring;
     a.ring_slots = e->ring_slots;
@@ -990,6 +992,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
         if (value < 1 || value > 4096) return fail(BMTK_E_INVALID, "trials must be 1..4096");
         e->n_trials = (uint32_t)value;
     }
+    else if (k == "trial_base") e->trial_base = (uint32_t)value;
     else if (k == "window") e->window_opt = (uint32_t)value;
     else if (k == "spike_capacity") e->spike_cap_opt = (uint64_t)value;
     else if (k == "log_capacity") e->log_cap = std::max<uint64_t>(1024, (uint64_t)value);

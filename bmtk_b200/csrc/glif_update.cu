@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(kUpdateThreads) glif_update_kernel(const Updat
         if (v < a.n_virtual * a.n_trials) {
             const uint32_t trial = v / a.n_virtual, cell = v - trial * a.n_virtual;
             const uint4 thr = a.poisson_thr[cell];
-            const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), trial, (uint32_t)a.seed,
+            const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base + trial,
+                                             (uint32_t)a.seed,
                                              (uint32_t)(a.seed >> 32)).x;
             k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
             e = (a.step_in_window << kSrcBits) | (a.ids.n_cells_all + v);

@@ -505,7 +505,8 @@ __global__ void __launch_bounds__(kPT, 1) persistent_kernel(const PersistArgs a)
                 if (v < n_virt_all) {
                     const uint32_t trial = v / a.n_virtual, cell = v - trial * a.n_virtual;
                     const uint4 thr = a.poisson_thr[cell];
-                    const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), trial, (uint32_t)a.seed,
+                    const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base + trial,
+                                                     (uint32_t)a.seed,
                                                      (uint32_t)(a.seed >> 32)).x;
                     k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
                 }

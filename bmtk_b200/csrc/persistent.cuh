@@ -13,6 +13,7 @@ struct PersistArgs {
     int32_t n_types;
     uint32_t n_local, n_pad, lo, n_global;
     uint32_t n_pad1, n_trials;   // cells per trial (padded) and number of trials sharing the CSR
+    uint32_t trial_base;         // Philox stream of local trial 0
     IdSpace ids;
     float* ring;
     uint32_t ring_slots;

@@ -9,6 +9,7 @@ excitatory/inhibitory class of source and target, virtual Poisson cells as input
   c1  10 000 unconnected neurons, one current step each (0..300 pA)
   c2  50 000 E/I neurons, fixed in-degree 1000
   c3  230 924 neurons / 17 types on a disk, Gaussian distance rule, ~70 M edges
+  c4  the c2 network as 64 independent trials over one CSR (per-trial Poisson streams)
 
 Every generator works target block by target block with its own child seed, so a rank that
 owns neurons [lo, hi) generates exactly its own edges and all ranks agree on the network.
@@ -198,12 +199,13 @@ def c1(n=10000, t_stop_ms=1500.0, dt=0.05, seed=1235):
 
 
 def c2(n=50000, in_degree=1000, t_stop_ms=1000.0, dt=0.1, seed=1236, n_virtual=2000, lo=0, hi=None,
-       input_weight=30.0, poisson_online=True, w_scale=1.0):
+       input_weight=120.0, poisson_online=True, w_scale=1.0):
     """E/I network: 80 % excitatory / 20 % inhibitory in 4 types each, every neuron receives
     exactly `in_degree` synapses from uniformly drawn sources (no self loops, multapses allowed),
     weights lognormal(ln 1.5, 0.6) pA with inhibitory sources scaled by -4, delays uniform
     0.8-3.0 ms on the dt grid, ports uniform over the 4 receptors; `n_virtual` Poisson cells at
-    10 Hz with out-degree 200 (scaled with n)."""
+    10 Hz with out-degree 200 (scaled with n). The configuration leaves the input weight open: 120 pA
+    puts the full-size network at about 6 Hz per neuron."""
     hi = n if hi is None else hi
     rng = np.random.default_rng(seed)
     net = Network('c2', dt, round(t_stop_ms / dt))
@@ -243,6 +245,15 @@ def c2(n=50000, in_degree=1000, t_stop_ms=1000.0, dt=0.1, seed=1236, n_virtual=2
     else:
         net.in_virt, net.in_stamp = _poisson_trains(np.random.default_rng(4323), rates, t_stop_ms, dt)
     net.probe_ids = np.linspace(lo, hi - 1, 16).astype(np.uint32)
+    return net
+
+
+def c4(n=50000, in_degree=1000, t_stop_ms=500.0, dt=0.1, trials=64, **kw):
+    """Trial sweep: the c2 network simulated as `trials` independent trials that share one CSR, each
+    with its own Philox stream for the Poisson cells (engine option "trials"); 500 ms."""
+    net = c2(n=n, in_degree=in_degree, t_stop_ms=t_stop_ms, dt=dt, poisson_online=True, **kw)
+    net.name = 'c4'
+    net.meta = dict(trials=int(trials))
     return net
 
 

@@ -129,6 +129,8 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
  *                   delivery, Poisson cells only): cell c of trial t is id t*n_pad1 + c in spike records,
  *                   probes and get_state (n_pad1 = counter "n_pad1" = n_local rounded up to 4), and Poisson
  *                   cell v of trial t draws from Philox counter (v, step, t)
+ *  "trial_base"     Philox stream of local trial 0 (default 0), so that several engines can each take a
+ *                   slice of one trial sweep
  *  "window"         steps per exchange window, 0 = min delay (default)
  *  "spike_capacity" entries of the per-window spike list, 0 = automatic
  *  "log_capacity"   entries of the device spike log between host drains
