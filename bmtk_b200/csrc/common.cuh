@@ -60,6 +60,7 @@ struct Ctl {
     // persistent kernel, option "profile": device-timer totals of the two phases of every window
     unsigned long long t_update_ns, t_prop_ns, n_windows;
     unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
+    unsigned long long t_dbg[4];                 // pipelined kernel: finer split of block 0's phases
 };
 
 // Trial batching: T independent copies ("trials") of one network share its CSR. Cell c of trial t has

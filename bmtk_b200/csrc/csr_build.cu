@@ -47,9 +47,21 @@ __global__ void fill_u64_kernel(unsigned long long* p, uint64_t n, unsigned long
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
 }
 
-__global__ void pack_log_kernel(uint32_t n, const uint32_t* stamp, const uint32_t* id, unsigned long long* keys) {
+// spike log: key = (stamp - stamp_base) << id_bits | id, so that the sort runs over the bits in use only
+__global__ void pack_log_kernel(uint32_t n, const uint32_t* stamp, const uint32_t* id, uint32_t stamp_base, uint32_t id_bits,
+                                unsigned long long* keys) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) keys[i] = ((unsigned long long)stamp[i] << 32) | id[i];
+    if (i < n) keys[i] = ((unsigned long long)(stamp[i] - stamp_base) << id_bits) | id[i];
+}
+
+__global__ void unpack_log_kernel(uint32_t n, const unsigned long long* keys, uint32_t stamp_base, uint32_t id_bits,
+                                  uint32_t* stamp, uint32_t* id) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const unsigned long long k = keys[i];
+        stamp[i] = (uint32_t)(k >> id_bits) + stamp_base;
+        id[i] = (uint32_t)(k & ((1ull << id_bits) - 1ull));
+    }
 }
 
 size_t spike_log_sort_tmp_bytes(uint32_t capacity) {
@@ -59,13 +71,19 @@ size_t spike_log_sort_tmp_bytes(uint32_t capacity) {
     return bytes + 16;
 }
 
-cudaError_t sort_spike_log(uint32_t n, const uint32_t* d_stamp, const uint32_t* d_id, unsigned long long* d_keys,
-                           unsigned long long* d_keys_out, void* tmp, size_t tmp_bytes, cudaStream_t stream) {
+cudaError_t sort_spike_log(uint32_t n, uint32_t* d_stamp, uint32_t* d_id, uint32_t stamp_base, uint32_t stamp_bits,
+                           uint32_t id_bits, unsigned long long* d_keys, unsigned long long* d_keys_out, void* tmp,
+                           size_t tmp_bytes, cudaStream_t stream) {
     if (n == 0) return cudaSuccess;
-    pack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_stamp, d_id, d_keys);
+    pack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_stamp, d_id, stamp_base, id_bits, d_keys);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return cub::DeviceRadixSort::SortKeys(tmp, tmp_bytes, d_keys, d_keys_out, (int)n, 0, 64, stream);
+    int end_bit = (int)(stamp_bits + id_bits);
+    if (end_bit > 64) end_bit = 64;
+    e = cub::DeviceRadixSort::SortKeys(tmp, tmp_bytes, d_keys, d_keys_out, (int)n, 0, end_bit, stream);
+    if (e != cudaSuccess) return e;
+    unpack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_keys_out, stamp_base, id_bits, d_stamp, d_id);
+    return cudaGetLastError();
 }
 
 #define CSR_CHECK(x)                      \

@@ -12,11 +12,14 @@ cudaError_t build_csr_device(uint64_t n_rows, uint64_t n_edges, const uint32_t* 
                              uint32_t target_bits, cudaStream_t stream, unsigned long long** d_rowptr_out,
                              uint2** d_entries_out);
 
-// Sorts the first n entries of the device spike log by (stamp, id): packs them into 64-bit keys,
-// radix-sorts (CUB) and leaves the sorted keys (stamp << 32 | id) in d_keys_out. tmp/tmp_bytes is
-// caller-provided scratch of at least spike_log_sort_tmp_bytes(capacity) bytes.
+// Sorts the first n entries of the device spike log (d_stamp, d_id) by (stamp, id) in place: packs
+// them into keys (stamp - stamp_base) << id_bits | id, radix-sorts (CUB) over the stamp_bits + id_bits
+// bits in use and unpacks the sorted keys back into the two arrays. Every stamp must be in
+// [stamp_base, stamp_base + 2^stamp_bits) and every id below 2^id_bits. d_keys / d_keys_out hold n keys
+// each; tmp/tmp_bytes is caller-provided scratch of at least spike_log_sort_tmp_bytes(capacity) bytes.
 size_t spike_log_sort_tmp_bytes(uint32_t capacity);
-cudaError_t sort_spike_log(uint32_t n, const uint32_t* d_stamp, const uint32_t* d_id, unsigned long long* d_keys,
-                           unsigned long long* d_keys_out, void* tmp, size_t tmp_bytes, cudaStream_t stream);
+cudaError_t sort_spike_log(uint32_t n, uint32_t* d_stamp, uint32_t* d_id, uint32_t stamp_base, uint32_t stamp_bits,
+                           uint32_t id_bits, unsigned long long* d_keys, unsigned long long* d_keys_out, void* tmp,
+                           size_t tmp_bytes, cudaStream_t stream);
 
 }  // namespace bmtk

@@ -13,7 +13,10 @@
 
 #include "common.cuh"
 #include "csr_build.cuh"
+#include <chrono>
+
 #include "persistent.cuh"
+#include "pipeline.cuh"
 #include "propagate_det.cuh"
 
 namespace bmtk {
@@ -280,12 +283,14 @@ struct bmtk_engine {
     std::vector<float> h_trace;
 
     // host store of recorded spikes: keys stamp << 32 | id, sorted (every drain appends a later, sorted run)
-    std::vector<unsigned long long> h_spk_keys;
+    // recorded spikes, (stamp, id)-sorted, in pinned host memory that grows by doubling
+    uint32_t* h_spk_stamp = nullptr;
+    uint32_t* h_spk_id = nullptr;
+    size_t h_spk_n = 0, h_spk_cap = 0;
+    uint64_t log_base_step = 0;       // every stamp in the device log is greater than this
     unsigned long long *d_log_keys = nullptr, *d_log_keys2 = nullptr;
     void* d_log_tmp = nullptr;
     size_t log_tmp_bytes = 0;
-    unsigned long long* h_pinned_keys = nullptr;   // pinned staging for the device-to-host copy
-    size_t h_pinned_cap = 0;
     uint64_t step = 0;
     uint64_t launches = 0;
     uint64_t events_total = 0, spikes_total = 0, input_spikes_total = 0;
@@ -304,6 +309,11 @@ struct bmtk_engine {
     bool persistent = true, phase_timers = false, ring_prefetch = false;
     int persist_blocks = 0;
     bool persist_resident = false;
+    uint4* d_pipe_seg = nullptr;
+    uint32_t* d_pipe_cnt = nullptr;
+    bool pipeline = true;     // option: use the pipelined kernel where it applies
+    bool pipe_ok = false;     // resident state, one trial, min delay >= 2 steps
+    int pipe_blocks = 0;
     uint32_t* d_virt2 = nullptr;
     uint4* d_plists[2] = {nullptr, nullptr};
     uint32_t* d_plist_counts = nullptr;
@@ -318,6 +328,8 @@ struct bmtk_engine {
     std::vector<uint64_t> ce_group_step;
     size_t ce_group_next = 0;
     double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
+    double phase_dbg[4] = {0, 0, 0, 0};
+    double drain_wait_ns = 0, drain_sort_ns = 0;   // host clock: waiting for the chunk's kernels; sorting + copying its spike log
     uint64_t phase_windows = 0;
 
     DetWorkspace det{};
@@ -586,10 +598,18 @@ static int upload_inputs(bmtk_engine* e) {
 }
 
 // Brings counters, spike log and traces of the finished chunk to the host.
+static double now_ns() {
+    return (double)std::chrono::duration_cast<std::chrono::nanoseconds>(
+               std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
 static int drain(bmtk_engine* e) {
     Ctl h{};
+    const double t0 = now_ns();
     CU(cudaMemcpyAsync(&h, e->d_ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, e->stream));
     CU(cudaStreamSynchronize(e->stream));
+    const double t1 = now_ns();
+    e->drain_wait_ns += t1 - t0;
     e->events_total = h.n_events;
     e->spikes_total = h.n_spikes;
     e->input_spikes_total = h.n_input_spikes;
@@ -599,7 +619,8 @@ static int drain(bmtk_engine* e) {
         e->phase_windows += h.n_windows;
         e->phase_sync1_ns += (double)h.t_sync1_ns;
         e->phase_sync2_ns += (double)h.t_sync2_ns;
-        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 40, e->stream));
+        for (int q = 0; q < 4; ++q) e->phase_dbg[q] += (double)h.t_dbg[q];
+        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 72, e->stream));
     }
     if (h.step_base != e->step)
         return fail(BMTK_E_INVALID, "device clock %llu differs from host clock %llu", (unsigned long long)h.step_base,
@@ -627,7 +648,8 @@ static int drain(bmtk_engine* e) {
         CU(cudaMemsetAsync(&e->d_ctl->error_flags, 0, 4, e->stream));
         if (f & kErrSpikeListFull)
             return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank; the persistent kernel also holds "
-                        "at most 4096 spikes per block and window): raise option spike_capacity or set persistent = 0",
+                        "at most 4096 spikes per block and window, the pipelined kernel 2048 per block and phase): raise option "
+                        "spike_capacity, or set pipeline = 0 or persistent = 0",
                         e->send_cap);
         if (f & kErrExchangeTimeout)
             return fail(BMTK_E_COMM, "spike exchange timed out: a rank did not publish its window within ~1 s "
@@ -642,22 +664,37 @@ static int drain(bmtk_engine* e) {
     if (e->record_spikes && h.log_count) {
         // sort the chunk's spikes by (stamp, id) on the device; chunks are consecutive in time, so the
         // host store stays sorted by appending
-        const size_t n0 = e->h_spk_keys.size(), n = h.log_count;
-        CU(sort_spike_log((uint32_t)n, e->d_log_stamp, e->d_log_id, e->d_log_keys, e->d_log_keys2, e->d_log_tmp,
-                          e->log_tmp_bytes, e->stream));
-        e->launches += 2;
-        if (e->h_pinned_cap < n) {
-            if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
-            e->h_pinned_keys = nullptr;
-            e->h_pinned_cap = std::max<size_t>(n * 2, 1u << 16);
-            CU(cudaMallocHost(&e->h_pinned_keys, 8 * e->h_pinned_cap));
+        const size_t n0 = e->h_spk_n, n = h.log_count;
+        auto bits_for = [](uint64_t v) { uint32_t b = 1; while (b < 64 && (v >> b)) ++b; return b; };
+        const uint32_t stamp_bits = bits_for(e->step - e->log_base_step + 1);
+        const uint32_t id_bits = bits_for(std::max<uint64_t>(e->n_global, e->n_pad));
+        CU(sort_spike_log((uint32_t)n, e->d_log_stamp, e->d_log_id, (uint32_t)e->log_base_step, stamp_bits, id_bits,
+                          e->d_log_keys, e->d_log_keys2, e->d_log_tmp, e->log_tmp_bytes, e->stream));
+        e->launches += 3;
+        if (e->h_spk_cap < n0 + n) {
+            const size_t cap = std::max<size_t>((n0 + n) * 2, 1u << 16);
+            uint32_t *ns = nullptr, *ni = nullptr;
+            CU(cudaMallocHost(&ns, 4 * cap));
+            CU(cudaMallocHost(&ni, 4 * cap));
+            if (n0) {
+                std::memcpy(ns, e->h_spk_stamp, 4 * n0);
+                std::memcpy(ni, e->h_spk_id, 4 * n0);
+            }
+            if (e->h_spk_stamp) cudaFreeHost(e->h_spk_stamp);
+            if (e->h_spk_id) cudaFreeHost(e->h_spk_id);
+            e->h_spk_stamp = ns;
+            e->h_spk_id = ni;
+            e->h_spk_cap = cap;
         }
-        CU(cudaMemcpyAsync(e->h_pinned_keys, e->d_log_keys2, 8 * n, cudaMemcpyDeviceToHost, e->stream));
+        // straight into the host store: chunks are consecutive in time, so it stays (stamp, id)-sorted
+        CU(cudaMemcpyAsync(e->h_spk_stamp + n0, e->d_log_stamp, 4 * n, cudaMemcpyDeviceToHost, e->stream));
+        CU(cudaMemcpyAsync(e->h_spk_id + n0, e->d_log_id, 4 * n, cudaMemcpyDeviceToHost, e->stream));
         CU(cudaMemsetAsync(&e->d_ctl->log_count, 0, 4, e->stream));
         CU(cudaStreamSynchronize(e->stream));
-        e->h_spk_keys.resize(n0 + n);
-        std::memcpy(e->h_spk_keys.data() + n0, e->h_pinned_keys, 8 * n);
+        e->h_spk_n = n0 + n;
+        e->drain_sort_ns += now_ns() - t1;
     }
+    e->log_base_step = e->step;
     if (!e->probe_ids.empty()) {
         const uint64_t have = e->step / e->probe_interval;
         const uint64_t n_new = have - e->samples_drained;
@@ -733,7 +770,15 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.xchg_cap = e->send_cap;
     a.seq0 = e->xchg_seq;
     for (int r = 0; r < e->n_ranks; ++r) a.peers[r] = e->xchg_peers[r];
-    CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
+    if (e->pipeline && e->pipe_ok && e->n_ranks == 1) {
+        a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
+        a.pipe_seg = e->d_pipe_seg;
+        a.pipe_cnt = e->d_pipe_cnt;
+        a.pipe_seg_cap = kPipeSegCap;
+        CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
+    } else {
+        CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
+    }
     ++e->launches;
     e->step += n;
     e->xchg_seq += (n + e->window - 1) / e->window;
@@ -846,8 +891,11 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     for (int r = 0; r < e->n_ranks && r < (int)kXRanks; ++r)
         if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r]);
     cudaFree(e->d_xchg);
+    cudaFree(e->d_pipe_seg);
+    cudaFree(e->d_pipe_cnt);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
-    if (e->h_pinned_keys) cudaFreeHost(e->h_pinned_keys);
+    if (e->h_spk_stamp) cudaFreeHost(e->h_spk_stamp);
+    if (e->h_spk_id) cudaFreeHost(e->h_spk_id);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return BMTK_OK;
@@ -978,6 +1026,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     if (k == "profile") { e->profile = value != 0; return BMTK_OK; }
     if (k == "use_graph") { e->use_graph = value != 0; return BMTK_OK; }
     if (k == "persistent") { e->persistent = value != 0; return BMTK_OK; }
+    if (k == "pipeline") { e->pipeline = value != 0; return BMTK_OK; }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
     if (k == "chunk_steps") {
@@ -1251,6 +1300,27 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
         if (!coop || blocks > 512) e->persist_blocks = 0;
+        if (e->persist_blocks > 0 && e->n_trials == 1 && e->window >= 2 && e->n_edges < (1ull << 32)) {
+            const int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt));
+            if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
+                // chunks of 32 groups are dealt round-robin to the update warps of the blocks
+                const uint64_t chunks = ((uint64_t)(e->n_pad / 4) + 31) / 32;
+                e->pipe_ok = (chunks + pb - 1) / pb <= pipelined_update_threads() / 32;
+                e->pipe_blocks = pb;
+                if (e->has_poisson) {
+                    // a block adds its share of the Poisson spikes to its segment of the phase list: leave half for neurons
+                    double lam = 0.0;
+                    for (uint64_t v = 0; v < e->n_virtual; ++v) lam += (double)e->poisson_rates[v] * e->dt * 1e-3;
+                    const double per_block = lam * (e->window / 2) / pb;
+                    if (per_block * 4.0 + 64.0 > (double)kPipeSegCap / 2) e->pipe_ok = false;
+                }
+                if (e->pipe_ok) {
+                    CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
+                    CU(cudaMalloc(&e->d_pipe_cnt, 4 * 3 * (size_t)pb));
+                    CU(cudaMemset(e->d_pipe_cnt, 0, 4 * 3 * (size_t)pb));
+                }
+            }
+        }
         if (e->persist_blocks > 0) {
             for (int q = 0; q < 2; ++q) CU(cudaMalloc(&e->d_plists[q], sizeof(uint4) * (size_t)e->send_cap));
             CU(cudaMalloc(&e->d_plist_counts, 8));
@@ -1281,23 +1351,23 @@ int bmtk_engine_run(bmtk_engine* e, uint64_t n_steps) {
 
 int bmtk_engine_spike_count(bmtk_engine* e, uint64_t* n) {
     if (!e || !n) return fail(BMTK_E_INVALID, "NULL argument");
-    *n = e->h_spk_keys.size();
+    *n = e->h_spk_n;
     return BMTK_OK;
 }
 
 int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step, uint32_t* id, uint64_t* n_out) {
     if (!e || !n_out) return fail(BMTK_E_INVALID, "NULL argument");
-    const size_t n = e->h_spk_keys.size();
+    const size_t n = e->h_spk_n;
     if (cap < n) return fail(BMTK_E_INVALID, "fetch_spikes: capacity %llu < %llu spikes", (unsigned long long)cap,
                              (unsigned long long)n);
     if (n && (!stamp_step || !id)) return fail(BMTK_E_INVALID, "fetch_spikes: NULL array");
     // already in canonical (stamp, id) order: sorted per chunk on the device, chunks consecutive in time
-    for (size_t i = 0; i < n; ++i) {
-        stamp_step[i] = (uint32_t)(e->h_spk_keys[i] >> 32);
-        id[i] = (uint32_t)e->h_spk_keys[i];
+    if (n) {
+        std::memcpy(stamp_step, e->h_spk_stamp, 4 * n);
+        std::memcpy(id, e->h_spk_id, 4 * n);
     }
     *n_out = n;
-    e->h_spk_keys.clear();
+    e->h_spk_n = 0;
     return BMTK_OK;
 }
 
@@ -1623,7 +1693,8 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
         const uint32_t s32 = (uint32_t)e->samples_drained;
         CU(cudaMemcpy(&e->d_ctl->sample_base, &s32, 4, cudaMemcpyHostToDevice));
     }
-    e->h_spk_keys.clear();
+    e->h_spk_n = 0;
+    e->log_base_step = e->step;
     e->h_trace.clear();
     // replayed inputs handed over before the load are re-indexed from the restored step
     return BMTK_OK;
@@ -1670,8 +1741,12 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "phase_windows") *out = e->phase_windows;
     else if (k == "phase_sync1_ns") *out = (uint64_t)e->phase_sync1_ns;
     else if (k == "phase_sync2_ns") *out = (uint64_t)e->phase_sync2_ns;
+    else if (k == "drain_wait_ns") *out = (uint64_t)e->drain_wait_ns;
+    else if (k == "drain_sort_ns") *out = (uint64_t)e->drain_sort_ns;
+    else if (k.rfind("phase_dbg", 0) == 0 && k.size() == 10 && k[9] >= '0' && k[9] <= '3') *out = (uint64_t)e->phase_dbg[k[9] - '0'];
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
+    else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && e->n_ranks == 1) ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else if (k == "n_pad1") *out = e->n_pad1;
     else if (k == "trials") *out = e->n_trials;

@@ -63,52 +63,52 @@ struct Neuron4 {
     }
 
     // One step for the four neurons with ring input in[port]. Returns the spike mask (bit j).
+    // Written without branches: both the refractory and the integrating update are evaluated and
+    // the result selected, so that the four neurons' dependency chains (and their loads of the
+    // type constants) interleave instead of running one after the other.
     __device__ __forceinline__ uint32_t step(const TypeConsts* types, const F4 (&in)[kPorts]) {
         uint32_t mask = 0;
 #pragma unroll
         for (int j = 0; j < kNeuronsPerThread; ++j) {
             const TypeConsts& c = types[ty[j]];
-            float u = U.v[j];
-            if (rf[j] > 0) {
-                // refractory: V is held; glif_psc resets on the step the countdown ends
-                if (--rf[j] == 0) {
-                    a0.v[j] = c.asc_amps[0] + a0.v[j] * c.asc_refr[0];
-                    a1.v[j] = c.asc_amps[1] + a1.v[j] * c.asc_refr[1];
-                    if (THETA && (c.flags & 1)) {
-                        u = c.reset_fraction * u + c.reset_add;
-                        ths.v[j] = ths.v[j] * c.theta_spike_refr + c.th_spike_add;
-                    } else {
-                        u = c.v_reset;
-                    }
-                }
-            } else {
-                const float asc_sum = c.asc_coeff[0] * a0.v[j] + c.asc_coeff[1] * a1.v[j];
-                a0.v[j] *= c.asc_decay[0];
-                a1.v[j] *= c.asc_decay[1];
-                if (THETA && (c.flags & 1)) ths.v[j] *= c.theta_spike_decay;
-                const float v_old = u;
-                const float drive = iex.v[j] + c.i_e + asc_sum;
-                u = v_old * c.P33 + drive * c.P30;
+            const float v_old = U.v[j];
+            const bool refr = rf[j] > 0;
+            const int rf_dec = rf[j] - 1;
+            const bool ends = refr && rf_dec == 0;   // glif_psc resets on the step the countdown ends
+            const bool sdt = THETA && (c.flags & 1);  // spike-dependent threshold
+
+            // ---- integrating neuron
+            const float asc_sum = c.asc_coeff[0] * a0.v[j] + c.asc_coeff[1] * a1.v[j];
+            const float drive = iex.v[j] + c.i_e + asc_sum;
+            float u_int = v_old * c.P33 + drive * c.P30;
 #pragma unroll
-                for (int p = 0; p < kPorts; ++p) u += c.P31[p] * y1[p].v[j] + c.P32[p] * y2[p].v[j];
-                float th = c.th_inf;
-                if (THETA) {
-                    if (c.flags & 2) {
-                        const float beta = drive * c.inv_G;
-                        const float d = c.phi * (v_old - beta);
-                        thv.v[j] = d * c.P33 + c.theta_voltage_decay * (thv.v[j] - d - c.abpara * beta) +
-                                   c.abpara * beta;
-                    }
-                    th += ths.v[j] + thv.v[j];
+            for (int p = 0; p < kPorts; ++p) u_int += c.P31[p] * y1[p].v[j] + c.P32[p] * y2[p].v[j];
+            float th = c.th_inf;
+            float ths_int = ths.v[j], thv_int = thv.v[j];
+            if (THETA) {
+                if (sdt) ths_int = ths.v[j] * c.theta_spike_decay;
+                if (c.flags & 2) {
+                    const float beta = drive * c.inv_G;
+                    const float d = c.phi * (v_old - beta);
+                    thv_int = d * c.P33 + c.theta_voltage_decay * (thv.v[j] - d - c.abpara * beta) + c.abpara * beta;
                 }
-                const bool fire = (c.flags & 8) ? (u >= th) : (u > th);
-                if (fire) {
-                    rf[j] = c.n_ref;
-                    mask |= 1u << j;
-                    if (c.flags & 4) u = c.v_reset;  // iaf_psc_alpha: reset in the spike step
-                }
+                th += ths_int + thv_int;
             }
-            U.v[j] = u;
+            const bool fire = !refr && ((c.flags & 8) ? (u_int >= th) : (u_int > th));
+            if ((c.flags & 4) && fire) u_int = c.v_reset;   // iaf_psc_alpha: reset in the spike step
+
+            // ---- refractory neuron: V is held; after-spike currents and V change when the countdown ends
+            const float u_end = sdt ? c.reset_fraction * v_old + c.reset_add : c.v_reset;
+
+            U.v[j] = refr ? (ends ? u_end : v_old) : u_int;
+            a0.v[j] = refr ? (ends ? c.asc_amps[0] + a0.v[j] * c.asc_refr[0] : a0.v[j]) : a0.v[j] * c.asc_decay[0];
+            a1.v[j] = refr ? (ends ? c.asc_amps[1] + a1.v[j] * c.asc_refr[1] : a1.v[j]) : a1.v[j] * c.asc_decay[1];
+            if (THETA) {
+                ths.v[j] = refr ? ((ends && sdt) ? ths.v[j] * c.theta_spike_refr + c.th_spike_add : ths.v[j]) : ths_int;
+                thv.v[j] = refr ? thv.v[j] : thv_int;
+            }
+            rf[j] = refr ? rf_dec : (fire ? c.n_ref : rf[j]);
+            mask |= fire ? (1u << j) : 0u;
 #pragma unroll
             for (int p = 0; p < kPorts; ++p) {
                 const float y1o = y1[p].v[j];

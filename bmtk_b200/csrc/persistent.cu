@@ -29,11 +29,6 @@ constexpr int kPT = 512;         // threads per block, one block per SM
 constexpr int kSub = 128;        // threads that stream one CSR row together
 constexpr int kSmemTypesP = 128;
 
-__device__ __forceinline__ F4 ld4cg(const float* p) {
-    const float4 t = __ldcg(reinterpret_cast<const float4*>(p));
-    return F4{{t.x, t.y, t.z, t.w}};
-}
-
 // 16-byte asynchronous copy global -> shared that caches in L2 only (the ring is written by other SMs)
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
@@ -41,12 +36,6 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ unsigned long long gtimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 constexpr uint32_t kPend = 4096;   // spikes one block can hold for one window
 
@@ -171,16 +160,10 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, 
 
 // ---- several ranks: the exchange is part of this kernel, over peer memory (NVLink / NVSwitch)
 
-typedef unsigned long long u64;
-
 __device__ __forceinline__ u64* x_counts(u64* x, uint32_t parity) { return x + parity * kXRanks; }
 __device__ __forceinline__ u64* x_inbox(const PersistArgs& a, u64* x, uint32_t parity, uint32_t src_rank) {
     return x + 2 * kXRanks + ((size_t)parity * a.n_ranks + src_rank) * a.xchg_cap;
 }
-__device__ __forceinline__ void st_word(u64* p, uint32_t seq, uint32_t payload) {
-    *reinterpret_cast<volatile u64*>(p) = ((u64)seq << 32) | payload;
-}
-__device__ __forceinline__ u64 ld_word(const u64* p) { return *reinterpret_cast<const volatile u64*>(p); }
 
 // End of a window with several ranks: the block reserves a range behind this rank's window counter
 // and stores its spikes, tagged with the window's sequence number, into inbox[parity][rank] of every
@@ -222,7 +205,6 @@ __device__ __forceinline__ unsigned long long flush_block_multi(const PersistArg
 // rank; the first n_ranks threads of block 0 then wait (bounded) until the count word of every rank
 // carries this window's tag. On a time-out the sticky error bit is set and all later waits are
 // skipped, so the launch still ends; the host turns the bit into BMTK_E_COMM.
-constexpr unsigned int kWaitSpins = 4000000u;   // x (load + 100 ns sleep): about a second
 
 __device__ __forceinline__ void publish_and_wait(const PersistArgs& a, uint32_t parity, uint32_t seq) {
     if (blockIdx.x != 0) return;

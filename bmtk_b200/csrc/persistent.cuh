@@ -1,5 +1,8 @@
 #pragma once
 #include "common.cuh"
+#ifdef __CUDACC__
+#include "glif_math.cuh"
+#endif
 
 namespace bmtk {
 
@@ -44,6 +47,11 @@ struct PersistArgs {
     const uint32_t* in_src;
     // stepping
     uint32_t n_steps, window;
+    uint32_t half;             // pipelined kernel: steps per phase, <= min_delay / 2
+    // pipelined kernel: chunk lists [3][blocks][pipe_seg_cap] and their per-block counts [3][blocks]
+    uint4* pipe_seg;
+    uint32_t* pipe_cnt;
+    uint32_t pipe_seg_cap;
     // clamp events grouped by step: group g covers events [ce_group_ptr[g], ce_group_ptr[g+1])
     const unsigned long long* ce_group_step;
     const uint32_t* ce_group_ptr;
@@ -70,6 +78,33 @@ struct PersistArgs {
     uint32_t xchg_cap;
     uint32_t seq0;             // windows completed before this launch
 };
+
+#ifdef __CUDACC__
+// ---- device helpers shared by the persistent kernels
+
+// ring cells and lists are written by other SMs between barriers: read them through L2
+__device__ __forceinline__ F4 ld4cg(const float* p) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(p));
+    return F4{{t.x, t.y, t.z, t.w}};
+}
+
+__device__ __forceinline__ unsigned long long gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+typedef unsigned long long u64;
+
+// exchange words: {sequence number : 32 | payload : 32}, one 8-byte store / load each
+__device__ __forceinline__ void st_word(u64* p, uint32_t seq, uint32_t payload) {
+    *reinterpret_cast<volatile u64*>(p) = ((u64)seq << 32) | payload;
+}
+__device__ __forceinline__ u64 ld_word(const u64* p) { return *reinterpret_cast<const volatile u64*>(p); }
+
+// bound of every wait on a peer: x (load + 100 ns sleep), about a second
+constexpr unsigned int kWaitSpins = 4000000u;
+#endif
 
 constexpr size_t xchg_words(uint32_t n_ranks, uint32_t cap) { return 2 * (size_t)kXRanks + 2 * (size_t)n_ranks * cap; }
 

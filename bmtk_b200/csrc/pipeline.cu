@@ -1,0 +1,487 @@
+// Pipelined persistent kernel: neuron update and spike delivery run CONCURRENTLY on every SM.
+//
+// One block per SM stays resident for a whole chunk of steps (cooperative launch). Its first 512
+// threads ("update warps") own four neurons each, state in registers for the whole launch; its last
+// 128 threads ("delivery warps") stream CSR rows into the ring. Time is cut into phases of
+// h = floor(min_delay / 2) steps. In phase p
+//   * the update warps run the phase's h steps back to back (ring slot in, state update, slot
+//     cleared); a spike is cut into chunks of at most 256 CSR entries whose descriptors
+//     {first entry, length, ring slot of emission} go to the block's segment of a global list,
+//     at a position taken from a SHARED-memory counter (no global atomic on the update path);
+//   * half of the delivery warps draw the phase's Poisson cells (or pick up replayed virtual
+//     spikes) and add their chunks to the same list;
+//   * all delivery warps of the GRID share the chunks listed in phase p-1: warp w takes chunks
+//     w, w + W, ... of the concatenated segments (one coalesced read of the per-block counts, one
+//     descriptor read, then up to 8 entries per lane in flight), so a busy block's spikes are
+//     delivered by everybody;
+// and ONE grid barrier closes the phase. Whatever is emitted in phase p is due min_delay >= 2h steps
+// later, i.e. not before phase p+2 begins, so delivering it during phase p+1 neither touches a ring
+// slot that phase reads nor arrives late. Compared with update -> barrier -> deliver -> barrier per
+// window, the two latency chains (ring slot -> update, and list -> row -> ring reduction) overlap
+// instead of adding up, and there is one barrier per h steps instead of two per 2h.
+// Lists rotate over three buffers: written in phase p, read in p+1, cleared in p+2.
+//
+// Replaces NEST's update/deliver cycle inside nest.Simulate (bmtk/simulator/pointnet/pointsimulator.py:166).
+#include <cooperative_groups.h>
+
+#include "glif_math.cuh"
+#include "persistent.cuh"
+#include "philox.cuh"
+#include "pipeline.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace bmtk {
+
+constexpr int kUT = 512;            // update threads (four warpgroups)
+constexpr int kDT = 128;            // delivery threads (one warpgroup)
+constexpr int kBT = kUT + kDT;
+constexpr int kInFlight = 8;        // row entries each delivery lane has in flight
+constexpr uint32_t kChunk = 32 * kInFlight;   // entries of one chunk: one round of one delivery warp
+constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
+constexpr int kProducers = kUT / 32 + kDT / 64;   // warps that add chunks to a block's segment
+constexpr int kCntPerLane = (int)((kPipeMaxBlocks + 31) / 32);
+constexpr int kSmemTypesPipe = 128;
+#ifndef BMTK_PIPE_SETMAXNREG
+#define BMTK_PIPE_SETMAXNREG 1
+#endif
+// The block is launched with 96 registers per thread (64 K / 640, rounded down to 8). The delivery
+// warpgroup drops to 64 and the four update warpgroups rise to 104:
+// 128 x (96 - 64) registers released = 512 x (104 - 96) claimed.
+constexpr int kRegsUpdate = 104;
+constexpr int kRegsDelivery = 64;
+
+struct PipeShared {
+    uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
+    uint32_t chunks[3];             // chunk descriptors this block has added to list L
+    uint32_t arrive[3];             // producer warps that are done with list L
+    uint2 rows[kUT * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
+    uint32_t pend[2][kPendP];       // step in phase << kSrcBits | id
+};
+
+__device__ __forceinline__ uint32_t wrap_slot(uint32_t slot, uint32_t n) { return slot >= n ? slot - n : slot; }
+
+// Adds the CSR row [begin, begin + len), emitted at ring slot slot0, to this block's segment of list L.
+__device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t begin, uint32_t len,
+                                            uint32_t slot0) {
+    const uint32_t n = (len + kChunk - 1) / kChunk;
+    if (n == 0) return;
+    const uint32_t pos = atomicAdd(&sh.chunks[L], n);
+    uint4* seg = a.pipe_seg + ((size_t)L * gridDim.x + blockIdx.x) * a.pipe_seg_cap;
+    for (uint32_t c = 0; c < n; ++c) {
+        if (pos + c < a.pipe_seg_cap) seg[pos + c] = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, 0u);
+        else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+    }
+}
+
+// A producer warp is done with list L; the last one of the block publishes the block's chunk count.
+__device__ __forceinline__ void warp_arrive(const PersistArgs& a, PipeShared& sh, uint32_t L) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) {
+        const uint32_t old = atomicAdd(&sh.arrive[L], 1u);
+        if (old == kProducers - 1) __stcg(a.pipe_cnt + L * gridDim.x + blockIdx.x, min(sh.chunks[L], a.pipe_seg_cap));
+    }
+}
+
+struct DeliveryTotals {
+    unsigned long long events, inputs, spikes;
+};
+
+// Input spikes of the phase [start, start + len) whose first step uses ring slot `slot`: Poisson
+// cells (dealt round-robin over the blocks) and this block's share of the replayed spikes, on
+// `n_thr` threads of which this is thread `t`.
+__device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared& sh, uint32_t L, unsigned long long start,
+                                               uint32_t slot, uint32_t len, uint32_t t, uint32_t n_thr, DeliveryTotals& tot) {
+    if (a.poisson_thr) {
+        for (uint32_t v = t * gridDim.x + blockIdx.x; v < a.n_virtual; v += n_thr * gridDim.x) {
+            const uint4 thr = __ldg(a.poisson_thr + v);
+            for (uint32_t j = 0; j < len; ++j) {
+                const unsigned long long step = start + j;
+                const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base, (uint32_t)a.seed,
+                                                 (uint32_t)(a.seed >> 32)).x;
+                const uint32_t k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
+                if (k) {
+                    const unsigned long long rb = a.rowptr[a.n_global + v], re = a.rowptr[a.n_global + v + 1];
+                    for (uint32_t c = 0; c < k; ++c)
+                        push_chunks(a, sh, L, (uint32_t)rb, (uint32_t)(re - rb), wrap_slot(slot + j, a.ring_slots));
+                    tot.inputs += k;
+                }
+            }
+        }
+    }
+    if (a.in_ptr) {
+        unsigned long long lo = start > a.in_ptr_base ? start - a.in_ptr_base : 0ull;
+        unsigned long long hi = start + len > a.in_ptr_base ? start + len - a.in_ptr_base : 0ull;
+        const unsigned long long last = a.in_ptr_len - 1;
+        if (lo > last) lo = last;
+        if (hi > last) hi = last;
+        const uint32_t in_begin = a.in_ptr[lo], in_end = a.in_ptr[hi];
+        for (uint32_t idx = in_begin + t * gridDim.x + blockIdx.x; idx < in_end; idx += n_thr * gridDim.x) {
+            const uint32_t src = a.in_src[idx];
+            const unsigned long long rb = a.rowptr[src], re = a.rowptr[src + 1];
+            push_chunks(a, sh, L, (uint32_t)rb, (uint32_t)(re - rb),
+                        wrap_slot(slot + (uint32_t)(a.in_step[idx] - start), a.ring_slots));
+        }
+    }
+}
+
+// Delivery of list L by the delivery warps of the whole grid: warp gw of n_warps takes chunks
+// gw, gw + n_warps, ... of the blocks' segments laid end to end. Called by whole warps.
+__device__ __forceinline__ void deliver_list(const PersistArgs& a, uint32_t L, uint32_t gw, uint32_t n_warps, uint32_t lane,
+                                             DeliveryTotals& tot) {
+    // lane l holds the counts of blocks [l * kCntPerLane, (l + 1) * kCntPerLane) and their exclusive prefix
+    uint32_t cnt[kCntPerLane], pre[kCntPerLane];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int k = 0; k < kCntPerLane; ++k) {
+        const uint32_t b = lane * kCntPerLane + k;
+        cnt[k] = b < gridDim.x ? __ldcg(a.pipe_cnt + L * gridDim.x + b) : 0u;
+        pre[k] = sum;
+        sum += cnt[k];
+    }
+    uint32_t incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= (uint32_t)d) incl += t;
+    }
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    const uint32_t base = incl - sum;
+    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
+    const size_t plane = (size_t)a.n_pad;
+    for (uint32_t g = gw; g < total; g += n_warps) {
+        // which block's segment holds chunk g, and where
+        uint32_t blk = 0, off = 0;
+        bool have = false;
+#pragma unroll
+        for (int k = 0; k < kCntPerLane; ++k) {
+            const uint32_t lo = base + pre[k];
+            if (g >= lo && g < lo + cnt[k]) {
+                have = true;
+                blk = lane * kCntPerLane + k;
+                off = g - lo;
+            }
+        }
+        const uint32_t src = __ffs(__ballot_sync(0xffffffffu, have)) - 1u;
+        blk = __shfl_sync(0xffffffffu, blk, src);
+        off = __shfl_sync(0xffffffffu, off, src);
+        const uint4 d = __ldcg(a.pipe_seg + ((size_t)L * gridDim.x + blk) * a.pipe_seg_cap + off);
+        if (lane == 0) tot.events += d.y;
+        uint2 e[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+            if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            if (lane + 32u * u < d.y) {
+                uint32_t slot = d.z + (e[u].x >> (tb + 2));
+                if (slot >= a.ring_slots) slot -= a.ring_slots;
+                atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
+                          __uint_as_float(e[u].y));
+            }
+        }
+    }
+}
+
+// Spike log of the phase whose list has parity q (stamps count from prev_start); one warp.
+__device__ __forceinline__ void write_log(const PersistArgs& a, PipeShared& sh, uint32_t lane, uint32_t n_rec, uint32_t q,
+                                          unsigned long long prev_start) {
+    uint32_t lbase = 0;
+    if (lane == 0) lbase = atomicAdd(&a.ctl->log_count, n_rec);
+    lbase = __shfl_sync(0xffffffffu, lbase, 0);
+    for (uint32_t k = lane; k < n_rec; k += 32) {
+        const uint32_t e = sh.pend[q][k];
+        if (lbase + k < a.log_cap) {
+            a.log_stamp[lbase + k] = (uint32_t)(prev_start + (e >> kSrcBits) + 1ull);
+            a.log_id[lbase + k] = e & kSrcMask;
+        } else {
+            atomicOr(&a.ctl->error_flags, kErrLogFull);
+        }
+    }
+}
+
+template <bool THETA, bool IEXT>
+__global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    cg::grid_group grid = cg::this_grid();
+    PipeShared& sh = *reinterpret_cast<PipeShared*>(smem_raw);
+    TypeConsts* s_types = reinterpret_cast<TypeConsts*>(smem_raw + sizeof(PipeShared));
+    const bool use_smem = a.n_types <= kSmemTypesPipe;
+    if (threadIdx.x == 0) {
+        sh.count[0] = sh.count[1] = 0u;
+        sh.chunks[0] = sh.chunks[1] = sh.chunks[2] = 0u;
+        sh.arrive[0] = sh.arrive[1] = sh.arrive[2] = 0u;
+    }
+    if (use_smem) {
+        const int words = a.n_types * (int)(sizeof(TypeConsts) / 4);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(a.types);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(s_types);
+        for (int i = threadIdx.x; i < words; i += kBT) dst[i] = src[i];
+    }
+    const TypeConsts* types = use_smem ? s_types : a.types;
+
+    const bool is_upd = threadIdx.x < kUT;
+    const uint32_t dtid = threadIdx.x - kUT;
+    const uint32_t n_groups = a.n_pad / kNeuronsPerThread;
+    const unsigned long long step_base = __ldcg(&a.ctl->step_base);
+    const uint32_t sample_base = __ldcg(&a.ctl->sample_base);
+    // Neurons are dealt to the update warps in chunks of 128 (32 lanes x 4), round-robin over the blocks:
+    // chunk c belongs to warp c / gridDim.x of block c % gridDim.x. Neurons are sorted by type, so every
+    // block gets its share of every type.
+    const uint32_t my_group = ((threadIdx.x >> 5) * gridDim.x + blockIdx.x) * 32u + (threadIdx.x & 31u);
+    const uint32_t i0 = my_group * kNeuronsPerThread;
+    const bool mine = is_upd && my_group < n_groups;
+    const bool timer_u = a.profile && blockIdx.x == 0 && threadIdx.x == 0;
+    const bool timer_d = a.profile && blockIdx.x == 0 && threadIdx.x == kUT;
+
+    // clamp changes already in force at the first step of this launch
+    uint32_t cgi = a.ce_group_begin;
+    if (IEXT) {
+        bool any = false;
+        while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= step_base) {
+            const uint32_t b = a.ce_group_ptr[cgi], e = a.ce_group_ptr[cgi + 1];
+            for (uint32_t k = b + blockIdx.x * kBT + threadIdx.x; k < e; k += gridDim.x * kBT)
+                atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
+            ++cgi;
+            any = true;
+        }
+        if (any) grid.sync();
+    }
+    __syncthreads();
+
+    const uint32_t S = a.ring_slots;
+    uint32_t slot = (uint32_t)(step_base % S);   // ring slot of the phase's first step
+    uint32_t s = 0, p = 0;
+    // phase timers (option): block 0's first update and first delivery thread sum their busy and waiting
+    // time in registers and add them to the control block when the launch ends
+    unsigned long long t_mark = (timer_u || timer_d) ? gtimer() : 0ull;
+    unsigned long long acc_work = 0ull, acc_wait = 0ull, acc_rows = 0ull;
+
+    // Both roles walk the same phase schedule: h steps, cut short where a clamp change takes effect
+    // (a change always starts a phase) and at the end of the launch.
+#define PIPE_PHASE_BEGIN()                                                   \
+    const unsigned long long start = step_base + s;                          \
+    uint32_t len = min(a.half, a.n_steps - s);                               \
+    bool clamp_next = false;                                                 \
+    if (IEXT && cgi < a.ce_group_end) {                                      \
+        const unsigned long long gs = a.ce_group_step[cgi]; /* > start */    \
+        if (gs - start <= (unsigned long long)len) {                         \
+            len = (uint32_t)(gs - start);                                    \
+            clamp_next = true;                                               \
+        }                                                                    \
+    }                                                                        \
+    const uint32_t par = p & 1u;                                             \
+    const uint32_t L = p % 3u;
+
+    if (is_upd) {
+        // ================= update warps: take the registers the delivery warps give up
+#if BMTK_PIPE_SETMAXNREG
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsUpdate));
+#endif
+        Neuron4<THETA, IEXT> nr;
+        int pslot[4] = {-1, -1, -1, -1};
+        if (mine) {
+            nr.load(a.st, a.n_pad, i0);
+            if (IEXT) nr.iex = ld4cg(a.st.i_ext + i0);
+            if (a.probe_slot) {
+                const int4 qd = *reinterpret_cast<const int4*>(a.probe_slot + i0);
+                pslot[0] = qd.x; pslot[1] = qd.y; pslot[2] = qd.z; pslot[3] = qd.w;
+            }
+#pragma unroll
+            for (int j = 0; j < kNeuronsPerThread; ++j) {
+                const unsigned long long rb = a.rowptr[a.lo + i0 + j], re = a.rowptr[a.lo + i0 + j + 1];
+                sh.rows[threadIdx.x * kNeuronsPerThread + j] = make_uint2((uint32_t)rb, (uint32_t)(re - rb));
+            }
+        }
+        // probes: a sample is taken after the step that ends a recording interval
+        uint32_t pctr = 0;                 // (step + 1) mod interval of the next step to run
+        unsigned long long sample = 0;     // sample that step writes when pctr == 0, relative to the drained ones
+        if (a.probe_slot) {
+            pctr = (uint32_t)((step_base + 1ull) % a.probe_interval);
+            sample = (step_base + 1ull) / a.probe_interval - 1ull - sample_base;
+            if (pctr != 0) sample += 1ull;   // the next multiple of the interval
+        }
+        while (s < a.n_steps) {
+            PIPE_PHASE_BEGIN()
+            uint32_t sl = slot;
+            for (uint32_t j = 0; j < len; ++j) {
+                uint32_t mask = 0;
+                if (mine) {
+                    float* ring = a.ring + (size_t)sl * kPorts * a.n_pad + i0;
+                    F4 in[kPorts];
+#pragma unroll
+                    for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
+                    mask = nr.step(types, in);
+                    if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
+                    const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                    for (int pt = 0; pt < kPorts; ++pt) {
+                        const bool nz = in[pt].v[0] != 0.f || in[pt].v[1] != 0.f || in[pt].v[2] != 0.f || in[pt].v[3] != 0.f;
+                        if (nz) st4(ring + (size_t)pt * a.n_pad, zero);   // most cells are still zero
+                    }
+                }
+                if (a.probe_slot) {
+                    if (pctr == 0) {
+                        if (mine && sample < a.trace_cap) {
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                if (pslot[jj] >= 0)
+                                    a.trace[(size_t)sample * a.n_probe + pslot[jj]] = nr.U.v[jj] + types[nr.ty[jj]].E_L;
+                        }
+                        ++sample;
+                    }
+                    if (++pctr == a.probe_interval) pctr = 0;
+                }
+                if (mask) {
+                    // spikes are rare: each firing lane appends for itself
+#pragma unroll
+                    for (int jj = 0; jj < kNeuronsPerThread; ++jj) {
+                        if (mask >> jj & 1u) {
+                            const uint32_t pos = atomicAdd(&sh.count[par], 1u);
+                            if (pos < kPendP) sh.pend[par][pos] = (j << kSrcBits) | (a.lo + i0 + jj);
+                            else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+                            const uint2 r = sh.rows[threadIdx.x * kNeuronsPerThread + jj];
+                            push_chunks(a, sh, L, r.x, r.y, sl);
+                        }
+                    }
+                }
+                sl = wrap_slot(sl + 1u, S);
+            }
+            warp_arrive(a, sh, L);
+            const unsigned long long t_work = timer_u ? gtimer() : 0ull;
+            grid.sync();
+            if (timer_u) {
+                const unsigned long long t_end = gtimer();
+                acc_work += t_work - t_mark;
+                acc_wait += t_end - t_work;
+                t_mark = t_end;
+            }
+            if (IEXT && clamp_next) {
+                while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= start + len) ++cgi;
+                if (mine) nr.iex = ld4cg(a.st.i_ext + i0);
+            }
+            slot = (uint32_t)((slot + len) % S);
+            s += len;
+            ++p;
+        }
+        if (mine) nr.store(a.st, a.n_pad, i0);
+        if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->step_base = step_base + a.n_steps;
+        if (timer_u) {
+            a.ctl->t_update_ns += acc_work;
+            a.ctl->t_sync1_ns += acc_wait;
+            a.ctl->n_windows += p;
+        }
+    } else {
+        // ================= delivery warps
+#if BMTK_PIPE_SETMAXNREG
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsDelivery));
+#endif
+        const uint32_t lane = dtid & 31u;
+        const uint32_t n_warps = gridDim.x * (kDT / 32);
+        const uint32_t gw = (dtid >> 5) * gridDim.x + blockIdx.x;   // consecutive chunks go to different SMs
+        unsigned long long prev_start = step_base;
+        DeliveryTotals tot = {0ull, 0ull, 0ull};
+        while (s < a.n_steps) {
+            PIPE_PHASE_BEGIN()
+            const uint32_t q = par ^ 1u;
+            if (dtid == 0) {
+                // the list of the NEXT phase was last read one phase ago
+                const uint32_t Ln = (p + 1u) % 3u;
+                sh.chunks[Ln] = 0u;
+                sh.arrive[Ln] = 0u;
+            }
+            if (p > 0) deliver_list(a, (p + 2u) % 3u, gw, n_warps, lane, tot);
+            const unsigned long long t_rows = timer_d ? gtimer() : 0ull;
+            // ---- off the rows' critical path. First half of the delivery warps: spike log of the previous
+            // phase; second half: this phase's input spikes.
+            if (dtid < kDT / 2) {
+                if (dtid < 32 && p > 0) {
+                    const uint32_t n_rec = min(sh.count[q], kPendP);
+                    if (a.log_stamp && n_rec) write_log(a, sh, dtid, n_rec, q, prev_start);
+                    __syncwarp();
+                    if (dtid == 0) {
+                        sh.count[q] = 0u;    // the update warps append to it again in the next phase
+                        tot.spikes += n_rec;
+                    }
+                }
+            } else {
+                prepare_inputs(a, sh, L, start, slot, len, dtid - kDT / 2, kDT / 2, tot);
+                warp_arrive(a, sh, L);
+            }
+            if (IEXT && clamp_next) {
+                // changes effective from the next phase's first step: nobody reads i_ext before the barrier
+                for (uint32_t g = cgi; g < a.ce_group_end && a.ce_group_step[g] <= start + len; ++g) {
+                    const uint32_t b = a.ce_group_ptr[g], e = a.ce_group_ptr[g + 1];
+                    for (uint32_t k = b + blockIdx.x * kDT + dtid; k < e; k += gridDim.x * kDT)
+                        atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
+                }
+            }
+            const unsigned long long t_work = timer_d ? gtimer() : 0ull;
+            grid.sync();
+            if (timer_d) {
+                const unsigned long long t_end = gtimer();
+                acc_work += t_work - t_mark;
+                acc_wait += t_end - t_work;
+                acc_rows += t_rows - t_mark;
+                t_mark = t_end;
+            }
+            if (IEXT && clamp_next)
+                while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= start + len) ++cgi;
+            prev_start = start;
+            slot = (uint32_t)((slot + len) % S);
+            s += len;
+            ++p;
+        }
+        // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
+        if (p > 0) {
+            deliver_list(a, (p + 2u) % 3u, gw, n_warps, lane, tot);
+            if (dtid < 32) {
+                const uint32_t q = (p & 1u) ^ 1u;
+                const uint32_t n_rec = min(sh.count[q], kPendP);
+                if (a.log_stamp && n_rec) write_log(a, sh, dtid, n_rec, q, prev_start);
+                if (dtid == 0) tot.spikes += n_rec;
+            }
+        }
+        if (timer_d) {
+            a.ctl->t_prop_ns += acc_work;
+            a.ctl->t_sync2_ns += acc_wait;
+            a.ctl->t_dbg[0] += acc_rows;
+        }
+        if (tot.events) atomicAdd(&a.ctl->n_events, tot.events);
+        if (tot.inputs) atomicAdd(&a.ctl->n_input_spikes, tot.inputs);
+        if (tot.spikes) atomicAdd(&a.ctl->n_spikes, tot.spikes);
+    }
+#undef PIPE_PHASE_BEGIN
+}
+
+static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext) {
+    if (has_theta) return has_iext ? (const void*)pipelined_kernel<true, true> : (const void*)pipelined_kernel<true, false>;
+    return has_iext ? (const void*)pipelined_kernel<false, true> : (const void*)pipelined_kernel<false, false>;
+}
+
+size_t pipelined_smem(int n_types) {
+    return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0);
+}
+
+uint32_t pipelined_update_threads() { return kUT; }
+
+int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem) {
+    int per_sm = 0, sms = 0;
+    const void* f = pipelined_kernel_ptr(has_theta, has_iext);
+    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, kBT, smem) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    return per_sm > 0 ? sms : 0;   // one block per SM
+}
+
+cudaError_t launch_pipelined(const PersistArgs& a, bool has_theta, bool has_iext, int blocks, cudaStream_t s) {
+    const size_t smem = pipelined_smem(a.n_types);
+    const void* f = pipelined_kernel_ptr(has_theta, has_iext);
+    cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    PersistArgs copy = a;
+    void* args[] = {&copy};
+    return cudaLaunchCooperativeKernel(f, dim3(blocks), dim3(kBT), args, smem, s);
+}
+
+}  // namespace bmtk

@@ -1,0 +1,16 @@
+#pragma once
+#include "persistent.cuh"
+
+namespace bmtk {
+
+constexpr uint32_t kPipeMaxBlocks = 160;    // blocks (SMs) the delivery warps' count scan is laid out for
+constexpr uint32_t kPipeSegCap = 1024;      // chunk descriptors one block can add to one phase's list
+
+// Pipelined persistent kernel (update and delivery warps side by side on every SM). Takes the
+// same arguments as the two-phase persistent kernel plus PersistArgs::half, the phase length.
+size_t pipelined_smem(int n_types);
+uint32_t pipelined_update_threads();
+int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem);
+cudaError_t launch_pipelined(const PersistArgs& a, bool has_theta, bool has_iext, int blocks, cudaStream_t s);
+
+}  // namespace bmtk

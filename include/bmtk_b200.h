@@ -138,6 +138,10 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
  *  "persistent"     0|1 run each chunk as ONE cooperative kernel that loops over the steps with the
  *                   neuron state held in registers (default 1; single rank, atomic delivery; may
  *                   be changed between runs)
+ *  "pipeline"       0|1 persistent stepping with update and delivery warps side by side on every SM and one
+ *                   grid barrier per min_delay / 2 steps (default 1; used when the state fits in registers,
+ *                   there is one trial and the minimum delay is at least 2 steps; counter "pipelined"; may be
+ *                   changed between runs)
  *  "ring_prefetch"  0|1 persistent kernel with resident state: fetch the next step's ring slot into shared
  *                   memory with cp.async while the current step computes (default 0: on the 2-step
  *                   windows of the benchmark network it measured 3 % slower than plain L2 loads)
