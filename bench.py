@@ -262,9 +262,12 @@ def main():
                          options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
                          libnccl=libnccl, p2p=args.exchange == 'p2p')
     t_build = time.time() - t0
+    n_warm = 0
     for _ in range(args.warmup):
         eng.run(steps_per_bench_step)
-        eng.fetch_spikes()
+        n_warm = max(n_warm, len(eng.fetch_spikes()[0]))
+    # the timed launches leave their spikes in the host store: pin it before the clock starts
+    eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
     torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -282,7 +285,8 @@ def main():
     eng.fetch_spikes()
     dev_ms = reduce(dev_ms, dist.ReduceOp.MAX if world > 1 else None)
     wall_ms = reduce(wall_ms, dist.ReduceOp.MAX if world > 1 else None)
-    events = reduce(eng.counter('events') - ev0, dist.ReduceOp.SUM if world > 1 else None)
+    local_events = eng.counter('events') - ev0
+    events = reduce(local_events, dist.ReduceOp.SUM if world > 1 else None)
     spikes = reduce(eng.counter('spikes') - sp0, dist.ReduceOp.SUM if world > 1 else None)
     launches = reduce(eng.counter('launches') - l0, dist.ReduceOp.SUM if world > 1 else None)
     value = events / (dev_ms * 1e-3)
@@ -299,15 +303,23 @@ def main():
         pu, pp = eng.counter('phase_update_ns') / nw, eng.counter('phase_propagate_ns') / nw
         ev_w = (eng.counter('events') - e0) / nw
         win = eng.counter('window')
+        pipelined = bool(eng.counter('pipelined'))
+        steps_w = steps_per_bench_step / nw          # steps between two grid barriers
+        s1, s2 = eng.counter('phase_sync1_ns') / nw, eng.counter('phase_sync2_ns') / nw
         phases = {
-            'timing': 'in-kernel %globaltimer around the two phases of every window (one cooperative launch per bench step)',
-            'windows': nw, 'steps_per_window': win,
+            'kernel': 'pipelined (update and delivery warps side by side, one barrier per phase)' if pipelined
+                      else 'two-phase (update, barrier, delivery, barrier per window)',
+            'timing': 'in-kernel %globaltimer, block 0, summed in registers over one cooperative launch (= one bench step)',
+            'windows': nw, 'steps_per_window': steps_w,
             'update_phase_us': pu * 1e-3, 'propagate_phase_us': pp * 1e-3,
-            'of_which_barrier_wait_us': [eng.counter('phase_sync1_ns') / nw * 1e-3, eng.counter('phase_sync2_ns') / nw * 1e-3],
-            'update_gbs': BYTES_PER_NEURON_STEP * eng.counter('n_pad') * win / pu,
-            'propagate_gbs': BYTES_PER_EVENT * ev_w / pp, 'events_per_window': ev_w,
-            'resident_state': bool(eng.counter('persistent_resident')),
+            'of_which_barrier_wait_us': [s1 * 1e-3, s2 * 1e-3],
+            'update_gbs': BYTES_PER_NEURON_STEP * eng.counter('n_pad') * steps_w / (pu - s1 if pipelined else pu),
+            'propagate_gbs': BYTES_PER_EVENT * ev_w / (pp - s2 if pipelined else pp), 'events_per_window': ev_w,
+            'resident_state': bool(eng.counter('persistent_resident')), 'pipelined': pipelined,
         }
+        if pipelined:
+            phases['phase_us'] = pu * 1e-3           # both sides span the whole phase
+            phases['row_streaming_us'] = eng.counter('phase_rows_ns') / nw * 1e-3
 
     # ---------------- profiled pass: per-launch CUDA events around both kernels
     prof_steps = min(steps_per_bench_step, 800)
@@ -330,21 +342,23 @@ def main():
                       'achieved_gbs': pr_bytes / (pr_ns / pr_n), 'traffic': NCU_TRAFFIC_BYTES['propagate']},
     }
     if phases:
-        # the timed region runs the persistent kernel: its phases are the roofline subject
-        dom_phase = 'update' if phases['update_phase_us'] >= phases['propagate_phase_us'] else 'propagate'
-        ach = phases['update_gbs'] if dom_phase == 'update' else phases['propagate_gbs']
+        # The timed region is ONE cooperative launch per bench step: that launch is the dominant kernel.
+        # Algorithmic bytes of this rank's launch over its CUDA-event duration (engine marks on the stream).
+        alg_bytes = BYTES_PER_NEURON_STEP * n_pad * steps_per_bench_step + BYTES_PER_EVENT * local_events / args.steps
+        launch_ns = dev_ms / args.steps * 1e6
         roofline = {
-            'kernel': 'persistent_kernel / %s phase' % dom_phase, 'bound': 'hbm', 'achieved': ach, 'peak': peak,
-            'unit': 'GB/s', 'frac': ach / peak, 'traffic': NCU_TRAFFIC_BYTES['persistent_per_step'] * steps_per_bench_step, 'peak_kind': peak_kind,
+            'kernel': 'pipelined_kernel' if phases['pipelined'] else 'persistent_kernel', 'bound': 'hbm',
+            'achieved': alg_bytes / launch_ns, 'peak': peak, 'unit': 'GB/s', 'frac': alg_bytes / launch_ns / peak,
+            'traffic': NCU_TRAFFIC_BYTES['persistent_per_step'] * steps_per_bench_step, 'peak_kind': peak_kind,
             'traffic_note': 'dram bytes of one persistent launch (= one bench step), ncu on a 100-step launch scaled by steps',
-            'timing': phases['timing'],
-            'note': 'algorithmic bytes = 128 B per neuron-step (update) / 16 B per event (delivery); the persistent '
-                    'kernel keeps the 96 B of neuron state in registers, so only the 32 B of ring traffic per neuron-step '
-                    'actually moves (ring-only rate: %.0f GB/s) and the fraction can exceed 1'
-                    % (32.0 * n_pad * phases['steps_per_window'] / (phases['update_phase_us'] * 1e3)),
+            'timing': 'CUDA events on the launching stream around the %d timed launches (one per bench step)' % args.steps,
+            'bytes_per_launch': alg_bytes,
+            'note': 'algorithmic bytes = 128 B per neuron-step + 16 B per synaptic event; the kernel keeps the 96 B of '
+                    'neuron state in registers, so what actually moves per neuron-step is the 32 B of ring traffic: the '
+                    'launch is bound by L2 / barrier latency per step, not by HBM',
             'persistent_phases': phases,
             'per_step_kernels': dict(kernels, timing='CUDA events around every launch of the per-step kernels '
-                                                     '(engine option profile; the path used with several ranks)'),
+                                                     '(engine option profile; the path used without cooperative launch)'),
         }
     else:
         dom = 'glif_update' if up_ns >= pr_ns else 'propagate'
@@ -455,9 +469,11 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
                          options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000))
     MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
+    n_warm = 0
     for _ in range(args.warmup):
         eng.run(n_steps)
-        eng.fetch_spikes()
+        n_warm = max(n_warm, len(eng.fetch_spikes()[0]))
+    eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
     torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None

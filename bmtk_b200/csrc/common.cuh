@@ -60,7 +60,8 @@ struct Ctl {
     // persistent kernel, option "profile": device-timer totals of the two phases of every window
     unsigned long long t_update_ns, t_prop_ns, n_windows;
     unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
-    unsigned long long t_dbg[4];                 // pipelined kernel: finer split of block 0's phases
+    unsigned long long t_rows_ns;                // pipelined kernel: of the delivery warps' busy time, streaming rows
+    unsigned long long pad2[3];
 };
 
 // Trial batching: T independent copies ("trials") of one network share its CSR. Cell c of trial t has

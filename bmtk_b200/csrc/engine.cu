@@ -283,10 +283,11 @@ struct bmtk_engine {
     std::vector<float> h_trace;
 
     // host store of recorded spikes: keys stamp << 32 | id, sorted (every drain appends a later, sorted run)
-    // recorded spikes, (stamp, id)-sorted, in pinned host memory that grows by doubling
-    uint32_t* h_spk_stamp = nullptr;
-    uint32_t* h_spk_id = nullptr;
-    size_t h_spk_n = 0, h_spk_cap = 0;
+    // recorded spikes, (stamp, id)-sorted, in pinned host blocks of kSpkBlock entries ({stamps | ids});
+    // blocks are added as the store grows and kept for re-use after a fetch (pinning memory is slow)
+    static constexpr size_t kSpkBlock = 1u << 21;
+    std::vector<uint32_t*> h_spk_blocks;
+    size_t h_spk_n = 0;
     uint64_t log_base_step = 0;       // every stamp in the device log is greater than this
     unsigned long long *d_log_keys = nullptr, *d_log_keys2 = nullptr;
     void* d_log_tmp = nullptr;
@@ -310,7 +311,6 @@ struct bmtk_engine {
     int persist_blocks = 0;
     bool persist_resident = false;
     uint4* d_pipe_seg = nullptr;
-    uint32_t* d_pipe_cnt = nullptr;
     bool pipeline = true;     // option: use the pipelined kernel where it applies
     bool pipe_ok = false;     // resident state, one trial, min delay >= 2 steps
     int pipe_blocks = 0;
@@ -328,7 +328,7 @@ struct bmtk_engine {
     std::vector<uint64_t> ce_group_step;
     size_t ce_group_next = 0;
     double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
-    double phase_dbg[4] = {0, 0, 0, 0};
+    double phase_rows_ns = 0;
     double drain_wait_ns = 0, drain_sort_ns = 0;   // host clock: waiting for the chunk's kernels; sorting + copying its spike log
     uint64_t phase_windows = 0;
 
@@ -619,7 +619,7 @@ static int drain(bmtk_engine* e) {
         e->phase_windows += h.n_windows;
         e->phase_sync1_ns += (double)h.t_sync1_ns;
         e->phase_sync2_ns += (double)h.t_sync2_ns;
-        for (int q = 0; q < 4; ++q) e->phase_dbg[q] += (double)h.t_dbg[q];
+        e->phase_rows_ns += (double)h.t_rows_ns;
         CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 72, e->stream));
     }
     if (h.step_base != e->step)
@@ -671,24 +671,20 @@ static int drain(bmtk_engine* e) {
         CU(sort_spike_log((uint32_t)n, e->d_log_stamp, e->d_log_id, (uint32_t)e->log_base_step, stamp_bits, id_bits,
                           e->d_log_keys, e->d_log_keys2, e->d_log_tmp, e->log_tmp_bytes, e->stream));
         e->launches += 3;
-        if (e->h_spk_cap < n0 + n) {
-            const size_t cap = std::max<size_t>((n0 + n) * 2, 1u << 16);
-            uint32_t *ns = nullptr, *ni = nullptr;
-            CU(cudaMallocHost(&ns, 4 * cap));
-            CU(cudaMallocHost(&ni, 4 * cap));
-            if (n0) {
-                std::memcpy(ns, e->h_spk_stamp, 4 * n0);
-                std::memcpy(ni, e->h_spk_id, 4 * n0);
-            }
-            if (e->h_spk_stamp) cudaFreeHost(e->h_spk_stamp);
-            if (e->h_spk_id) cudaFreeHost(e->h_spk_id);
-            e->h_spk_stamp = ns;
-            e->h_spk_id = ni;
-            e->h_spk_cap = cap;
-        }
         // straight into the host store: chunks are consecutive in time, so it stays (stamp, id)-sorted
-        CU(cudaMemcpyAsync(e->h_spk_stamp + n0, e->d_log_stamp, 4 * n, cudaMemcpyDeviceToHost, e->stream));
-        CU(cudaMemcpyAsync(e->h_spk_id + n0, e->d_log_id, 4 * n, cudaMemcpyDeviceToHost, e->stream));
+        constexpr size_t B = bmtk_engine::kSpkBlock;
+        for (size_t done = 0; done < n;) {
+            const size_t pos = n0 + done, blk = pos / B, off = pos % B, take = std::min(n - done, B - off);
+            if (blk == e->h_spk_blocks.size()) {
+                uint32_t* p = nullptr;
+                CU(cudaMallocHost(&p, 4 * 2 * B));
+                e->h_spk_blocks.push_back(p);
+            }
+            uint32_t* p = e->h_spk_blocks[blk];
+            CU(cudaMemcpyAsync(p + off, e->d_log_stamp + done, 4 * take, cudaMemcpyDeviceToHost, e->stream));
+            CU(cudaMemcpyAsync(p + B + off, e->d_log_id + done, 4 * take, cudaMemcpyDeviceToHost, e->stream));
+            done += take;
+        }
         CU(cudaMemsetAsync(&e->d_ctl->log_count, 0, 4, e->stream));
         CU(cudaStreamSynchronize(e->stream));
         e->h_spk_n = n0 + n;
@@ -773,7 +769,6 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     if (e->pipeline && e->pipe_ok && e->n_ranks == 1) {
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
         a.pipe_seg = e->d_pipe_seg;
-        a.pipe_cnt = e->d_pipe_cnt;
         a.pipe_seg_cap = kPipeSegCap;
         CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
     } else {
@@ -892,10 +887,8 @@ int bmtk_engine_destroy(bmtk_engine* e) {
         if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r]);
     cudaFree(e->d_xchg);
     cudaFree(e->d_pipe_seg);
-    cudaFree(e->d_pipe_cnt);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
-    if (e->h_spk_stamp) cudaFreeHost(e->h_spk_stamp);
-    if (e->h_spk_id) cudaFreeHost(e->h_spk_id);
+    for (uint32_t* p : e->h_spk_blocks) cudaFreeHost(p);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     return BMTK_OK;
@@ -1026,6 +1019,19 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     if (k == "profile") { e->profile = value != 0; return BMTK_OK; }
     if (k == "use_graph") { e->use_graph = value != 0; return BMTK_OK; }
     if (k == "persistent") { e->persistent = value != 0; return BMTK_OK; }
+    if (k == "spike_store_reserve") {
+        // pin host blocks for this many recorded spikes now rather than as they arrive
+        constexpr size_t B = bmtk_engine::kSpkBlock;
+        if (value < 0 || (uint64_t)value > (1ull << 34)) return fail(BMTK_E_INVALID, "spike_store_reserve out of range");
+        int rc = set_device(e);
+        if (rc) return rc;
+        while (e->h_spk_blocks.size() * B < (uint64_t)value) {
+            uint32_t* p = nullptr;
+            CU(cudaMallocHost(&p, 4 * 2 * B));
+            e->h_spk_blocks.push_back(p);
+        }
+        return BMTK_OK;
+    }
     if (k == "pipeline") { e->pipeline = value != 0; return BMTK_OK; }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
@@ -1316,8 +1322,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 }
                 if (e->pipe_ok) {
                     CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
-                    CU(cudaMalloc(&e->d_pipe_cnt, 4 * 3 * (size_t)pb));
-                    CU(cudaMemset(e->d_pipe_cnt, 0, 4 * 3 * (size_t)pb));
+                    // a descriptor is valid by its tag (first step of its phase + 1): none is at rest
+                    CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
                 }
             }
         }
@@ -1362,9 +1368,11 @@ int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step,
                              (unsigned long long)n);
     if (n && (!stamp_step || !id)) return fail(BMTK_E_INVALID, "fetch_spikes: NULL array");
     // already in canonical (stamp, id) order: sorted per chunk on the device, chunks consecutive in time
-    if (n) {
-        std::memcpy(stamp_step, e->h_spk_stamp, 4 * n);
-        std::memcpy(id, e->h_spk_id, 4 * n);
+    constexpr size_t B = bmtk_engine::kSpkBlock;
+    for (size_t done = 0; done < n; done += B) {
+        const size_t take = std::min(n - done, B);
+        std::memcpy(stamp_step + done, e->h_spk_blocks[done / B], 4 * take);
+        std::memcpy(id + done, e->h_spk_blocks[done / B] + B, 4 * take);
     }
     *n_out = n;
     e->h_spk_n = 0;
@@ -1696,6 +1704,8 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
     e->h_spk_n = 0;
     e->log_base_step = e->step;
     e->h_trace.clear();
+    // descriptors left from steps after the restored one would carry tags that come again
+    if (e->d_pipe_seg) CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap));
     // replayed inputs handed over before the load are re-indexed from the restored step
     return BMTK_OK;
 }
@@ -1743,7 +1753,7 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "phase_sync2_ns") *out = (uint64_t)e->phase_sync2_ns;
     else if (k == "drain_wait_ns") *out = (uint64_t)e->drain_wait_ns;
     else if (k == "drain_sort_ns") *out = (uint64_t)e->drain_sort_ns;
-    else if (k.rfind("phase_dbg", 0) == 0 && k.size() == 10 && k[9] >= '0' && k[9] <= '3') *out = (uint64_t)e->phase_dbg[k[9] - '0'];
+    else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && e->n_ranks == 1) ? 1 : 0;

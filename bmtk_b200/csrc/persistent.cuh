@@ -48,9 +48,8 @@ struct PersistArgs {
     // stepping
     uint32_t n_steps, window;
     uint32_t half;             // pipelined kernel: steps per phase, <= min_delay / 2
-    // pipelined kernel: chunk lists [3][blocks][pipe_seg_cap] and their per-block counts [3][blocks]
+    // pipelined kernel: chunk lists [3][blocks][pipe_seg_cap] of {first entry, length, ring slot, phase tag}
     uint4* pipe_seg;
-    uint32_t* pipe_cnt;
     uint32_t pipe_seg_cap;
     // clamp events grouped by step: group g covers events [ce_group_ptr[g], ce_group_ptr[g+1])
     const unsigned long long* ce_group_step;

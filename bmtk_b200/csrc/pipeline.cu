@@ -10,10 +10,11 @@
 //     at a position taken from a SHARED-memory counter (no global atomic on the update path);
 //   * half of the delivery warps draw the phase's Poisson cells (or pick up replayed virtual
 //     spikes) and add their chunks to the same list;
-//   * all delivery warps of the GRID share the chunks listed in phase p-1: warp w takes chunks
-//     w, w + W, ... of the concatenated segments (one coalesced read of the per-block counts, one
-//     descriptor read, then up to 8 entries per lane in flight), so a busy block's spikes are
-//     delivered by everybody;
+//   * the delivery warps share the chunks listed in phase p-1 with their neighbours: chunk j of
+//     block b is delivered by warp j mod 4 of block b + j / 4, so a busy block's spikes spill over
+//     to the following SMs. A descriptor carries the tag of its phase, so a warp simply loads the
+//     few slots it is responsible for (one round trip, no counts to read first), keeps those with
+//     the right tag and streams them, up to 8 entries per lane in flight;
 // and ONE grid barrier closes the phase. Whatever is emitted in phase p is due min_delay >= 2h steps
 // later, i.e. not before phase p+2 begins, so delivering it during phase p+1 neither touches a ring
 // slot that phase reads nor arrives late. Compared with update -> barrier -> deliver -> barrier per
@@ -39,8 +40,7 @@ constexpr int kBT = kUT + kDT;
 constexpr int kInFlight = 8;        // row entries each delivery lane has in flight
 constexpr uint32_t kChunk = 32 * kInFlight;   // entries of one chunk: one round of one delivery warp
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
-constexpr int kProducers = kUT / 32 + kDT / 64;   // warps that add chunks to a block's segment
-constexpr int kCntPerLane = (int)((kPipeMaxBlocks + 31) / 32);
+constexpr uint32_t kSpill = 4;      // a block's chunks 4r .. 4r+3 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
 #ifndef BMTK_PIPE_SETMAXNREG
 #define BMTK_PIPE_SETMAXNREG 1
@@ -51,35 +51,26 @@ constexpr int kSmemTypesPipe = 128;
 constexpr int kRegsUpdate = 104;
 constexpr int kRegsDelivery = 64;
 
-struct PipeShared {
+struct __align__(16) PipeShared {
     uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
-    uint32_t arrive[3];             // producer warps that are done with list L
     uint2 rows[kUT * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
     uint32_t pend[2][kPendP];       // step in phase << kSrcBits | id
 };
+static_assert(sizeof(PipeShared) % 16 == 0, "the type table behind it is read with 128-bit loads");
 
 __device__ __forceinline__ uint32_t wrap_slot(uint32_t slot, uint32_t n) { return slot >= n ? slot - n : slot; }
 
 // Adds the CSR row [begin, begin + len), emitted at ring slot slot0, to this block's segment of list L.
-__device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t begin, uint32_t len,
-                                            uint32_t slot0) {
+__device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t begin,
+                                            uint32_t len, uint32_t slot0) {
     const uint32_t n = (len + kChunk - 1) / kChunk;
     if (n == 0) return;
     const uint32_t pos = atomicAdd(&sh.chunks[L], n);
     uint4* seg = a.pipe_seg + ((size_t)L * gridDim.x + blockIdx.x) * a.pipe_seg_cap;
     for (uint32_t c = 0; c < n; ++c) {
-        if (pos + c < a.pipe_seg_cap) seg[pos + c] = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, 0u);
+        if (pos + c < a.pipe_seg_cap) seg[pos + c] = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, tag);
         else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
-    }
-}
-
-// A producer warp is done with list L; the last one of the block publishes the block's chunk count.
-__device__ __forceinline__ void warp_arrive(const PersistArgs& a, PipeShared& sh, uint32_t L) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) {
-        const uint32_t old = atomicAdd(&sh.arrive[L], 1u);
-        if (old == kProducers - 1) __stcg(a.pipe_cnt + L * gridDim.x + blockIdx.x, min(sh.chunks[L], a.pipe_seg_cap));
     }
 }
 
@@ -90,7 +81,8 @@ struct DeliveryTotals {
 // Input spikes of the phase [start, start + len) whose first step uses ring slot `slot`: Poisson
 // cells (dealt round-robin over the blocks) and this block's share of the replayed spikes, on
 // `n_thr` threads of which this is thread `t`.
-__device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared& sh, uint32_t L, unsigned long long start,
+__device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag,
+                                               unsigned long long start,
                                                uint32_t slot, uint32_t len, uint32_t t, uint32_t n_thr, DeliveryTotals& tot) {
     if (a.poisson_thr) {
         for (uint32_t v = t * gridDim.x + blockIdx.x; v < a.n_virtual; v += n_thr * gridDim.x) {
@@ -103,7 +95,7 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
                 if (k) {
                     const unsigned long long rb = a.rowptr[a.n_global + v], re = a.rowptr[a.n_global + v + 1];
                     for (uint32_t c = 0; c < k; ++c)
-                        push_chunks(a, sh, L, (uint32_t)rb, (uint32_t)(re - rb), wrap_slot(slot + j, a.ring_slots));
+                        push_chunks(a, sh, L, tag, (uint32_t)rb, (uint32_t)(re - rb), wrap_slot(slot + j, a.ring_slots));
                     tot.inputs += k;
                 }
             }
@@ -119,68 +111,64 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
         for (uint32_t idx = in_begin + t * gridDim.x + blockIdx.x; idx < in_end; idx += n_thr * gridDim.x) {
             const uint32_t src = a.in_src[idx];
             const unsigned long long rb = a.rowptr[src], re = a.rowptr[src + 1];
-            push_chunks(a, sh, L, (uint32_t)rb, (uint32_t)(re - rb),
+            push_chunks(a, sh, L, tag, (uint32_t)rb, (uint32_t)(re - rb),
                         wrap_slot(slot + (uint32_t)(a.in_step[idx] - start), a.ring_slots));
         }
     }
 }
 
-// Delivery of list L by the delivery warps of the whole grid: warp gw of n_warps takes chunks
-// gw, gw + n_warps, ... of the blocks' segments laid end to end. Called by whole warps.
-__device__ __forceinline__ void deliver_list(const PersistArgs& a, uint32_t L, uint32_t gw, uint32_t n_warps, uint32_t lane,
-                                             DeliveryTotals& tot) {
-    // lane l holds the counts of blocks [l * kCntPerLane, (l + 1) * kCntPerLane) and their exclusive prefix
-    uint32_t cnt[kCntPerLane], pre[kCntPerLane];
-    uint32_t sum = 0;
-#pragma unroll
-    for (int k = 0; k < kCntPerLane; ++k) {
-        const uint32_t b = lane * kCntPerLane + k;
-        cnt[k] = b < gridDim.x ? __ldcg(a.pipe_cnt + L * gridDim.x + b) : 0u;
-        pre[k] = sum;
-        sum += cnt[k];
-    }
-    uint32_t incl = sum;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= (uint32_t)d) incl += t;
-    }
-    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    const uint32_t base = incl - sum;
+// Streams one chunk into the ring with one warp: up to kInFlight entries per lane in flight.
+__device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d, uint32_t lane) {
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
-    for (uint32_t g = gw; g < total; g += n_warps) {
-        // which block's segment holds chunk g, and where
-        uint32_t blk = 0, off = 0;
-        bool have = false;
+    uint2 e[kInFlight];
 #pragma unroll
-        for (int k = 0; k < kCntPerLane; ++k) {
-            const uint32_t lo = base + pre[k];
-            if (g >= lo && g < lo + cnt[k]) {
-                have = true;
-                blk = lane * kCntPerLane + k;
-                off = g - lo;
-            }
-        }
-        const uint32_t src = __ffs(__ballot_sync(0xffffffffu, have)) - 1u;
-        blk = __shfl_sync(0xffffffffu, blk, src);
-        off = __shfl_sync(0xffffffffu, off, src);
-        const uint4 d = __ldcg(a.pipe_seg + ((size_t)L * gridDim.x + blk) * a.pipe_seg_cap + off);
-        if (lane == 0) tot.events += d.y;
-        uint2 e[kInFlight];
+    for (int u = 0; u < kInFlight; ++u)
+        if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
 #pragma unroll
-        for (int u = 0; u < kInFlight; ++u)
-            if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
-#pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-            if (lane + 32u * u < d.y) {
-                uint32_t slot = d.z + (e[u].x >> (tb + 2));
-                if (slot >= a.ring_slots) slot -= a.ring_slots;
-                atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
-                          __uint_as_float(e[u].y));
-            }
+    for (int u = 0; u < kInFlight; ++u) {
+        if (lane + 32u * u < d.y) {
+            uint32_t slot = d.z + (e[u].x >> (tb + 2));
+            if (slot >= a.ring_slots) slot -= a.ring_slots;
+            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
+                      __uint_as_float(e[u].y));
         }
     }
+}
+
+// Delivery of list L (written in the phase with tag `tag`) by warp `w` of this block's delivery
+// warps: chunk 4r + w of block b - r for r < kSpill, found by their tag, then this block's own
+// chunks beyond 4 * kSpill. Called by whole warps.
+__device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t w,
+                                             uint32_t lane, DeliveryTotals& tot) {
+    const uint32_t G = gridDim.x;
+    uint4 d = make_uint4(0u, 0u, 0u, 0u);
+    if (lane < kSpill) {
+        const uint32_t src = (blockIdx.x + G - lane % G) % G;
+        d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + 4u * lane + w);
+    }
+    uint32_t valid = __ballot_sync(0xffffffffu, lane < kSpill && lane < G && d.w == tag && 4u * lane + w < a.pipe_seg_cap);
+    unsigned long long events = 0ull;
+    while (valid) {
+        const int r = __ffs(valid) - 1;
+        valid &= valid - 1u;
+        uint4 c;
+        c.x = __shfl_sync(0xffffffffu, d.x, r);
+        c.y = __shfl_sync(0xffffffffu, d.y, r);
+        c.z = __shfl_sync(0xffffffffu, d.z, r);
+        c.w = tag;
+        events += c.y;
+        stream_chunk(a, c, lane);
+    }
+    // a block with more than 4 * kSpill chunks (or fewer blocks than kSpill) keeps the rest
+    const uint32_t n_own = min(sh.chunks[L], a.pipe_seg_cap);
+    const uint32_t first = 4u * min(kSpill, G);
+    for (uint32_t j = first + w; j < n_own; j += 4u) {
+        const uint4 c = __ldcg(a.pipe_seg + ((size_t)L * G + blockIdx.x) * a.pipe_seg_cap + j);
+        events += c.y;
+        stream_chunk(a, c, lane);
+    }
+    if (lane == 0) tot.events += events;
 }
 
 // Spike log of the phase whose list has parity q (stamps count from prev_start); one warp.
@@ -210,7 +198,6 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     if (threadIdx.x == 0) {
         sh.count[0] = sh.count[1] = 0u;
         sh.chunks[0] = sh.chunks[1] = sh.chunks[2] = 0u;
-        sh.arrive[0] = sh.arrive[1] = sh.arrive[2] = 0u;
     }
     if (use_smem) {
         const int words = a.n_types * (int)(sizeof(TypeConsts) / 4);
@@ -271,7 +258,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }                                                                    \
     }                                                                        \
     const uint32_t par = p & 1u;                                             \
-    const uint32_t L = p % 3u;
+    const uint32_t L = p % 3u;                                               \
+    const uint32_t tag = (uint32_t)start + 1u; /* of what this phase emits */
 
     if (is_upd) {
         // ================= update warps: take the registers the delivery warps give up
@@ -341,18 +329,17 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                             if (pos < kPendP) sh.pend[par][pos] = (j << kSrcBits) | (a.lo + i0 + jj);
                             else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
                             const uint2 r = sh.rows[threadIdx.x * kNeuronsPerThread + jj];
-                            push_chunks(a, sh, L, r.x, r.y, sl);
+                            push_chunks(a, sh, L, tag, r.x, r.y, sl);
                         }
                     }
                 }
                 sl = wrap_slot(sl + 1u, S);
             }
-            warp_arrive(a, sh, L);
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
             grid.sync();
             if (timer_u) {
                 const unsigned long long t_end = gtimer();
-                acc_work += t_work - t_mark;
+                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
                 acc_wait += t_end - t_work;
                 t_mark = t_end;
             }
@@ -376,9 +363,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
 #if BMTK_PIPE_SETMAXNREG
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsDelivery));
 #endif
-        const uint32_t lane = dtid & 31u;
-        const uint32_t n_warps = gridDim.x * (kDT / 32);
-        const uint32_t gw = (dtid >> 5) * gridDim.x + blockIdx.x;   // consecutive chunks go to different SMs
+        const uint32_t lane = dtid & 31u, dwarp = dtid >> 5;
         unsigned long long prev_start = step_base;
         DeliveryTotals tot = {0ull, 0ull, 0ull};
         while (s < a.n_steps) {
@@ -386,11 +371,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             const uint32_t q = par ^ 1u;
             if (dtid == 0) {
                 // the list of the NEXT phase was last read one phase ago
-                const uint32_t Ln = (p + 1u) % 3u;
-                sh.chunks[Ln] = 0u;
-                sh.arrive[Ln] = 0u;
+                sh.chunks[(p + 1u) % 3u] = 0u;
             }
-            if (p > 0) deliver_list(a, (p + 2u) % 3u, gw, n_warps, lane, tot);
+            if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
             const unsigned long long t_rows = timer_d ? gtimer() : 0ull;
             // ---- off the rows' critical path. First half of the delivery warps: spike log of the previous
             // phase; second half: this phase's input spikes.
@@ -405,8 +388,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     }
                 }
             } else {
-                prepare_inputs(a, sh, L, start, slot, len, dtid - kDT / 2, kDT / 2, tot);
-                warp_arrive(a, sh, L);
+                prepare_inputs(a, sh, L, tag, start, slot, len, dtid - kDT / 2, kDT / 2, tot);
             }
             if (IEXT && clamp_next) {
                 // changes effective from the next phase's first step: nobody reads i_ext before the barrier
@@ -420,7 +402,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             grid.sync();
             if (timer_d) {
                 const unsigned long long t_end = gtimer();
-                acc_work += t_work - t_mark;
+                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
                 acc_wait += t_end - t_work;
                 acc_rows += t_rows - t_mark;
                 t_mark = t_end;
@@ -434,7 +416,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
         if (p > 0) {
-            deliver_list(a, (p + 2u) % 3u, gw, n_warps, lane, tot);
+            deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
             if (dtid < 32) {
                 const uint32_t q = (p & 1u) ^ 1u;
                 const uint32_t n_rec = min(sh.count[q], kPendP);
@@ -445,7 +427,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         if (timer_d) {
             a.ctl->t_prop_ns += acc_work;
             a.ctl->t_sync2_ns += acc_wait;
-            a.ctl->t_dbg[0] += acc_rows;
+            a.ctl->t_rows_ns += acc_rows;
         }
         if (tot.events) atomicAdd(&a.ctl->n_events, tot.events);
         if (tot.inputs) atomicAdd(&a.ctl->n_input_spikes, tot.inputs);

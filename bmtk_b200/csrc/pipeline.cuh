@@ -3,7 +3,7 @@
 
 namespace bmtk {
 
-constexpr uint32_t kPipeMaxBlocks = 160;    // blocks (SMs) the delivery warps' count scan is laid out for
+constexpr uint32_t kPipeMaxBlocks = 512;    // largest grid (one block per SM)
 constexpr uint32_t kPipeSegCap = 1024;      // chunk descriptors one block can add to one phase's list
 
 // Pipelined persistent kernel (update and delivery warps side by side on every SM). Takes the

@@ -145,8 +145,13 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
  *  "ring_prefetch"  0|1 persistent kernel with resident state: fetch the next step's ring slot into shared
  *                   memory with cp.async while the current step computes (default 0: on the 2-step
  *                   windows of the benchmark network it measured 3 % slower than plain L2 loads)
- *  "phase_timers"   0|1 let the persistent kernel accumulate the device time of its update and
- *                   delivery phases (counters "phase_update_ns", "phase_propagate_ns", "phase_windows")
+ *  "spike_store_reserve"  pin host memory for this many recorded spikes now (the store otherwise grows in
+ *                   blocks of 2 Mi spikes as they arrive; any time)
+ *  "phase_timers"   0|1 let the persistent kernels accumulate device time as seen by block 0 (counters
+ *                   "phase_windows" = barrier-delimited phases timed; "phase_update_ns" / "phase_propagate_ns" =
+ *                   time of the update / delivery side including its barrier wait, "phase_sync1_ns" /
+ *                   "phase_sync2_ns" = that wait; the two sides follow each other in the two-phase kernel and
+ *                   run side by side in the pipelined one, where "phase_rows_ns" is the row-streaming part)
  *  "use_graph"      0|1 replay each window as a CUDA graph when not persistent (default 1)
  *  "chunk_steps"    steps between host drains of the spike log / traces */
 int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
