@@ -37,23 +37,25 @@ namespace bmtk {
 constexpr int kUT = 512;            // update threads (four warpgroups)
 constexpr int kDT = 128;            // delivery threads (one warpgroup)
 constexpr int kBT = kUT + kDT;
-constexpr int kInFlight = 8;        // row entries each delivery lane has in flight
+constexpr int kInFlight = 8; // row entries each delivery lane has in flight
 constexpr uint32_t kChunk = 32 * kInFlight;   // entries of one chunk: one round of one delivery warp
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
 constexpr uint32_t kSpill = 4;      // a block's chunks 4r .. 4r+3 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
 #ifndef BMTK_PIPE_SETMAXNREG
-#define BMTK_PIPE_SETMAXNREG 1
+#define BMTK_PIPE_SETMAXNREG 0
 #endif
-// The block is launched with 96 registers per thread (64 K / 640, rounded down to 8). The delivery
-// warpgroup drops to 64 and the four update warpgroups rise to 104:
-// 128 x (96 - 64) registers released = 512 x (104 - 96) claimed.
+// Optional (off: it measured 3 % slower on the benchmark network): the block is launched with 96
+// registers per thread (64 K / 640, rounded down to 8); the delivery warpgroup drops to 64 and the
+// four update warpgroups rise to 104: 128 x (96 - 64) registers released = 512 x (104 - 96) claimed.
 constexpr int kRegsUpdate = 104;
 constexpr int kRegsDelivery = 64;
 
 struct __align__(16) PipeShared {
     uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
+    uint32_t pad;
+    uint4 own[3][kDT / 32];         // copies of the first descriptors of list L: the ones this block delivers itself
     uint2 rows[kUT * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
     uint32_t pend[2][kPendP];       // step in phase << kSrcBits | id
 };
@@ -69,7 +71,9 @@ __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh
     const uint32_t pos = atomicAdd(&sh.chunks[L], n);
     uint4* seg = a.pipe_seg + ((size_t)L * gridDim.x + blockIdx.x) * a.pipe_seg_cap;
     for (uint32_t c = 0; c < n; ++c) {
-        if (pos + c < a.pipe_seg_cap) seg[pos + c] = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, tag);
+        const uint4 d = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, tag);
+        if (pos + c < kDT / 32) sh.own[L][pos + c] = d;   // stays on the SM: no round trip to find it
+        else if (pos + c < a.pipe_seg_cap) seg[pos + c] = d;
         else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
     }
 }
@@ -142,13 +146,20 @@ __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d
 __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t w,
                                              uint32_t lane, DeliveryTotals& tot) {
     const uint32_t G = gridDim.x;
+    // the neighbours' descriptors are requested first, then this block's own chunk (descriptor in shared
+    // memory) is streamed while they are on their way
     uint4 d = make_uint4(0u, 0u, 0u, 0u);
-    if (lane < kSpill) {
-        const uint32_t src = (blockIdx.x + G - lane % G) % G;
+    if (lane >= 1 && lane < kSpill && lane < G) {
+        const uint32_t src = (blockIdx.x + G - lane) % G;
         d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + 4u * lane + w);
     }
-    uint32_t valid = __ballot_sync(0xffffffffu, lane < kSpill && lane < G && d.w == tag && 4u * lane + w < a.pipe_seg_cap);
     unsigned long long events = 0ull;
+    if (w < min(sh.chunks[L], a.pipe_seg_cap)) {
+        const uint4 c = sh.own[L][w];
+        events += c.y;
+        stream_chunk(a, c, lane);
+    }
+    uint32_t valid = __ballot_sync(0xffffffffu, lane >= 1 && lane < kSpill && lane < G && d.w == tag);
     while (valid) {
         const int r = __ffs(valid) - 1;
         valid &= valid - 1u;

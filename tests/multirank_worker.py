@@ -69,7 +69,7 @@ def main():
             k = min(len(ast), len(rst))
             neq = np.nonzero((ast[:k] != rst[:k]) | (aids[:k] != rids[:k]))[0]
             div = int(ast[neq[0]]) if len(neq) else net.n_steps
-            ok &= div > 800 and abs(len(ast) - len(rst)) <= 0.03 * len(rst) and eng.counter('launches') < 20
+            ok &= div > 800 and abs(len(ast) - len(rst)) <= 0.03 * len(rst) and eng.counter('launches') < 40   # 5 cooperative launches + log sorts, not 300 windows x 2
             rowptr = ref.csr()[0].astype(np.int64)
             outdeg = np.diff(rowptr)
             sys.path.insert(0, os.path.join(ROOT, 'tests'))
