@@ -42,7 +42,8 @@ BYTES_PER_EVENT = 16.0
 # per update step for the persistent kernel (profiles/persistent_kernel_c3_phases.md), per launch for the others
 # (profiles/glif_update_2M_neurons_ncu_full.md scaled to this network, profiles/propagate_atomic_c2like_100k_ncu_full.md
 # at 12.4 B per event)
-NCU_TRAFFIC_BYTES = {'glif_update': 102.8 * 230924, 'propagate': None, 'persistent_per_step': 5.97e6}
+NCU_TRAFFIC_BYTES = {'glif_update': 102.8 * 230924, 'propagate': None, 'persistent_per_step': 5.97e6,
+                     'pipelined_per_step': 4.05e6}
 
 
 def parse_args():
@@ -349,8 +350,9 @@ def main():
         roofline = {
             'kernel': 'pipelined_kernel' if phases['pipelined'] else 'persistent_kernel', 'bound': 'hbm',
             'achieved': alg_bytes / launch_ns, 'peak': peak, 'unit': 'GB/s', 'frac': alg_bytes / launch_ns / peak,
-            'traffic': NCU_TRAFFIC_BYTES['persistent_per_step'] * steps_per_bench_step, 'peak_kind': peak_kind,
-            'traffic_note': 'dram bytes of one persistent launch (= one bench step), ncu on a 100-step launch scaled by steps',
+            'traffic': NCU_TRAFFIC_BYTES['pipelined_per_step' if phases['pipelined'] else 'persistent_per_step'] * steps_per_bench_step,
+            'peak_kind': peak_kind,
+            'traffic_note': 'dram bytes of one cooperative launch (= one bench step), ncu on a 100-step launch scaled by steps',
             'timing': 'CUDA events on the launching stream around the %d timed launches (one per bench step)' % args.steps,
             'bytes_per_launch': alg_bytes,
             'note': 'algorithmic bytes = 128 B per neuron-step + 16 B per synaptic event; the kernel keeps the 96 B of '
