@@ -61,10 +61,20 @@ def parse_args():
                     help='c3: the V1-scale network (the headline line). c4: trial sweep, the 50 000-neuron E/I network as 64 '
                          'independent trials over one CSR, trials sharded over the ranks, one step = 500 ms')
     ap.add_argument('--trials', type=int, default=64)
+    ap.add_argument('--engine-option', action='append', default=[], metavar='KEY=VALUE',
+                    help='extra engine option (bmtk_engine_set_option), e.g. pipeline=0 for the two-phase persistent kernel')
     ap.add_argument('--exchange', default='p2p', choices=['p2p', 'nccl'],
                     help='several ranks: spike exchange inside the persistent kernel over peer memory, or one NCCL '
                          'all-gather per window around the per-step kernels')
     return ap.parse_args()
+
+
+def extra_options(args):
+    out = {}
+    for kv in args.engine_option:
+        k, _, v = kv.partition('=')
+        out[k] = int(v)
+    return out
 
 
 def make_network(scale, lo_hi=None, poisson_online=True):
@@ -260,7 +270,7 @@ def main():
     # ---------------- device-resident run
     t0 = time.time()
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                         options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
+                         options=dict(chunk_steps=steps_per_bench_step, **extra_options(args)), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
                          libnccl=libnccl, p2p=args.exchange == 'p2p')
     t_build = time.time() - t0
     n_warm = 0
@@ -376,7 +386,7 @@ def main():
     if not args.no_e2e:
         net.poisson_rate_hz, rates = None, net.poisson_rate_hz.astype(np.float64)
         eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                             options=dict(chunk_steps=steps_per_bench_step), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
+                             options=dict(chunk_steps=steps_per_bench_step, **extra_options(args)), rank=rank, n_ranks=world, nccl_uid=fresh_uid(),
                              libnccl=libnccl, p2p=args.exchange == 'p2p')
         rng = np.random.default_rng(99)   # same seed on every rank: virtual cells are replicated
         n_chunks = 1 + args.steps
@@ -469,7 +479,7 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
     net = W.c4(n=n, in_degree=min(1000, n // 4), n_virtual=max(8, int(round(2000 * args.scale))), t_stop_ms=step_ms)
     n_steps = int(round(step_ms / net.dt))
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                         options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000))
+                         options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000, **extra_options(args)))
     MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
     n_warm = 0
     for _ in range(args.warmup):
