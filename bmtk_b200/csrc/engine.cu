@@ -314,6 +314,7 @@ struct bmtk_engine {
     bool pipeline = true;     // option: use the pipelined kernel where it applies
     bool pipe_ok = false;     // resident state, one trial, min delay >= 2 steps
     int pipe_blocks = 0;
+    uint32_t pipe_upd_warps = 0;   // update warps per block: what the network needs at 128 neurons per warp
     uint32_t* d_virt2 = nullptr;
     uint4* d_plists[2] = {nullptr, nullptr};
     uint32_t* d_plist_counts = nullptr;
@@ -770,6 +771,17 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
         a.pipe_seg = e->d_pipe_seg;
         a.pipe_seg_cap = kPipeSegCap;
+        a.upd_warps = e->pipe_upd_warps;
+        // input warps: one thread per 2 Poisson cells of the block's share, at most half of the non-update warps;
+        // replayed spikes alone get one warp
+        {
+            const uint32_t free_warps = pipelined_warps() - e->pipe_upd_warps;
+            uint32_t iw = 0;
+            if (e->has_poisson) iw = (uint32_t)((e->n_virtual / e->pipe_blocks + 63) / 64);
+            if (e->d_in_ptr) iw = std::max(iw, 1u);
+            if (e->has_poisson) iw = std::max(iw, 1u);
+            a.input_warps = std::min(iw, free_warps / 2);
+        }
         CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
     } else {
         CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
@@ -1311,7 +1323,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
             if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
                 // chunks of 32 groups are dealt round-robin to the update warps of the blocks
                 const uint64_t chunks = ((uint64_t)(e->n_pad / 4) + 31) / 32;
-                e->pipe_ok = (chunks + pb - 1) / pb <= pipelined_update_threads() / 32;
+                e->pipe_upd_warps = (uint32_t)std::max<uint64_t>(1, (chunks + pb - 1) / pb);
+                e->pipe_ok = e->pipe_upd_warps <= pipelined_max_update_warps();
                 e->pipe_blocks = pb;
                 if (e->has_poisson) {
                     // a block adds its share of the Poisson spikes to its segment of the phase list: leave half for neurons
@@ -1756,6 +1769,7 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
+    else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;
     else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && e->n_ranks == 1) ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else if (k == "n_pad1") *out = e->n_pad1;

@@ -1,8 +1,8 @@
 // Pipelined persistent kernel: neuron update and spike delivery run CONCURRENTLY on every SM.
 //
-// One block per SM stays resident for a whole chunk of steps (cooperative launch). Its first 512
-// threads ("update warps") own four neurons each, state in registers for the whole launch; its last
-// 128 threads ("delivery warps") stream CSR rows into the ring. Time is cut into phases of
+// One block of 640 threads per SM stays resident for a whole chunk of steps (cooperative launch). Its
+// first 13 warps ("update warps") own four neurons per thread, state in registers for the whole launch;
+// its last 7 warps ("delivery warps") stream CSR rows into the ring. Time is cut into phases of
 // h = floor(min_delay / 2) steps. In phase p
 //   * the update warps run the phase's h steps back to back (ring slot in, state update, slot
 //     cleared); a spike is cut into chunks of at most 256 CSR entries whose descriptors
@@ -11,7 +11,7 @@
 //   * half of the delivery warps draw the phase's Poisson cells (or pick up replayed virtual
 //     spikes) and add their chunks to the same list;
 //   * the delivery warps share the chunks listed in phase p-1 with their neighbours: chunk j of
-//     block b is delivered by warp j mod 4 of block b + j / 4, so a busy block's spikes spill over
+//     block b is delivered by warp j mod D of block b + j / D (D delivery warps), so a busy block's spikes spill over
 //     to the following SMs. A descriptor carries the tag of its phase, so a warp simply loads the
 //     few slots it is responsible for (one round trip, no counts to read first), keeps those with
 //     the right tag and streams them, up to 8 entries per lane in flight;
@@ -34,29 +34,23 @@ namespace cg = cooperative_groups;
 
 namespace bmtk {
 
-constexpr int kUT = 512;            // update threads (four warpgroups)
-constexpr int kDT = 128;            // delivery threads (one warpgroup)
-constexpr int kBT = kUT + kDT;
-constexpr int kInFlight = 8; // row entries each delivery lane has in flight
+// A block has 20 warps (640 threads, 96 registers each). The first PersistArgs::upd_warps of them are
+// update warps - as many as the network needs at 128 neurons per warp, at most 16 - and the rest
+// deliver: 13 + 7 for 230 924 neurons on 148 SMs, 3 + 17 for 50 000.
+constexpr int kBT = 640;
+constexpr int kWarps = kBT / 32;
+constexpr int kMaxUpdWarps = 16;
+constexpr int kInFlight = 8;         // row entries each delivery lane has in flight (more spills registers: slower)
 constexpr uint32_t kChunk = 32 * kInFlight;   // entries of one chunk: one round of one delivery warp
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
-constexpr uint32_t kSpill = 4;      // a block's chunks 4r .. 4r+3 go to block b + r, for r < kSpill; the rest stay home
+constexpr uint32_t kSpill = 4;      // a block's chunks kDW*r .. kDW*r + kDW-1 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
-#ifndef BMTK_PIPE_SETMAXNREG
-#define BMTK_PIPE_SETMAXNREG 0
-#endif
-// Optional (off: it measured 3 % slower on the benchmark network): the block is launched with 96
-// registers per thread (64 K / 640, rounded down to 8); the delivery warpgroup drops to 64 and the
-// four update warpgroups rise to 104: 128 x (96 - 64) registers released = 512 x (104 - 96) claimed.
-constexpr int kRegsUpdate = 104;
-constexpr int kRegsDelivery = 64;
-
 struct __align__(16) PipeShared {
     uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
     uint32_t pad;
-    uint4 own[3][kDT / 32];         // copies of the first descriptors of list L: the ones this block delivers itself
-    uint2 rows[kUT * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
+    uint4 own[3][kWarps];      // copies of the first descriptors of list L: the ones this block delivers itself
+    uint2 rows[kMaxUpdWarps * 32 * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
     uint32_t pend[2][kPendP];       // step in phase << kSrcBits | id
 };
 static_assert(sizeof(PipeShared) % 16 == 0, "the type table behind it is read with 128-bit loads");
@@ -69,10 +63,11 @@ __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh
     const uint32_t n = (len + kChunk - 1) / kChunk;
     if (n == 0) return;
     const uint32_t pos = atomicAdd(&sh.chunks[L], n);
+    const uint32_t kDW = kWarps - a.upd_warps - a.input_warps;   // warps that stream chunks
     uint4* seg = a.pipe_seg + ((size_t)L * gridDim.x + blockIdx.x) * a.pipe_seg_cap;
     for (uint32_t c = 0; c < n; ++c) {
         const uint4 d = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, tag);
-        if (pos + c < kDT / 32) sh.own[L][pos + c] = d;   // stays on the SM: no round trip to find it
+        if (pos + c < kDW) sh.own[L][pos + c] = d;   // stays on the SM: no round trip to find it
         else if (pos + c < a.pipe_seg_cap) seg[pos + c] = d;
         else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
     }
@@ -85,21 +80,32 @@ struct DeliveryTotals {
 // Input spikes of the phase [start, start + len) whose first step uses ring slot `slot`: Poisson
 // cells (dealt round-robin over the blocks) and this block's share of the replayed spikes, on
 // `n_thr` threads of which this is thread `t`.
+struct CachedCell {
+    uint4 thr;           // Poisson thresholds of the thread's first cell
+    uint32_t begin, len; // its CSR row
+};
+
 __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag,
-                                               unsigned long long start,
+                                               const CachedCell& cc, unsigned long long start,
                                                uint32_t slot, uint32_t len, uint32_t t, uint32_t n_thr, DeliveryTotals& tot) {
     if (a.poisson_thr) {
-        for (uint32_t v = t * gridDim.x + blockIdx.x; v < a.n_virtual; v += n_thr * gridDim.x) {
-            const uint4 thr = __ldg(a.poisson_thr + v);
+        const uint32_t v0 = t * gridDim.x + blockIdx.x;
+        for (uint32_t v = v0; v < a.n_virtual; v += n_thr * gridDim.x) {
+            // the first cell of a thread is kept in registers: no load between the barrier and its spikes
+            const uint4 thr = v == v0 ? cc.thr : __ldg(a.poisson_thr + v);
             for (uint32_t j = 0; j < len; ++j) {
                 const unsigned long long step = start + j;
                 const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base, (uint32_t)a.seed,
                                                  (uint32_t)(a.seed >> 32)).x;
                 const uint32_t k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
                 if (k) {
-                    const unsigned long long rb = a.rowptr[a.n_global + v], re = a.rowptr[a.n_global + v + 1];
-                    for (uint32_t c = 0; c < k; ++c)
-                        push_chunks(a, sh, L, tag, (uint32_t)rb, (uint32_t)(re - rb), wrap_slot(slot + j, a.ring_slots));
+                    uint32_t rb = cc.begin, rl = cc.len;
+                    if (v != v0) {
+                        const unsigned long long b0 = a.rowptr[a.n_global + v], b1 = a.rowptr[a.n_global + v + 1];
+                        rb = (uint32_t)b0;
+                        rl = (uint32_t)(b1 - b0);
+                    }
+                    for (uint32_t c = 0; c < k; ++c) push_chunks(a, sh, L, tag, rb, rl, wrap_slot(slot + j, a.ring_slots));
                     tot.inputs += k;
                 }
             }
@@ -141,17 +147,17 @@ __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d
 }
 
 // Delivery of list L (written in the phase with tag `tag`) by warp `w` of this block's delivery
-// warps: chunk 4r + w of block b - r for r < kSpill, found by their tag, then this block's own
-// chunks beyond 4 * kSpill. Called by whole warps.
+// warps: chunk kDW*r + w of block b - r for r < kSpill, found by their tag, then this block's own
+// chunks beyond kDW * kSpill. Called by whole warps.
 __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t w,
                                              uint32_t lane, DeliveryTotals& tot) {
-    const uint32_t G = gridDim.x;
+    const uint32_t G = gridDim.x, kDW = kWarps - a.upd_warps - a.input_warps;   // warps that stream chunks
     // the neighbours' descriptors are requested first, then this block's own chunk (descriptor in shared
     // memory) is streamed while they are on their way
     uint4 d = make_uint4(0u, 0u, 0u, 0u);
     if (lane >= 1 && lane < kSpill && lane < G) {
         const uint32_t src = (blockIdx.x + G - lane) % G;
-        d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + 4u * lane + w);
+        d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + kDW * lane + w);
     }
     unsigned long long events = 0ull;
     if (w < min(sh.chunks[L], a.pipe_seg_cap)) {
@@ -171,10 +177,10 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
         events += c.y;
         stream_chunk(a, c, lane);
     }
-    // a block with more than 4 * kSpill chunks (or fewer blocks than kSpill) keeps the rest
+    // a block with more than kDW * kSpill chunks (or fewer blocks than kSpill) keeps the rest
     const uint32_t n_own = min(sh.chunks[L], a.pipe_seg_cap);
-    const uint32_t first = 4u * min(kSpill, G);
-    for (uint32_t j = first + w; j < n_own; j += 4u) {
+    const uint32_t first = kDW * min(kSpill, G);
+    for (uint32_t j = first + w; j < n_own; j += kDW) {
         const uint4 c = __ldcg(a.pipe_seg + ((size_t)L * G + blockIdx.x) * a.pipe_seg_cap + j);
         events += c.y;
         stream_chunk(a, c, lane);
@@ -218,6 +224,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     }
     const TypeConsts* types = use_smem ? s_types : a.types;
 
+    const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
+    const uint32_t kCW = kDW - a.input_warps;   // delivery warps that stream chunks; the others prepare input spikes
     const bool is_upd = threadIdx.x < kUT;
     const uint32_t dtid = threadIdx.x - kUT;
     const uint32_t n_groups = a.n_pad / kNeuronsPerThread;
@@ -273,10 +281,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     const uint32_t tag = (uint32_t)start + 1u; /* of what this phase emits */
 
     if (is_upd) {
-        // ================= update warps: take the registers the delivery warps give up
-#if BMTK_PIPE_SETMAXNREG
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsUpdate));
-#endif
+        // ================= update warps
         Neuron4<THETA, IEXT> nr;
         int pslot[4] = {-1, -1, -1, -1};
         if (mine) {
@@ -371,12 +376,19 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
     } else {
         // ================= delivery warps
-#if BMTK_PIPE_SETMAXNREG
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsDelivery));
-#endif
         const uint32_t lane = dtid & 31u, dwarp = dtid >> 5;
+        const bool input_role = dwarp >= kCW;
+        const uint32_t it = dtid - 32u * kCW, n_it = 32u * a.input_warps;   // input thread index / count
         unsigned long long prev_start = step_base;
         DeliveryTotals tot = {0ull, 0ull, 0ull};
+        CachedCell cc = {make_uint4(0u, 0u, 0u, 0u), 0u, 0u};
+        if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual) {
+            const uint32_t v0 = it * gridDim.x + blockIdx.x;
+            cc.thr = __ldg(a.poisson_thr + v0);
+            const unsigned long long b0 = a.rowptr[a.n_global + v0], b1 = a.rowptr[a.n_global + v0 + 1];
+            cc.begin = (uint32_t)b0;
+            cc.len = (uint32_t)(b1 - b0);
+        }
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
             const uint32_t q = par ^ 1u;
@@ -384,11 +396,14 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 // the list of the NEXT phase was last read one phase ago
                 sh.chunks[(p + 1u) % 3u] = 0u;
             }
-            if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
-            const unsigned long long t_rows = timer_d ? gtimer() : 0ull;
-            // ---- off the rows' critical path. First half of the delivery warps: spike log of the previous
-            // phase; second half: this phase's input spikes.
-            if (dtid < kDT / 2) {
+            unsigned long long t_rows = 0ull;
+            if (input_role) {
+                // this phase's input spikes, from the start of the phase
+                prepare_inputs(a, sh, L, tag, cc, start, slot, len, it, n_it, tot);
+            } else {
+                if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                if (timer_d) t_rows = gtimer();
+                // off the chunks' critical path: the spike log of the previous phase
                 if (dtid < 32 && p > 0) {
                     const uint32_t n_rec = min(sh.count[q], kPendP);
                     if (a.log_stamp && n_rec) write_log(a, sh, dtid, n_rec, q, prev_start);
@@ -398,8 +413,6 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                         tot.spikes += n_rec;
                     }
                 }
-            } else {
-                prepare_inputs(a, sh, L, tag, start, slot, len, dtid - kDT / 2, kDT / 2, tot);
             }
             if (IEXT && clamp_next) {
                 // changes effective from the next phase's first step: nobody reads i_ext before the barrier
@@ -415,7 +428,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
                 acc_wait += t_end - t_work;
-                acc_rows += t_rows - t_mark;
+                acc_rows += (t_rows ? t_rows : t_mark) - t_mark;
                 t_mark = t_end;
             }
             if (IEXT && clamp_next)
@@ -426,7 +439,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             ++p;
         }
         // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
-        if (p > 0) {
+        if (p > 0 && !input_role) {
             deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
             if (dtid < 32) {
                 const uint32_t q = (p & 1u) ^ 1u;
@@ -456,7 +469,8 @@ size_t pipelined_smem(int n_types) {
     return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0);
 }
 
-uint32_t pipelined_update_threads() { return kUT; }
+uint32_t pipelined_max_update_warps() { return kMaxUpdWarps; }
+uint32_t pipelined_warps() { return kWarps; }
 
 int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem) {
     int per_sm = 0, sms = 0;
