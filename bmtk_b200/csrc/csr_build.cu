@@ -54,6 +54,23 @@ __global__ void pack_log_kernel(uint32_t n, const uint32_t* stamp, const uint32_
     if (i < n) keys[i] = ((unsigned long long)(stamp[i] - stamp_base) << id_bits) | id[i];
 }
 
+// The same for a log kept in per-block segments of seg_cap entries with counts seg_cnt[n_seg]: thread
+// block b packs segment b behind the segments before it (every block adds up the counts before its own).
+__global__ void pack_log_segments_kernel(uint32_t n_seg, uint32_t seg_cap, const uint32_t* seg_cnt, const uint32_t* stamp,
+                                         const uint32_t* id, uint32_t stamp_base, uint32_t id_bits, unsigned long long* keys) {
+    __shared__ uint32_t s_off;
+    if (threadIdx.x == 0) {
+        uint32_t off = 0;
+        for (uint32_t b = 0; b < blockIdx.x; ++b) off += seg_cnt[b];
+        s_off = off;
+    }
+    __syncthreads();
+    const uint32_t n = seg_cnt[blockIdx.x], off = s_off;
+    const size_t base = (size_t)blockIdx.x * seg_cap;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x)
+        keys[off + i] = ((unsigned long long)(stamp[base + i] - stamp_base) << id_bits) | id[base + i];
+}
+
 __global__ void unpack_log_kernel(uint32_t n, const unsigned long long* keys, uint32_t stamp_base, uint32_t id_bits,
                                   uint32_t* stamp, uint32_t* id) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -73,9 +90,10 @@ size_t spike_log_sort_tmp_bytes(uint32_t capacity) {
 
 cudaError_t sort_spike_log(uint32_t n, uint32_t* d_stamp, uint32_t* d_id, uint32_t stamp_base, uint32_t stamp_bits,
                            uint32_t id_bits, unsigned long long* d_keys, unsigned long long* d_keys_out, void* tmp,
-                           size_t tmp_bytes, cudaStream_t stream) {
+                           size_t tmp_bytes, cudaStream_t stream, uint32_t n_seg, uint32_t seg_cap, const uint32_t* d_seg_cnt) {
     if (n == 0) return cudaSuccess;
-    pack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_stamp, d_id, stamp_base, id_bits, d_keys);
+    if (n_seg) pack_log_segments_kernel<<<n_seg, 256, 0, stream>>>(n_seg, seg_cap, d_seg_cnt, d_stamp, d_id, stamp_base, id_bits, d_keys);
+    else pack_log_kernel<<<(n + 255) / 256, 256, 0, stream>>>(n, d_stamp, d_id, stamp_base, id_bits, d_keys);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     int end_bit = (int)(stamp_bits + id_bits);

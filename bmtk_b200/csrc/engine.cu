@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "csr_build.cuh"
 #include <chrono>
+#include <cstddef>
 
 #include "persistent.cuh"
 #include "pipeline.cuh"
@@ -311,6 +312,8 @@ struct bmtk_engine {
     int persist_blocks = 0;
     bool persist_resident = false;
     uint4* d_pipe_seg = nullptr;
+    uint32_t* d_log_seg_cnt = nullptr;   // pipelined kernel: spikes each block logged in the last launch
+    bool log_segmented = false;          // the device log of the current chunk is in per-block segments
     bool pipeline = true;     // option: use the pipelined kernel where it applies
     bool pipe_ok = false;     // resident state, one trial, min delay >= 2 steps
     int pipe_blocks = 0;
@@ -330,6 +333,7 @@ struct bmtk_engine {
     size_t ce_group_next = 0;
     double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
     double phase_rows_ns = 0;
+    double phase_class_ns[3] = {0, 0, 0};   // pipelined kernel: sum over phases of the last update / chunk / input warp's finish
     double drain_wait_ns = 0, drain_sort_ns = 0;   // host clock: waiting for the chunk's kernels; sorting + copying its spike log
     uint64_t phase_windows = 0;
 
@@ -621,7 +625,8 @@ static int drain(bmtk_engine* e) {
         e->phase_sync1_ns += (double)h.t_sync1_ns;
         e->phase_sync2_ns += (double)h.t_sync2_ns;
         e->phase_rows_ns += (double)h.t_rows_ns;
-        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, 72, e->stream));
+        for (int q = 0; q < 3; ++q) e->phase_class_ns[q] += (double)h.t_class_sum[q];
+        CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, sizeof(Ctl) - offsetof(Ctl, t_update_ns), e->stream));
     }
     if (h.step_base != e->step)
         return fail(BMTK_E_INVALID, "device clock %llu differs from host clock %llu", (unsigned long long)h.step_base,
@@ -658,7 +663,7 @@ static int drain(bmtk_engine* e) {
         if (f & kErrVirtListFull)
             return fail(BMTK_E_OVERFLOW, "Poisson spike list full (capacity %u): raise option spike_capacity", e->virt_cap);
         if (f & kErrLogFull)
-            return fail(BMTK_E_OVERFLOW, "spike log full (capacity %llu): raise log_capacity or lower chunk_steps",
+            return fail(BMTK_E_OVERFLOW, "spike log full (capacity %llu, split evenly over the blocks of the pipelined kernel): raise log_capacity or lower chunk_steps",
                         (unsigned long long)e->log_cap);
         return fail(BMTK_E_OVERFLOW, "device buffer overflow (flags %u)", f);
     }
@@ -670,7 +675,9 @@ static int drain(bmtk_engine* e) {
         const uint32_t stamp_bits = bits_for(e->step - e->log_base_step + 1);
         const uint32_t id_bits = bits_for(std::max<uint64_t>(e->n_global, e->n_pad));
         CU(sort_spike_log((uint32_t)n, e->d_log_stamp, e->d_log_id, (uint32_t)e->log_base_step, stamp_bits, id_bits,
-                          e->d_log_keys, e->d_log_keys2, e->d_log_tmp, e->log_tmp_bytes, e->stream));
+                          e->d_log_keys, e->d_log_keys2, e->d_log_tmp, e->log_tmp_bytes, e->stream,
+                          e->log_segmented ? (uint32_t)e->pipe_blocks : 0u, (uint32_t)(e->log_cap / std::max(e->pipe_blocks, 1)),
+                          e->d_log_seg_cnt));
         e->launches += 3;
         // straight into the host store: chunks are consecutive in time, so it stays (stamp, id)-sorted
         constexpr size_t B = bmtk_engine::kSpkBlock;
@@ -692,6 +699,7 @@ static int drain(bmtk_engine* e) {
         e->drain_sort_ns += now_ns() - t1;
     }
     e->log_base_step = e->step;
+    e->log_segmented = false;
     if (!e->probe_ids.empty()) {
         const uint64_t have = e->step / e->probe_interval;
         const uint64_t n_new = have - e->samples_drained;
@@ -771,6 +779,9 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
         a.pipe_seg = e->d_pipe_seg;
         a.pipe_seg_cap = kPipeSegCap;
+        a.log_seg_cap = (uint32_t)(e->log_cap / e->pipe_blocks);
+        a.log_seg_cnt = e->d_log_seg_cnt;
+        e->log_segmented = e->record_spikes;
         a.upd_warps = e->pipe_upd_warps;
         // input warps: one thread per 2 Poisson cells of the block's share, at most half of the non-update warps;
         // replayed spikes alone get one warp
@@ -899,6 +910,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
         if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r]);
     cudaFree(e->d_xchg);
     cudaFree(e->d_pipe_seg);
+    cudaFree(e->d_log_seg_cnt);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     for (uint32_t* p : e->h_spk_blocks) cudaFreeHost(p);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -1335,6 +1347,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 }
                 if (e->pipe_ok) {
                     CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
+                    CU(cudaMalloc(&e->d_log_seg_cnt, 4 * (size_t)pb));
+                    CU(cudaMemset(e->d_log_seg_cnt, 0, 4 * (size_t)pb));
                     // a descriptor is valid by its tag (first step of its phase + 1): none is at rest
                     CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
                 }
@@ -1767,6 +1781,9 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "drain_wait_ns") *out = (uint64_t)e->drain_wait_ns;
     else if (k == "drain_sort_ns") *out = (uint64_t)e->drain_sort_ns;
     else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
+    else if (k == "phase_last_update_ns") *out = (uint64_t)e->phase_class_ns[0];
+    else if (k == "phase_last_chunk_ns") *out = (uint64_t)e->phase_class_ns[1];
+    else if (k == "phase_last_input_ns") *out = (uint64_t)e->phase_class_ns[2];
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;

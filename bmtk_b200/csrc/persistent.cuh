@@ -51,6 +51,8 @@ struct PersistArgs {
     // pipelined kernel: chunk lists [3][blocks][pipe_seg_cap] of {first entry, length, ring slot, phase tag}
     uint4* pipe_seg;
     uint32_t pipe_seg_cap;
+    uint32_t log_seg_cap;      // pipelined kernel: block b logs spikes into [b * log_seg_cap, (b + 1) * log_seg_cap) ...
+    uint32_t* log_seg_cnt;     // ... and leaves its entry count here
     uint32_t upd_warps;        // pipelined kernel: update warps of a block
     uint32_t input_warps;      // pipelined kernel: warps of a block that prepare input spikes; the rest stream chunks
     // clamp events grouped by step: group g covers events [ce_group_ptr[g], ce_group_ptr[g+1])

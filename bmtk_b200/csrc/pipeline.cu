@@ -188,21 +188,23 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
     if (lane == 0) tot.events += events;
 }
 
-// Spike log of the phase whose list has parity q (stamps count from prev_start); one warp.
+// Spike log of the phase whose list has parity q (stamps count from prev_start); one warp. Every block
+// logs into its own segment [blockIdx.x * log_seg_cap, ...) of the log arrays at a position the warp
+// carries in a register (`pos`, same on all lanes): no atomic, no round trip. The segments are laid end
+// to end when the host drains the log.
 __device__ __forceinline__ void write_log(const PersistArgs& a, PipeShared& sh, uint32_t lane, uint32_t n_rec, uint32_t q,
-                                          unsigned long long prev_start) {
-    uint32_t lbase = 0;
-    if (lane == 0) lbase = atomicAdd(&a.ctl->log_count, n_rec);
-    lbase = __shfl_sync(0xffffffffu, lbase, 0);
+                                          unsigned long long prev_start, uint32_t& pos) {
+    const size_t seg = (size_t)blockIdx.x * a.log_seg_cap;
     for (uint32_t k = lane; k < n_rec; k += 32) {
         const uint32_t e = sh.pend[q][k];
-        if (lbase + k < a.log_cap) {
-            a.log_stamp[lbase + k] = (uint32_t)(prev_start + (e >> kSrcBits) + 1ull);
-            a.log_id[lbase + k] = e & kSrcMask;
+        if (pos + k < a.log_seg_cap) {
+            a.log_stamp[seg + pos + k] = (uint32_t)(prev_start + (e >> kSrcBits) + 1ull);
+            a.log_id[seg + pos + k] = e & kSrcMask;
         } else {
             atomicOr(&a.ctl->error_flags, kErrLogFull);
         }
     }
+    pos = min(pos + n_rec, a.log_seg_cap);
 }
 
 template <bool THETA, bool IEXT>
@@ -352,8 +354,13 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 sl = wrap_slot(sl + 1u, S);
             }
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
+            if (a.profile && (threadIdx.x & 31) == 0) atomicMax(&a.ctl->t_class_last[par][0], gtimer());
             grid.sync();
             if (timer_u) {
+                a.ctl->t_class_sum[0] += __ldcg(&a.ctl->t_class_last[par][0]) - t_mark;
+                a.ctl->t_class_sum[1] += __ldcg(&a.ctl->t_class_last[par][1]) - t_mark;
+                a.ctl->t_class_sum[2] += __ldcg(&a.ctl->t_class_last[par][2]) - t_mark;
+                a.ctl->t_class_last[par ^ 1u][0] = a.ctl->t_class_last[par ^ 1u][1] = a.ctl->t_class_last[par ^ 1u][2] = t_mark;
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
                 acc_wait += t_end - t_work;
@@ -378,6 +385,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         // ================= delivery warps
         const uint32_t lane = dtid & 31u, dwarp = dtid >> 5;
         const bool input_role = dwarp >= kCW;
+        const uint32_t log_warp = a.input_warps ? kCW : 0u;   // the first input warp, else chunk warp 0
+        uint32_t log_pos = 0;   // entries this block has logged in this launch
         const uint32_t it = dtid - 32u * kCW, n_it = 32u * a.input_warps;   // input thread index / count
         unsigned long long prev_start = step_base;
         DeliveryTotals tot = {0ull, 0ull, 0ull};
@@ -403,15 +412,16 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             } else {
                 if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
                 if (timer_d) t_rows = gtimer();
-                // off the chunks' critical path: the spike log of the previous phase
-                if (dtid < 32 && p > 0) {
-                    const uint32_t n_rec = min(sh.count[q], kPendP);
-                    if (a.log_stamp && n_rec) write_log(a, sh, dtid, n_rec, q, prev_start);
-                    __syncwarp();
-                    if (dtid == 0) {
-                        sh.count[q] = 0u;    // the update warps append to it again in the next phase
-                        tot.spikes += n_rec;
-                    }
+            }
+            // The spike log of the previous phase (one atomic with a round trip, then stores) is kept off the
+            // chunk warps' path when there are input warps: they are done early. Otherwise chunk warp 0 has it.
+            if (dwarp == log_warp && p > 0) {
+                const uint32_t n_rec = min(sh.count[q], kPendP);
+                if (a.log_stamp && n_rec) write_log(a, sh, lane, n_rec, q, prev_start, log_pos);
+                __syncwarp();
+                if (lane == 0) {
+                    sh.count[q] = 0u;    // the update warps append to it again in the next phase
+                    tot.spikes += n_rec;
                 }
             }
             if (IEXT && clamp_next) {
@@ -423,6 +433,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 }
             }
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
+            if (a.profile && lane == 0) atomicMax(&a.ctl->t_class_last[par][input_role ? 2 : 1], gtimer());
             grid.sync();
             if (timer_d) {
                 const unsigned long long t_end = gtimer();
@@ -439,14 +450,18 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             ++p;
         }
         // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
-        if (p > 0 && !input_role) {
-            deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
-            if (dtid < 32) {
+        if (p > 0) {
+            if (!input_role) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+            if (dwarp == log_warp) {
                 const uint32_t q = (p & 1u) ^ 1u;
                 const uint32_t n_rec = min(sh.count[q], kPendP);
-                if (a.log_stamp && n_rec) write_log(a, sh, dtid, n_rec, q, prev_start);
-                if (dtid == 0) tot.spikes += n_rec;
+                if (a.log_stamp && n_rec) write_log(a, sh, lane, n_rec, q, prev_start, log_pos);
+                if (lane == 0) tot.spikes += n_rec;
             }
+        }
+        if (dwarp == log_warp && lane == 0 && a.log_stamp) {
+            a.log_seg_cnt[blockIdx.x] = log_pos;
+            if (log_pos) atomicAdd(&a.ctl->log_count, log_pos);
         }
         if (timer_d) {
             a.ctl->t_prop_ns += acc_work;
