@@ -21,6 +21,8 @@ enum : uint32_t {
     kErrVirtListFull = 4u,
     kErrEventsFull = 8u,
     kErrExchangeTimeout = 16u,
+    kErrSyncTimeout = 32u,
+    kErrBadChunk = 64u,
 };
 
 // Per node type constants for one resolution, fp32 copies of fp64 host values.

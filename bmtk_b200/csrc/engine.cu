@@ -312,6 +312,7 @@ struct bmtk_engine {
     int persist_blocks = 0;
     bool persist_resident = false;
     uint4* d_pipe_seg = nullptr;
+    uint32_t* d_pipe_sync = nullptr;     // pipelined kernel: the two phase counters
     uint32_t* d_log_seg_cnt = nullptr;   // pipelined kernel: spikes each block logged in the last launch
     bool log_segmented = false;          // the device log of the current chunk is in per-block segments
     bool pipeline = true;     // option: use the pipelined kernel where it applies
@@ -657,6 +658,12 @@ static int drain(bmtk_engine* e) {
                         "at most 4096 spikes per block and window, the pipelined kernel 2048 per block and phase): raise option "
                         "spike_capacity, or set pipeline = 0 or persistent = 0",
                         e->send_cap);
+        if (f & kErrBadChunk)
+            return fail(BMTK_E_CUDA, "pipelined kernel: a chunk descriptor outside the CSR was read (a list was not complete); "
+                        "the results of this run are invalid (set option pipeline = 0)");
+        if (f & kErrSyncTimeout)
+            return fail(BMTK_E_CUDA, "pipelined kernel: a phase hand-over between update and delivery warps timed out; "
+                        "the results of this run are invalid (set option pipeline = 0)");
         if (f & kErrExchangeTimeout)
             return fail(BMTK_E_COMM, "spike exchange timed out: a rank did not publish its window within ~1 s "
                         "(rank %d of %d); the results of this run are invalid", e->rank, e->n_ranks);
@@ -779,6 +786,9 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
         a.pipe_seg = e->d_pipe_seg;
         a.pipe_seg_cap = kPipeSegCap;
+        a.n_entries = e->n_edges;
+        a.pipe_sync = e->d_pipe_sync;
+        CU(cudaMemsetAsync(e->d_pipe_sync, 0, 32, e->stream));
         a.log_seg_cap = (uint32_t)(e->log_cap / e->pipe_blocks);
         a.log_seg_cnt = e->d_log_seg_cnt;
         e->log_segmented = e->record_spikes;
@@ -911,6 +921,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_xchg);
     cudaFree(e->d_pipe_seg);
     cudaFree(e->d_log_seg_cnt);
+    cudaFree(e->d_pipe_sync);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     for (uint32_t* p : e->h_spk_blocks) cudaFreeHost(p);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -1347,6 +1358,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 }
                 if (e->pipe_ok) {
                     CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
+                    CU(cudaMalloc(&e->d_pipe_sync, 32));
                     CU(cudaMalloc(&e->d_log_seg_cnt, 4 * (size_t)pb));
                     CU(cudaMemset(e->d_log_seg_cnt, 0, 4 * (size_t)pb));
                     // a descriptor is valid by its tag (first step of its phase + 1): none is at rest

@@ -51,6 +51,8 @@ struct PersistArgs {
     // pipelined kernel: chunk lists [3][blocks][pipe_seg_cap] of {first entry, length, ring slot, phase tag}
     uint4* pipe_seg;
     uint32_t pipe_seg_cap;
+    unsigned long long n_entries;   // CSR entries (bounds of a chunk descriptor)
+    uint32_t* pipe_sync;       // pipelined kernel: [0..3] blocks whose producing side, [4..7] whose chunk warps finished phase p mod 4
     uint32_t log_seg_cap;      // pipelined kernel: block b logs spikes into [b * log_seg_cap, (b + 1) * log_seg_cap) ...
     uint32_t* log_seg_cnt;     // ... and leaves its entry count here
     uint32_t upd_warps;        // pipelined kernel: update warps of a block

@@ -73,6 +73,49 @@ __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh
     }
 }
 
+// ---- hand-over between the two sides of a phase
+// The producing side (update + input warps) of phase p needs the consuming side (chunk warps) of phase
+// p-1 finished on EVERY block - its reductions fill the ring slots phase p reads - and the chunk warps
+// of phase p need the producing side of phase p-1 finished on every block - its chunk lists. Neither
+// needs the other blocks of its OWN side, so instead of one grid barrier per phase each side counts
+// its finished blocks in global counters (block-local named barrier, fence, one atomic per block) and
+// the leader of the other side polls them. Because a block's side may be a phase or two ahead of
+// another block's, arrivals are counted per phase: phase p uses counter p mod 4 and is complete at
+// (p / 4 + 1) x blocks (nobody can be four phases ahead). Waits are bounded; a time-out (which a
+// cooperative launch rules out short of a bug) sets a sticky error bit and the launch ends.
+constexpr unsigned int kSyncSpins = 4000000u;
+
+// End of a phase for one side of a block (`n_threads` threads that use named barrier `barrier_id`):
+// everybody arrives; the side's leader publishes the block in `mine` and then waits until `other` has
+// reached `target` (all blocks' other side have finished the phase); everybody leaves. The fence after
+// the barrier is cumulative: it covers the stores and reductions of all threads that arrived.
+__device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mine, const uint32_t* other, uint32_t target,
+                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead) {
+    // barrier.sync, not bar.sync (= barrier.sync.aligned): the leader reaches the second barrier long after the
+    // other lanes of its warp
+    asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
+    if (leader) {
+        // release: cumulative over what the threads that arrived at the barrier have written (a full
+        // fence here would also hold up the other role's warps, which are in the middle of their loads)
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
+        if (wait && !dead) {
+            // plain polling loads (an acquire load per poll would invalidate the SM's L1 under the other
+            // role's feet every time), one acquire load once the count is there
+            unsigned int spins = 0;
+            while ((int32_t)(*reinterpret_cast<const volatile uint32_t*>(other) - target) < 0) {
+                if (++spins > kSyncSpins) {
+                    atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
+                    dead = true;
+                    break;
+                }
+            }
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
+        }
+    }
+    asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
+}
+
 struct DeliveryTotals {
     unsigned long long events, inputs, spikes;
 };
@@ -129,6 +172,12 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
 
 // Streams one chunk into the ring with one warp: up to kInFlight entries per lane in flight.
 __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d, uint32_t lane) {
+    // a descriptor that does not describe a piece of the CSR is not followed (it would mean a list was read
+    // before it was complete): the launch goes on and the host reports the error
+    if ((unsigned long long)d.x + d.y > a.n_entries || d.y > kChunk || d.z >= a.ring_slots) {
+        if (lane == 0) atomicOr(&a.ctl->error_flags, kErrBadChunk);
+        return;
+    }
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
     uint2 e[kInFlight];
@@ -228,6 +277,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
 
     const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
     const uint32_t kCW = kDW - a.input_warps;   // delivery warps that stream chunks; the others prepare input spikes
+    const uint32_t n_prod_threads = kUT + 32u * a.input_warps, n_cons_threads = 32u * kCW;
+    uint32_t* const cnt_prod = a.pipe_sync;        // [4] blocks whose update + input warps finished phase p (index p mod 4)
+    uint32_t* const cnt_cons = a.pipe_sync + 4;    // [4] blocks whose chunk warps finished phase p
+    bool sync_dead = false;
     const bool is_upd = threadIdx.x < kUT;
     const uint32_t dtid = threadIdx.x - kUT;
     const uint32_t n_groups = a.n_pad / kNeuronsPerThread;
@@ -285,6 +338,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     if (is_upd) {
         // ================= update warps
         Neuron4<THETA, IEXT> nr;
+        bool clamp_now = false;
         int pslot[4] = {-1, -1, -1, -1};
         if (mine) {
             nr.load(a.st, a.n_pad, i0);
@@ -309,6 +363,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
+            if (IEXT && clamp_now) {
+                if (mine) nr.iex = ld4cg(a.st.i_ext + i0);
+                clamp_now = false;
+            }
             uint32_t sl = slot;
             for (uint32_t j = 0; j < len; ++j) {
                 uint32_t mask = 0;
@@ -353,22 +411,19 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 }
                 sl = wrap_slot(sl + 1u, S);
             }
+            // done with phase p; the next one needs the chunk warps of phase p finished everywhere (ring slots final)
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
-            if (a.profile && (threadIdx.x & 31) == 0) atomicMax(&a.ctl->t_class_last[par][0], gtimer());
-            grid.sync();
+            side_handover(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
+                          threadIdx.x == 0, s + len < a.n_steps, sync_dead);
             if (timer_u) {
-                a.ctl->t_class_sum[0] += __ldcg(&a.ctl->t_class_last[par][0]) - t_mark;
-                a.ctl->t_class_sum[1] += __ldcg(&a.ctl->t_class_last[par][1]) - t_mark;
-                a.ctl->t_class_sum[2] += __ldcg(&a.ctl->t_class_last[par][2]) - t_mark;
-                a.ctl->t_class_last[par ^ 1u][0] = a.ctl->t_class_last[par ^ 1u][1] = a.ctl->t_class_last[par ^ 1u][2] = t_mark;
                 const unsigned long long t_end = gtimer();
-                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
+                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
                 acc_wait += t_end - t_work;
                 t_mark = t_end;
             }
             if (IEXT && clamp_next) {
                 while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= start + len) ++cgi;
-                if (mine) nr.iex = ld4cg(a.st.i_ext + i0);
+                clamp_now = true;   // reload i_ext once the chunk warps that applied the change are done
             }
             slot = (uint32_t)((slot + len) % S);
             s += len;
@@ -401,20 +456,26 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
             const uint32_t q = par ^ 1u;
-            if (dtid == 0) {
-                // the list of the NEXT phase was last read one phase ago
-                sh.chunks[(p + 1u) % 3u] = 0u;
-            }
             unsigned long long t_rows = 0ull;
             if (input_role) {
                 // this phase's input spikes, from the start of the phase
                 prepare_inputs(a, sh, L, tag, cc, start, slot, len, it, n_it, tot);
             } else {
+                if (dtid == 0) sh.chunks[(p + 1u) % 3u] = 0u;   // the list of the NEXT phase was last read one phase ago
                 if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
                 if (timer_d) t_rows = gtimer();
+                if (IEXT && clamp_next) {
+                    // changes effective from the next phase's first step: the update warps reload i_ext after
+                    // they have seen this side finish
+                    for (uint32_t g = cgi; g < a.ce_group_end && a.ce_group_step[g] <= start + len; ++g) {
+                        const uint32_t b = a.ce_group_ptr[g], e = a.ce_group_ptr[g + 1];
+                        for (uint32_t k = b + blockIdx.x * n_cons_threads + dtid; k < e; k += gridDim.x * n_cons_threads)
+                            atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
+                    }
+                }
             }
-            // The spike log of the previous phase (one atomic with a round trip, then stores) is kept off the
-            // chunk warps' path when there are input warps: they are done early. Otherwise chunk warp 0 has it.
+            // The spike log of the previous phase is kept off the chunk warps' path when there are input warps
+            // (they are done early). Otherwise chunk warp 0 has it.
             if (dwarp == log_warp && p > 0) {
                 const uint32_t n_rec = min(sh.count[q], kPendP);
                 if (a.log_stamp && n_rec) write_log(a, sh, lane, n_rec, q, prev_start, log_pos);
@@ -424,20 +485,18 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     tot.spikes += n_rec;
                 }
             }
-            if (IEXT && clamp_next) {
-                // changes effective from the next phase's first step: nobody reads i_ext before the barrier
-                for (uint32_t g = cgi; g < a.ce_group_end && a.ce_group_step[g] <= start + len; ++g) {
-                    const uint32_t b = a.ce_group_ptr[g], e = a.ce_group_ptr[g + 1];
-                    for (uint32_t k = b + blockIdx.x * kDT + dtid; k < e; k += gridDim.x * kDT)
-                        atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
-                }
-            }
+            // input warps belong to the producing side (their chunks go into this phase's lists); the chunk warps'
+            // next phase - and their last pass after the loop - needs the producing side of this phase finished
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
-            if (a.profile && lane == 0) atomicMax(&a.ctl->t_class_last[par][input_role ? 2 : 1], gtimer());
-            grid.sync();
+            if (input_role)
+                side_handover(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads, false,
+                              s + len < a.n_steps, sync_dead);
+            else
+                side_handover(a, cnt_cons + (p & 3u), cnt_prod + (p & 3u), (p / 4u + 1u) * gridDim.x, 1, n_cons_threads,
+                              dtid == 0, true, sync_dead);
             if (timer_d) {
                 const unsigned long long t_end = gtimer();
-                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the barrier
+                acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
                 acc_wait += t_end - t_work;
                 acc_rows += (t_rows ? t_rows : t_mark) - t_mark;
                 t_mark = t_end;
@@ -451,7 +510,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
         if (p > 0) {
-            if (!input_role) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+            if (!input_role) {
+                deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+            }
             if (dwarp == log_warp) {
                 const uint32_t q = (p & 1u) ^ 1u;
                 const uint32_t n_rec = min(sh.count[q], kPendP);
