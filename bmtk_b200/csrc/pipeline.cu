@@ -1,25 +1,28 @@
 // Pipelined persistent kernel: neuron update and spike delivery run CONCURRENTLY on every SM.
 //
-// One block of 640 threads per SM stays resident for a whole chunk of steps (cooperative launch). Its
-// first 13 warps ("update warps") own four neurons per thread, state in registers for the whole launch;
-// its last 7 warps ("delivery warps") stream CSR rows into the ring. Time is cut into phases of
-// h = floor(min_delay / 2) steps. In phase p
+// One block of 20 warps per SM stays resident for a whole chunk of steps (cooperative launch, so that
+// all blocks are co-resident). The first warps ("update warps", as many as the network needs at 128
+// neurons per warp) own four neurons per thread, state in registers for the whole launch; one or more
+// "input warps" draw the Poisson cells / pick up the replayed virtual spikes; the remaining "chunk
+// warps" stream CSR rows into the ring. Time is cut into phases of h = floor(min_delay / 2) steps. In
+// phase p
 //   * the update warps run the phase's h steps back to back (ring slot in, state update, slot
-//     cleared); a spike is cut into chunks of at most 256 CSR entries whose descriptors
-//     {first entry, length, ring slot of emission} go to the block's segment of a global list,
-//     at a position taken from a SHARED-memory counter (no global atomic on the update path);
-//   * half of the delivery warps draw the phase's Poisson cells (or pick up replayed virtual
-//     spikes) and add their chunks to the same list;
-//   * the delivery warps share the chunks listed in phase p-1 with their neighbours: chunk j of
-//     block b is delivered by warp j mod D of block b + j / D (D delivery warps), so a busy block's spikes spill over
-//     to the following SMs. A descriptor carries the tag of its phase, so a warp simply loads the
-//     few slots it is responsible for (one round trip, no counts to read first), keeps those with
-//     the right tag and streams them, up to 8 entries per lane in flight;
-// and ONE grid barrier closes the phase. Whatever is emitted in phase p is due min_delay >= 2h steps
-// later, i.e. not before phase p+2 begins, so delivering it during phase p+1 neither touches a ring
-// slot that phase reads nor arrives late. Compared with update -> barrier -> deliver -> barrier per
-// window, the two latency chains (ring slot -> update, and list -> row -> ring reduction) overlap
-// instead of adding up, and there is one barrier per h steps instead of two per 2h.
+//     cleared where it received input); a spike is cut into chunks of at most 256 CSR entries whose
+//     descriptors {first entry, length, ring slot of emission, phase tag} go to the block's segment of
+//     a list, at a position taken from a SHARED-memory counter (no global atomic on the update path);
+//   * the input warps add the chunks of the phase's input spikes to the same list;
+//   * the chunk warps deliver the list of phase p-1, sharing it with their neighbours: chunk j of
+//     block b is delivered by chunk warp j mod D of block b + j / D (D chunk warps per block), so a busy
+//     block's spikes spill over to the following SMs. The first D descriptors of a block stay in its
+//     shared memory; the neighbours' carry the tag of their phase, so a warp simply loads the few slots
+//     it is responsible for (one round trip, no counts to read first) and keeps those with the right
+//     tag; up to 8 entries per lane are in flight.
+// Whatever is emitted in phase p is due min_delay >= 2h steps later, i.e. not before phase p+2 begins,
+// so delivering it during phase p+1 neither touches a ring slot that phase reads nor arrives late.
+// Compared with update -> barrier -> deliver -> barrier per window, the two latency chains (ring slot
+// -> update, and list -> row -> ring reduction) overlap instead of adding up, and no grid barrier is
+// left: the update + input warps of phase p+1 wait for the chunk warps of phase p of all blocks, the
+// chunk warps of phase p+1 for the update + input warps of phase p of all blocks (side_handover).
 // Lists rotate over three buffers: written in phase p, read in p+1, cleared in p+2.
 //
 // Replaces NEST's update/deliver cycle inside nest.Simulate (bmtk/simulator/pointnet/pointsimulator.py:166).
