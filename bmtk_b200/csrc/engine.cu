@@ -327,6 +327,7 @@ struct bmtk_engine {
     unsigned long long* xchg_peers[kXRanks] = {};     // every rank's buffer as mapped here
     bool p2p_ready = false, p2p_by_pointer = false;
     uint32_t xchg_seq = 0;                      // windows exchanged so far
+    uint32_t xp_off = 0;                        // pipelined kernel: start of its exchange area (64-bit words)
     int32_t* d_probe_slot = nullptr;
     unsigned long long* d_ce_group_step = nullptr;
     uint32_t* d_ce_group_ptr = nullptr;
@@ -658,15 +659,15 @@ static int drain(bmtk_engine* e) {
                         "at most 4096 spikes per block and window, the pipelined kernel 2048 per block and phase): raise option "
                         "spike_capacity, or set pipeline = 0 or persistent = 0",
                         e->send_cap);
+        if (f & kErrExchangeTimeout)
+            return fail(BMTK_E_COMM, "spike exchange timed out: a rank did not publish its window within ~1 s "
+                        "(rank %d of %d); the results of this run are invalid", e->rank, e->n_ranks);
         if (f & kErrBadChunk)
             return fail(BMTK_E_CUDA, "pipelined kernel: a chunk descriptor outside the CSR was read (a list was not complete); "
                         "the results of this run are invalid (set option pipeline = 0)");
         if (f & kErrSyncTimeout)
             return fail(BMTK_E_CUDA, "pipelined kernel: a phase hand-over between update and delivery warps timed out; "
                         "the results of this run are invalid (set option pipeline = 0)");
-        if (f & kErrExchangeTimeout)
-            return fail(BMTK_E_COMM, "spike exchange timed out: a rank did not publish its window within ~1 s "
-                        "(rank %d of %d); the results of this run are invalid", e->rank, e->n_ranks);
         if (f & kErrVirtListFull)
             return fail(BMTK_E_OVERFLOW, "Poisson spike list full (capacity %u): raise option spike_capacity", e->virt_cap);
         if (f & kErrLogFull)
@@ -782,7 +783,9 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.xchg_cap = e->send_cap;
     a.seq0 = e->xchg_seq;
     for (int r = 0; r < e->n_ranks; ++r) a.peers[r] = e->xchg_peers[r];
-    if (e->pipeline && e->pipe_ok && e->n_ranks == 1) {
+    const bool pipelined = e->pipeline && e->pipe_ok && (e->n_ranks == 1 || (e->p2p_ready && !e->has_iext));
+    if (pipelined) {
+        a.xp_off = e->xp_off;
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
         a.pipe_seg = e->d_pipe_seg;
         a.pipe_seg_cap = kPipeSegCap;
@@ -809,7 +812,8 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     }
     ++e->launches;
     e->step += n;
-    e->xchg_seq += (n + e->window - 1) / e->window;
+    // windows (two-phase kernel) or phases (pipelined kernel) exchanged so far: the same on every rank
+    e->xchg_seq += pipelined ? (n + a.half - 1) / a.half : (n + e->window - 1) / e->window;
     // lists are empty at rest, whichever path runs next
     if (e->d_virt) CU(cudaMemsetAsync(e->d_virt, 0, 4, e->stream));
     if (e->d_virt2) CU(cudaMemsetAsync(e->d_virt2, 0, 4, e->stream));
@@ -1371,9 +1375,12 @@ int bmtk_engine_finalize(bmtk_engine* e) {
             CU(cudaMalloc(&e->d_plist_counts, 8));
             CU(cudaMemset(e->d_plist_counts, 0, 8));
             if (e->n_ranks > 1) {
+                // two-phase area, then the pipelined kernel's area (64-bit words each)
                 const size_t words = xchg_words((uint32_t)e->n_ranks, e->send_cap);
-                CU(cudaMalloc(&e->d_xchg, 8 * words));
-                CU(cudaMemset(e->d_xchg, 0, 8 * words));
+                const size_t pwords = xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks));
+                e->xp_off = (uint32_t)words;
+                CU(cudaMalloc(&e->d_xchg, 8 * (words + pwords)));
+                CU(cudaMemset(e->d_xchg, 0, 8 * (words + pwords)));
             }
         }
     }
@@ -1743,7 +1750,9 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
     e->h_spk_n = 0;
     e->log_base_step = e->step;
     e->h_trace.clear();
-    // descriptors left from steps after the restored one would carry tags that come again
+    // descriptors and exchange words left from steps after the restored one would carry tags that come again
+    if (e->d_xchg && e->xp_off)
+        CU(cudaMemset(e->d_xchg + e->xp_off, 0, 8 * xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks))));
     if (e->d_pipe_seg) CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap));
     // replayed inputs handed over before the load are re-indexed from the restored step
     return BMTK_OK;
@@ -1799,7 +1808,7 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;
-    else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && e->n_ranks == 1) ? 1 : 0;
+    else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && (e->n_ranks == 1 || (e->p2p_ready && !e->has_iext))) ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else if (k == "n_pad1") *out = e->n_pad1;
     else if (k == "trials") *out = e->n_trials;

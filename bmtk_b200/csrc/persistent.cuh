@@ -82,6 +82,7 @@ struct PersistArgs {
     unsigned long long* peers[kXRanks];
     uint32_t xchg_cap;
     uint32_t seq0;             // windows completed before this launch
+    uint32_t xp_off;           // pipelined kernel: where its exchange area starts in an exchange buffer (64-bit words)
 };
 
 #ifdef __CUDACC__
@@ -112,6 +113,28 @@ constexpr unsigned int kWaitSpins = 4000000u;
 #endif
 
 constexpr size_t xchg_words(uint32_t n_ranks, uint32_t cap) { return 2 * (size_t)kXRanks + 2 * (size_t)n_ranks * cap; }
+
+// Exchange area of the pipelined kernel, in 64-bit words {phase tag : 32 | payload : 32} like the
+// two-phase area, behind it in every rank's exchange buffer:
+//   cnt[4][kXRanks][kXBlocks] | ent[4][n_ranks][blocks][kXPipeSeg]
+// cnt / ent hold what block b of rank r emitted in the phase with index p mod 4 (count; entries
+// step_in_phase << kSrcBits | global id), written by the emitting rank with plain 8-byte peer stores.
+// A word is valid when its tag is the phase's (first step + 1, the same on every rank), so no fence
+// and no counter crosses the link: block b of a rank waits for the count word of block b of every
+// other rank, and for each entry's tag.
+constexpr uint32_t kXBlocks = 512;
+constexpr uint32_t kXPipeSeg = 256;   // spikes one block can send in one phase
+constexpr size_t xpipe_words(uint32_t n_ranks, uint32_t blocks) {
+    return 4 * (size_t)kXRanks * kXBlocks + 4 * (size_t)n_ranks * blocks * kXPipeSeg;
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ u64* xp_cnt(u64* xp, uint32_t k, uint32_t r, uint32_t b) {
+    return xp + ((size_t)k * kXRanks + r) * kXBlocks + b;
+}
+__device__ __forceinline__ u64* xp_ent(u64* xp, uint32_t k, uint32_t r, uint32_t b, uint32_t n_ranks, uint32_t blocks) {
+    return xp + 4 * (size_t)kXRanks * kXBlocks + (((size_t)k * n_ranks + r) * blocks + b) * kXPipeSeg;
+}
+#endif
 
 const void* persistent_kernel_ptr(bool has_theta, bool has_iext, bool resident);
 int persistent_max_blocks(int device, bool has_theta, bool has_iext, bool resident, size_t smem);

@@ -86,20 +86,30 @@ __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh
 // another block's, arrivals are counted per phase: phase p uses counter p mod 4 and is complete at
 // (p / 4 + 1) x blocks (nobody can be four phases ahead). Waits are bounded; a time-out (which a
 // cooperative launch rules out short of a bug) sets a sticky error bit and the launch ends.
-constexpr unsigned int kSyncSpins = 4000000u;
+constexpr unsigned int kSyncSpins = 32000000u;   // far longer than the bounded waits on a peer, which it must outlast
 
 // End of a phase for one side of a block (`n_threads` threads that use named barrier `barrier_id`):
 // everybody arrives; the side's leader publishes the block in `mine` and then waits until `other` has
 // reached `target` (all blocks' other side have finished the phase); everybody leaves. The fence after
 // the barrier is cumulative: it covers the stores and reductions of all threads that arrived.
+template <bool MULTI>
 __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mine, const uint32_t* other, uint32_t target,
-                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead) {
+                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead,
+                                              uint32_t xk = 0, const uint32_t* x_count = nullptr, uint32_t x_tag = 0,
+                                              bool x_publish = false) {
     // barrier.sync, not bar.sync (= barrier.sync.aligned): the leader reaches the second barrier long after the
     // other lanes of its warp
     asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
     if (leader) {
         // release: cumulative over what the threads that arrived at the barrier have written (a full
         // fence here would also hold up the other role's warps, which are in the middle of their loads)
+        if (MULTI && x_publish) {
+            // several ranks, producing side: this block's spike count of the phase goes to block b of every
+            // other rank as one tagged word (the spikes went out the same way); no fence crosses the link
+            const uint32_t n_sent = min(*reinterpret_cast<const volatile uint32_t*>(x_count), kXPipeSeg);   // final: read after the barrier
+            for (uint32_t r = 0; r < a.n_ranks; ++r)
+                if (r != a.rank) st_word(xp_cnt(a.peers[r] + a.xp_off, xk, a.rank, blockIdx.x), x_tag, n_sent);
+        }
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
         if (wait && !dead) {
             // plain polling loads (an acquire load per poll would invalidate the SM's L1 under the other
@@ -240,6 +250,57 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
     if (lane == 0) tot.events += events;
 }
 
+// Several ranks: what block b of every other rank emitted in the phase with index k mod 4 and tag `tag` is
+// delivered by block b here (chunk warp w takes entries w, w + n_cw, ...): the warp waits (bounded) for
+// the tagged count word of that block and for each entry's tag, looks up the row of the spiking neuron
+// in THIS rank's CSR (all sources have a row, the targets are local) and streams it chunk by chunk.
+__device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, uint32_t k, uint32_t tag, uint32_t prev_slot,
+                                               uint32_t w, uint32_t n_cw, uint32_t lane, DeliveryTotals& tot, bool& dead) {
+    unsigned long long events = 0ull;
+    for (uint32_t r = 0; r < a.n_ranks; ++r) {
+        if (r == a.rank) continue;
+        u64 cw = 0;
+        if (lane == 0 && !dead) {
+            const u64* p = xp_cnt(xp, k, r, blockIdx.x);
+            unsigned int spins = 0;
+            while ((uint32_t)((cw = ld_word(p)) >> 32) != tag) {
+                if (++spins > kWaitSpins) {
+                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                    dead = true;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        cw = __shfl_sync(0xffffffffu, cw, 0);
+        if ((uint32_t)(cw >> 32) != tag) continue;   // timed out (uniform over the warp)
+        const uint32_t n = min((uint32_t)cw, kXPipeSeg);
+        const u64* ent = xp_ent(xp, k, r, blockIdx.x, a.n_ranks, gridDim.x);
+        for (uint32_t i = w; i < n; i += n_cw) {
+            u64 e = 0;
+            if (lane == 0) {
+                unsigned int spins = 0;
+                while ((uint32_t)((e = ld_word(ent + i)) >> 32) != tag) {   // its store may trail the count word
+                    if (++spins > kWaitSpins) {
+                        atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            e = __shfl_sync(0xffffffffu, e, 0);
+            if ((uint32_t)(e >> 32) != tag) continue;
+            const uint32_t src = (uint32_t)e & kSrcMask;
+            const unsigned long long rb = a.rowptr[src], re = a.rowptr[src + 1];
+            const uint32_t slot0 = wrap_slot(prev_slot + ((uint32_t)e >> kSrcBits), a.ring_slots);
+            events += re - rb;
+            for (unsigned long long c = rb; c < re; c += kChunk)
+                stream_chunk(a, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
+        }
+    }
+    if (lane == 0) tot.events += events;
+}
+
 // Spike log of the phase whose list has parity q (stamps count from prev_start); one warp. Every block
 // logs into its own segment [blockIdx.x * log_seg_cap, ...) of the log arrays at a position the warp
 // carries in a register (`pos`, same on all lanes): no atomic, no round trip. The segments are laid end
@@ -259,7 +320,7 @@ __device__ __forceinline__ void write_log(const PersistArgs& a, PipeShared& sh, 
     pos = min(pos + n_rec, a.log_seg_cap);
 }
 
-template <bool THETA, bool IEXT>
+template <bool THETA, bool IEXT, bool MULTI>
 __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     cg::grid_group grid = cg::this_grid();
@@ -281,8 +342,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
     const uint32_t kCW = kDW - a.input_warps;   // delivery warps that stream chunks; the others prepare input spikes
     const uint32_t n_prod_threads = kUT + 32u * a.input_warps, n_cons_threads = 32u * kCW;
-    uint32_t* const cnt_prod = a.pipe_sync;        // [4] blocks whose update + input warps finished phase p (index p mod 4)
-    uint32_t* const cnt_cons = a.pipe_sync + 4;    // [4] blocks whose chunk warps finished phase p
+    constexpr bool multi = MULTI;   // several ranks: a separate instantiation keeps the exchange out of the one-rank kernel
+    uint32_t* const cnt_prod = a.pipe_sync;        // [4] blocks of this rank whose update + input warps finished phase p (index p mod 4)
+    uint32_t* const cnt_cons = a.pipe_sync + 4;    // [4] blocks of this rank whose chunk warps finished phase p
+    u64* const xp_self = multi ? a.peers[a.rank] + a.xp_off : nullptr;
     bool sync_dead = false;
     const bool is_upd = threadIdx.x < kUT;
     const uint32_t dtid = threadIdx.x - kUT;
@@ -405,8 +468,20 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     for (int jj = 0; jj < kNeuronsPerThread; ++jj) {
                         if (mask >> jj & 1u) {
                             const uint32_t pos = atomicAdd(&sh.count[par], 1u);
-                            if (pos < kPendP) sh.pend[par][pos] = (j << kSrcBits) | (a.lo + i0 + jj);
+                            const uint32_t ent = (j << kSrcBits) | (a.lo + i0 + jj);
+                            if (pos < kPendP) sh.pend[par][pos] = ent;
                             else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+                            if (multi) {
+                                // the other ranks deliver this spike to their own targets: plain peer stores
+                                if (pos < kXPipeSeg) {
+                                    for (uint32_t r = 0; r < a.n_ranks; ++r)
+                                        if (r != a.rank)
+                                            st_word(xp_ent(a.peers[r] + a.xp_off, (a.seq0 + p) & 3u, a.rank, blockIdx.x, a.n_ranks, gridDim.x) + pos,
+                                                    tag, ent);
+                                } else {
+                                    atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+                                }
+                            }
                             const uint2 r = sh.rows[threadIdx.x * kNeuronsPerThread + jj];
                             push_chunks(a, sh, L, tag, r.x, r.y, sl);
                         }
@@ -416,8 +491,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             }
             // done with phase p; the next one needs the chunk warps of phase p finished everywhere (ring slots final)
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
-            side_handover(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
-                          threadIdx.x == 0, s + len < a.n_steps, sync_dead);
+            side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
+                          threadIdx.x == 0, s + len < a.n_steps, sync_dead, (a.seq0 + p) & 3u, &sh.count[par], tag, multi);
             if (timer_u) {
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
@@ -447,6 +522,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         uint32_t log_pos = 0;   // entries this block has logged in this launch
         const uint32_t it = dtid - 32u * kCW, n_it = 32u * a.input_warps;   // input thread index / count
         unsigned long long prev_start = step_base;
+        uint32_t prev_slot = slot;   // ring slot of the previous phase's first step
         DeliveryTotals tot = {0ull, 0ull, 0ull};
         CachedCell cc = {make_uint4(0u, 0u, 0u, 0u), 0u, 0u};
         if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual) {
@@ -465,7 +541,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 prepare_inputs(a, sh, L, tag, cc, start, slot, len, it, n_it, tot);
             } else {
                 if (dtid == 0) sh.chunks[(p + 1u) % 3u] = 0u;   // the list of the NEXT phase was last read one phase ago
-                if (p > 0) deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                if (p > 0) {
+                    deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                    if (multi) deliver_remote(a, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
+                }
                 if (timer_d) t_rows = gtimer();
                 if (IEXT && clamp_next) {
                     // changes effective from the next phase's first step: the update warps reload i_ext after
@@ -492,10 +571,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             // next phase - and their last pass after the loop - needs the producing side of this phase finished
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
             if (input_role)
-                side_handover(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads, false,
+                side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads, false,
                               s + len < a.n_steps, sync_dead);
             else
-                side_handover(a, cnt_cons + (p & 3u), cnt_prod + (p & 3u), (p / 4u + 1u) * gridDim.x, 1, n_cons_threads,
+                side_handover<MULTI>(a, cnt_cons + (p & 3u), cnt_prod + (p & 3u), (p / 4u + 1u) * gridDim.x, 1, n_cons_threads,
                               dtid == 0, true, sync_dead);
             if (timer_d) {
                 const unsigned long long t_end = gtimer();
@@ -507,6 +586,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             if (IEXT && clamp_next)
                 while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= start + len) ++cgi;
             prev_start = start;
+            prev_slot = slot;
             slot = (uint32_t)((slot + len) % S);
             s += len;
             ++p;
@@ -515,6 +595,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         if (p > 0) {
             if (!input_role) {
                 deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                if (multi) deliver_remote(a, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
             }
             if (dwarp == log_warp) {
                 const uint32_t q = (p & 1u) ^ 1u;
@@ -539,9 +620,12 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
 #undef PIPE_PHASE_BEGIN
 }
 
-static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext) {
-    if (has_theta) return has_iext ? (const void*)pipelined_kernel<true, true> : (const void*)pipelined_kernel<true, false>;
-    return has_iext ? (const void*)pipelined_kernel<false, true> : (const void*)pipelined_kernel<false, false>;
+static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext, bool multi) {
+    if (multi)   // clamp changes are not supported with several ranks (the phase schedules would differ)
+        return has_theta ? (const void*)pipelined_kernel<true, false, true> : (const void*)pipelined_kernel<false, false, true>;
+    if (has_theta)
+        return has_iext ? (const void*)pipelined_kernel<true, true, false> : (const void*)pipelined_kernel<true, false, false>;
+    return has_iext ? (const void*)pipelined_kernel<false, true, false> : (const void*)pipelined_kernel<false, false, false>;
 }
 
 size_t pipelined_smem(int n_types) {
@@ -553,7 +637,7 @@ uint32_t pipelined_warps() { return kWarps; }
 
 int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem) {
     int per_sm = 0, sms = 0;
-    const void* f = pipelined_kernel_ptr(has_theta, has_iext);
+    const void* f = pipelined_kernel_ptr(has_theta, has_iext, false);
     if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, kBT, smem) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
@@ -562,7 +646,7 @@ int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem)
 
 cudaError_t launch_pipelined(const PersistArgs& a, bool has_theta, bool has_iext, int blocks, cudaStream_t s) {
     const size_t smem = pipelined_smem(a.n_types);
-    const void* f = pipelined_kernel_ptr(has_theta, has_iext);
+    const void* f = pipelined_kernel_ptr(has_theta, has_iext, a.n_ranks > 1);
     cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     PersistArgs copy = a;
