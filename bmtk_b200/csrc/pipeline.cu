@@ -257,22 +257,23 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
 __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, uint32_t k, uint32_t tag, uint32_t prev_slot,
                                                uint32_t w, uint32_t n_cw, uint32_t lane, DeliveryTotals& tot, bool& dead) {
     unsigned long long events = 0ull;
+    // lane r waits for rank r's count word: the waits on the different ranks overlap
+    u64 my_cw = 0;
+    if (lane < a.n_ranks && lane != a.rank && !dead) {
+        const u64* p = xp_cnt(xp, k, lane, blockIdx.x);
+        unsigned int spins = 0;
+        while ((uint32_t)((my_cw = ld_word(p)) >> 32) != tag) {
+            if (++spins > kWaitSpins) {
+                atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                dead = true;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
     for (uint32_t r = 0; r < a.n_ranks; ++r) {
         if (r == a.rank) continue;
-        u64 cw = 0;
-        if (lane == 0 && !dead) {
-            const u64* p = xp_cnt(xp, k, r, blockIdx.x);
-            unsigned int spins = 0;
-            while ((uint32_t)((cw = ld_word(p)) >> 32) != tag) {
-                if (++spins > kWaitSpins) {
-                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
-                    dead = true;
-                    break;
-                }
-                __nanosleep(100);
-            }
-        }
-        cw = __shfl_sync(0xffffffffu, cw, 0);
+        const u64 cw = __shfl_sync(0xffffffffu, my_cw, r);
         if ((uint32_t)(cw >> 32) != tag) continue;   // timed out (uniform over the warp)
         const uint32_t n = min((uint32_t)cw, kXPipeSeg);
         const u64* ent = xp_ent(xp, k, r, blockIdx.x, a.n_ranks, gridDim.x);
