@@ -318,7 +318,7 @@ def main():
         steps_w = steps_per_bench_step / nw          # steps between two grid barriers
         s1, s2 = eng.counter('phase_sync1_ns') / nw, eng.counter('phase_sync2_ns') / nw
         phases = {
-            'kernel': 'pipelined (update and delivery warps side by side, one barrier per phase)' if pipelined
+            'kernel': 'pipelined (update and delivery warps side by side, per-side hand-over each phase)' if pipelined
                       else 'two-phase (update, barrier, delivery, barrier per window)',
             'timing': 'in-kernel %globaltimer, block 0, summed in registers over one cooperative launch (= one bench step)',
             'windows': nw, 'steps_per_window': steps_w,
@@ -452,7 +452,7 @@ def main():
                                       net.n_virtual),
                        'step': '%g ms of simulated time = %d update steps' % (STEP_MS, steps_per_bench_step),
                        'partition': ('neurons in %d contiguous blocks, spike ids of every %d-step window exchanged %s'
-                                     % (world, window, 'inside the persistent kernel over peer memory (NVLink)'
+                                     % (world, window, 'inside the stepping kernel over peer memory (NVLink)'
                                         if args.exchange == 'p2p' else 'with one NCCL all-gather'))
                        if world > 1 else 'single GPU',
                        'l2': 'state + ring (~80 MB) are re-read every step; the 560 MB CSR exceeds L2',
