@@ -64,10 +64,6 @@ struct Ctl {
     unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
     unsigned long long t_rows_ns;                // pipelined kernel: of the delivery warps' busy time, streaming rows
     unsigned long long pad2[3];
-    // pipelined kernel, option "phase_timers": when the last warp of each class (update, chunk, input)
-    // finished its phase, by phase parity (device clock), and the sums block 0 makes of them
-    unsigned long long t_class_last[2][3];
-    unsigned long long t_class_sum[3];
 };
 
 // Trial batching: T independent copies ("trials") of one network share its CSR. Cell c of trial t has

@@ -335,7 +335,6 @@ struct bmtk_engine {
     size_t ce_group_next = 0;
     double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
     double phase_rows_ns = 0;
-    double phase_class_ns[3] = {0, 0, 0};   // pipelined kernel: sum over phases of the last update / chunk / input warp's finish
     double drain_wait_ns = 0, drain_sort_ns = 0;   // host clock: waiting for the chunk's kernels; sorting + copying its spike log
     uint64_t phase_windows = 0;
 
@@ -627,7 +626,6 @@ static int drain(bmtk_engine* e) {
         e->phase_sync1_ns += (double)h.t_sync1_ns;
         e->phase_sync2_ns += (double)h.t_sync2_ns;
         e->phase_rows_ns += (double)h.t_rows_ns;
-        for (int q = 0; q < 3; ++q) e->phase_class_ns[q] += (double)h.t_class_sum[q];
         CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, sizeof(Ctl) - offsetof(Ctl, t_update_ns), e->stream));
     }
     if (h.step_base != e->step)
@@ -1802,9 +1800,6 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "drain_wait_ns") *out = (uint64_t)e->drain_wait_ns;
     else if (k == "drain_sort_ns") *out = (uint64_t)e->drain_sort_ns;
     else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
-    else if (k == "phase_last_update_ns") *out = (uint64_t)e->phase_class_ns[0];
-    else if (k == "phase_last_chunk_ns") *out = (uint64_t)e->phase_class_ns[1];
-    else if (k == "phase_last_input_ns") *out = (uint64_t)e->phase_class_ns[2];
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;
