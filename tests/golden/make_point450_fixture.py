@@ -44,4 +44,4 @@ def main(ref):
 
 
 if __name__ == '__main__':
-    main(sys.argv[1] if len(sys.argv) > 1 else '/root/reference')
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get('BMTK_REFERENCE', '/root/reference'))

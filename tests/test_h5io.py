@@ -7,7 +7,8 @@ import pytest
 
 from bmtk_b200 import h5io
 
-REF = '/root/reference/examples/point_450glifs'
+REF_ROOT = os.environ.get('BMTK_REFERENCE', '/root/reference')
+REF = REF_ROOT + '/examples/point_450glifs'
 needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason='reference tree not mounted')
 
 
@@ -66,13 +67,13 @@ def test_reads_library_written_spikes_file():
 @needs_ref
 def test_reads_chunked_deflate_datasets():
     """examples/bio_1cell/output_iclamp holds gzip-compressed, chunked datasets written by h5py."""
-    p = '/root/reference/examples/bio_1cell/output_iclamp/spikes.h5'
+    p = REF_ROOT + '/examples/bio_1cell/output_iclamp/spikes.h5'
     with h5io.File(p, 'r') as h:
         pops = h['spikes'].keys()
         g = h['spikes'][pops[0]]
         ts = g['timestamps'][()]
         assert ts.ndim == 1 and len(ts) == len(g['node_ids']) and np.all(np.isfinite(ts))
-    p = '/root/reference/examples/bio_1cell/output_iclamp/membrane_potential.h5'
+    p = REF_ROOT + '/examples/bio_1cell/output_iclamp/membrane_potential.h5'
     with h5io.File(p, 'r') as h:
         pop = h['report'][h['report'].keys()[0]]
         data = pop['data']

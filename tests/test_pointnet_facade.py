@@ -14,7 +14,7 @@ from bmtk_b200.pointnet.glif_utils import convert_aibs2nest
 from bmtk_b200.pointnet.modules import IClampMod
 from sonata_fixture import write_project
 
-REF = '/root/reference'
+REF = os.environ.get('BMTK_REFERENCE', '/root/reference')
 needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason='reference tree not mounted')
 
 
