@@ -76,3 +76,21 @@ def test_pipelined_clamps_and_probes(cabi):
     assert len(a[1]) > 100 and a[3].size > 0
     _same(a, b)
     assert np.array_equal(a[0].state('i_ext').view(np.uint32), b[0].state('i_ext').view(np.uint32))
+
+
+def test_pipelined_log_overflow_is_reported_and_reserve_is_harmless(cabi):
+    """The spike log of the pipelined kernel lives in per-block segments: a log that is too small is
+    reported as an error (nothing traps), and pinning the host store ahead changes no result."""
+    from bmtk_b200._cabi import EngineError
+    net = _grid_weights(W.c2(n=4000, in_degree=100, n_virtual=100, t_stop_ms=100.0, input_weight=90.0))
+    eng = W.build_engine(net, options=dict(pipeline=1, log_capacity=2048))
+    assert eng.counter('pipelined') == 1
+    with pytest.raises(EngineError) as ei:
+        eng.run(net.n_steps)
+    assert 'spike log full' in str(ei.value)
+    a = _run(net, pipeline=1)
+    e2 = W.build_engine(net, options=dict(pipeline=1))
+    e2.set_option('spike_store_reserve', 5000000)
+    e2.run(net.n_steps)
+    st, ids = e2.fetch_spikes()
+    assert np.array_equal(st.astype(np.int64), a[1]) and np.array_equal(ids.astype(np.int64), a[2])
