@@ -19,8 +19,9 @@ delivered per wall second (whole job), with sim-ms per wall-ms beside it.
          available) on a bounded slice of the same network, rank 0, N = 1 only.
 
 With N > 1 the neurons are split into N contiguous blocks (strong scaling: the network is fixed);
-each rank owns the CSR rows of its targets and the ranks all-gather the spike ids of every
-min-delay window with NCCL.
+each rank owns the CSR rows of its targets and the ranks exchange the spike ids of every phase
+inside the stepping kernel over peer memory (NVLink; --exchange nccl: one NCCL all-gather per
+min-delay window around the per-step kernels).
 """
 import argparse
 import json

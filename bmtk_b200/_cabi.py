@@ -61,6 +61,10 @@ _SIGNATURES = {
     'bmtk_comm_unique_id': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_comm_init': (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_char_p]),
     'bmtk_engine_finalize': (C.c_int, [_P]),
+    'bmtk_engine_local_layout': (C.c_int, [_P, _P]),
+    'bmtk_engine_set_global_layout': (C.c_int, [_P, _P]),
+    'bmtk_engine_exchange_layout': (C.c_int, [_P, _P]),
+    'bmtk_exchange_layout_compare': (C.c_int, [_P, _P, C.c_int]),
     'bmtk_engine_p2p_handle': (C.c_int, [_P, _P]),
     'bmtk_engine_p2p_connect': (C.c_int, [_P, _P]),
     'bmtk_engine_p2p_buffer': (C.c_int, [_P, C.POINTER(_P)]),

@@ -326,6 +326,14 @@ struct bmtk_engine {
     unsigned long long* d_xchg = nullptr;             // this rank's exchange buffer
     unsigned long long* xchg_peers[kXRanks] = {};     // every rank's buffer as mapped here
     bool p2p_ready = false, p2p_by_pointer = false;
+    // Exchange layout agreed between the ranks. set_global_layout supplies the network-wide minimum delay,
+    // the largest block and whether any rank has clamp changes; window, spike capacity and the offsets
+    // inside an exchange buffer follow from those, so every rank computes the same numbers. The first
+    // kXDescWords words of an exchange buffer describe the layout its owner uses; p2p_connect compares.
+    bool g_layout_set = false, g_any_clamps = false;
+    uint64_t g_min_delay = 0, g_max_local = 0;
+    bool peers_pipe_ok = true;   // every rank can run the pipelined kernel
+    bool any_iext = false;       // some rank has clamp changes (the pipelined exchange has no clamp schedule)
     uint32_t xchg_seq = 0;                      // windows exchanged so far
     uint32_t xp_off = 0;                        // pipelined kernel: start of its exchange area (64-bit words)
     int32_t* d_probe_slot = nullptr;
@@ -343,6 +351,42 @@ struct bmtk_engine {
 };
 
 namespace bmtk {
+
+constexpr uint32_t kXDescWords = 16;
+constexpr unsigned long long kXDescMagic = 0x424d544b58444553ull;   // "BMTKXDES"
+
+// What a rank's exchange buffer is laid out for (see bmtk_engine_exchange_layout in the header).
+static void describe_layout(const bmtk_engine* e, uint64_t* d) {
+    std::memset(d, 0, 8 * kXDescWords);
+    d[0] = kXDescMagic;
+    d[1] = (uint64_t)e->n_ranks;
+    d[2] = e->window;
+    d[3] = e->send_cap;
+    d[4] = e->xp_off;
+    d[5] = (uint64_t)e->persist_blocks;
+    d[6] = (uint64_t)e->pipe_blocks;
+    d[7] = (e->pipeline && e->pipe_ok) ? 1 : 0;
+    d[8] = e->has_iext ? 1 : 0;
+    d[9] = e->n_global;
+    d[10] = e->n_virtual;
+    std::memcpy(&d[11], &e->dt, 8);
+    d[12] = e->max_delay;
+}
+
+// Two ranks can exchange spikes only if these agree; words 7 and 8 may differ (they are combined).
+static int compare_layout(const uint64_t* a, const uint64_t* b, int rank_b) {
+    static const char* names[kXDescWords] = {"magic", "number of ranks", "exchange window (steps)", "spike capacity",
+                                             "offset of the pipelined exchange area", "blocks of the two-phase kernel",
+                                             "blocks of the pipelined kernel", "", "", "number of neurons",
+                                             "number of virtual cells", "dt", "", "", "", ""};
+    for (uint32_t i = 0; i < kXDescWords; ++i) {
+        if (!names[i][0] || a[i] == b[i]) continue;
+        return fail(BMTK_E_INVALID, "exchange layout differs from rank %d: %s is %llu here and %llu there; give every rank "
+                    "the same network-wide values with bmtk_engine_set_global_layout before finalize", rank_b, names[i],
+                    (unsigned long long)a[i], (unsigned long long)b[i]);
+    }
+    return BMTK_OK;
+}
 
 static int set_device(bmtk_engine* e) {
     CU(cudaSetDevice(e->device));
@@ -722,6 +766,15 @@ static int drain(bmtk_engine* e) {
     return BMTK_OK;
 }
 
+// The pipelined kernel runs when this rank can (resident state, one trial, min delay >= 2 steps) and,
+// with several ranks, when every rank can and none has clamp changes: the ranks must all run the same
+// exchange protocol.
+static bool use_pipelined(const bmtk_engine* e) {
+    if (!e->pipeline || !e->pipe_ok) return false;
+    if (e->n_ranks == 1) return true;
+    return e->p2p_ready && e->peers_pipe_ok && !e->any_iext;
+}
+
 // One cooperative launch that executes `n` steps (update + delivery of every window inside it).
 static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     PersistArgs a{};
@@ -781,7 +834,7 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.xchg_cap = e->send_cap;
     a.seq0 = e->xchg_seq;
     for (int r = 0; r < e->n_ranks; ++r) a.peers[r] = e->xchg_peers[r];
-    const bool pipelined = e->pipeline && e->pipe_ok && (e->n_ranks == 1 || (e->p2p_ready && !e->has_iext));
+    const bool pipelined = use_pipelined(e);
     if (pipelined) {
         a.xp_off = e->xp_off;
         a.half = std::min<uint32_t>(e->window / 2, (uint32_t)kMaxWindow);
@@ -919,7 +972,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_virt2); cudaFree(e->d_probe_slot); cudaFree(e->d_ce_group_step); cudaFree(e->d_ce_group_ptr);
     cudaFree(e->d_plists[0]); cudaFree(e->d_plists[1]); cudaFree(e->d_plist_counts);
     for (int r = 0; r < e->n_ranks && r < (int)kXRanks; ++r)
-        if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r]);
+        if (e->xchg_peers[r] && r != e->rank && !e->p2p_by_pointer) cudaIpcCloseMemHandle(e->xchg_peers[r] - kXDescWords);
     cudaFree(e->d_xchg);
     cudaFree(e->d_pipe_seg);
     cudaFree(e->d_log_seg_cnt);
@@ -1069,7 +1122,12 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
         }
         return BMTK_OK;
     }
-    if (k == "pipeline") { e->pipeline = value != 0; return BMTK_OK; }
+    if (k == "pipeline") {
+        if (e->finalized && e->n_ranks > 1)
+            return fail(BMTK_E_INVALID, "with several ranks option 'pipeline' must be set before finalize (the ranks agree on the kernel when they connect)");
+        e->pipeline = value != 0;
+        return BMTK_OK;
+    }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
     if (k == "chunk_steps") {
@@ -1153,6 +1211,15 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     if (e->n_edges == 0) dmin = kMaxWindow;
     e->max_delay = dmax;
     e->min_delay = dmin;
+    if (e->g_layout_set) {
+        if (e->n_edges && e->g_min_delay > dmin)
+            return fail(BMTK_E_INVALID, "set_global_layout: minimum delay %llu exceeds this rank's own minimum %u",
+                        (unsigned long long)e->g_min_delay, dmin);
+        if (e->g_max_local < e->n_local)
+            return fail(BMTK_E_INVALID, "set_global_layout: largest block %llu is smaller than this rank's %llu neurons",
+                        (unsigned long long)e->g_max_local, (unsigned long long)e->n_local);
+        dmin = (uint32_t)std::min<uint64_t>(e->g_min_delay ? e->g_min_delay : dmin, kMaxWindow);
+    }
     uint32_t tb = 1;
     while ((1ull << tb) < e->n_pad1) ++tb;
     uint32_t db = 1;
@@ -1232,7 +1299,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     cudaFree(d_init);
 
     // spike lists. Automatic capacity: every local neuron may fire in 1 of 8 steps of a window.
-    const uint64_t n_cells = (uint64_t)e->n_local * e->n_trials;
+    const uint64_t n_cells = (e->g_layout_set ? e->g_max_local : (uint64_t)e->n_local) * e->n_trials;
     uint64_t cap = e->spike_cap_opt ? e->spike_cap_opt : std::max<uint64_t>(4096, n_cells * w / 8);
     cap = std::min<uint64_t>(cap, n_cells * w + 4);
     cap = (cap + 3) / 4 * 4;
@@ -1377,8 +1444,12 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 const size_t words = xchg_words((uint32_t)e->n_ranks, e->send_cap);
                 const size_t pwords = xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks));
                 e->xp_off = (uint32_t)words;
-                CU(cudaMalloc(&e->d_xchg, 8 * (words + pwords)));
-                CU(cudaMemset(e->d_xchg, 0, 8 * (words + pwords)));
+                // [layout descriptor | two-phase area | pipelined area]; kernels see the buffer from the two-phase area on
+                CU(cudaMalloc(&e->d_xchg, 8 * (kXDescWords + words + pwords)));
+                CU(cudaMemset(e->d_xchg, 0, 8 * (kXDescWords + words + pwords)));
+                uint64_t desc[kXDescWords];
+                describe_layout(e, desc);
+                CU(cudaMemcpy(e->d_xchg, desc, sizeof(desc), cudaMemcpyHostToDevice));
             }
         }
     }
@@ -1387,8 +1458,67 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                                    (uint32_t)((size_t)e->send_cap * e->n_ranks + e->virt_cap + 65536), ring_cells);
         if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "deterministic workspace: %s", cudaGetErrorString(ce));
     }
+    if (e->comm) {
+        // the ranks must agree on window and capacity before the first all-gather of spike lists: a
+        // mismatch there would hang the collective, here it is one small all-gather and a clear error
+        uint64_t desc[kXDescWords];
+        describe_layout(e, desc);
+        unsigned long long *d_mine = nullptr, *d_all = nullptr;
+        CU(cudaMalloc(&d_mine, sizeof(desc)));
+        CU(cudaMalloc(&d_all, sizeof(desc) * e->n_ranks));
+        CU(cudaMemcpy(d_mine, desc, sizeof(desc), cudaMemcpyHostToDevice));
+        const int nrc = g_nccl.AllGather(d_mine, d_all, 2 * kXDescWords, kNcclUint32, e->comm, e->stream);
+        std::vector<uint64_t> all((size_t)kXDescWords * e->n_ranks);
+        cudaError_t ce = nrc == 0 ? cudaStreamSynchronize(e->stream) : cudaSuccess;
+        if (nrc == 0 && ce == cudaSuccess) ce = cudaMemcpy(all.data(), d_all, 8 * all.size(), cudaMemcpyDeviceToHost);
+        cudaFree(d_mine);
+        cudaFree(d_all);
+        if (nrc != 0) return fail(BMTK_E_COMM, "ncclAllGather of the exchange layout failed: %s",
+                                  g_nccl.GetErrorString ? g_nccl.GetErrorString(nrc) : "?");
+        if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "exchange layout all-gather: %s", cudaGetErrorString(ce));
+        for (int r = 0; r < e->n_ranks; ++r) {
+            if (r == e->rank) continue;
+            rc = compare_layout(desc, all.data() + (size_t)kXDescWords * r, r);
+            if (rc) return rc;
+        }
+    }
     e->finalized = true;
     return BMTK_OK;
+}
+
+int bmtk_engine_local_layout(bmtk_engine* e, uint64_t* out4) {
+    if (!e || !out4) return fail(BMTK_E_INVALID, "local_layout: NULL argument");
+    uint64_t dmin = 0xffffffffull;
+    for (uint16_t d : e->e_delay) dmin = std::min<uint64_t>(dmin, d);
+    if (e->finalized) dmin = e->n_edges ? e->min_delay : 0xffffffffull;
+    out4[0] = dmin;
+    out4[1] = e->n_local;
+    out4[2] = (e->has_iext || !e->ce_step_in.empty()) ? 1 : 0;
+    out4[3] = 0;
+    return BMTK_OK;
+}
+
+int bmtk_engine_set_global_layout(bmtk_engine* e, const uint64_t* in4) {
+    if (!e || e->finalized || !in4) return fail(BMTK_E_INVALID, "set_global_layout: engine missing, already finalized, or NULL");
+    if (in4[0] < 1) return fail(BMTK_E_INVALID, "set_global_layout: the minimum delay is at least one step");
+    e->g_min_delay = in4[0];
+    e->g_max_local = in4[1];
+    e->g_any_clamps = in4[2] != 0;
+    e->g_layout_set = true;
+    return BMTK_OK;
+}
+
+int bmtk_engine_exchange_layout(bmtk_engine* e, uint64_t* out16) {
+    if (!e || !e->finalized || !out16) return fail(BMTK_E_INVALID, "exchange_layout: engine missing, not finalized, or NULL");
+    describe_layout(e, out16);
+    return BMTK_OK;
+}
+
+int bmtk_exchange_layout_compare(const uint64_t* mine16, const uint64_t* theirs16, int their_rank) {
+    if (!mine16 || !theirs16) return fail(BMTK_E_INVALID, "exchange_layout_compare: NULL argument");
+    if (mine16[0] != kXDescMagic || theirs16[0] != kXDescMagic)
+        return fail(BMTK_E_INVALID, "exchange_layout_compare: not a layout written by bmtk_engine_exchange_layout");
+    return compare_layout(mine16, theirs16, their_rank);
 }
 
 int bmtk_engine_run(bmtk_engine* e, uint64_t n_steps) {
@@ -1627,6 +1757,28 @@ std::vector<CkptArray> ckpt_arrays(bmtk_engine* e) {
 }
 }  // namespace
 
+// Reads the layout descriptor at the head of every mapped exchange buffer and compares it with this
+// rank's: a sender indexes the receiver's buffer with its OWN capacity and offsets, so a difference
+// would put peer stores outside the receiver's allocation. Also settles what the ranks must decide
+// together: the pipelined kernel only if every rank can run it and no rank has clamp changes.
+static int check_peer_layouts(bmtk_engine* e) {
+    uint64_t mine[kXDescWords], theirs[kXDescWords];
+    describe_layout(e, mine);
+    e->peers_pipe_ok = mine[7] != 0;
+    e->any_iext = mine[8] != 0 || e->g_any_clamps;
+    for (int r = 0; r < e->n_ranks; ++r) {
+        if (r == e->rank) continue;
+        CU(cudaMemcpy(theirs, e->xchg_peers[r] - kXDescWords, sizeof(theirs), cudaMemcpyDeviceToHost));
+        if (theirs[0] != kXDescMagic)
+            return fail(BMTK_E_COMM, "p2p_connect: the buffer of rank %d is not an exchange buffer of this library", r);
+        const int rc = compare_layout(mine, theirs, r);
+        if (rc) return rc;
+        e->peers_pipe_ok = e->peers_pipe_ok && theirs[7] != 0;
+        e->any_iext = e->any_iext || theirs[8] != 0;
+    }
+    return BMTK_OK;
+}
+
 int bmtk_engine_p2p_handle(bmtk_engine* e, void* handle64) {
     if (!e || !e->finalized || !handle64) return fail(BMTK_E_INVALID, "p2p_handle: engine missing, not finalized, or NULL");
     if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_handle: no exchange buffer (one rank, or cooperative launch unavailable)");
@@ -1646,7 +1798,7 @@ int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
     if (rc) return rc;
     for (int r = 0; r < e->n_ranks; ++r) {
         if (r == e->rank) {
-            e->xchg_peers[r] = e->d_xchg;
+            e->xchg_peers[r] = e->d_xchg + kXDescWords;
             continue;
         }
         cudaIpcMemHandle_t h;
@@ -1655,8 +1807,10 @@ int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
         cudaError_t ce = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
         if (ce != cudaSuccess)
             return fail(BMTK_E_COMM, "p2p_connect: cannot map the exchange buffer of rank %d: %s", r, cudaGetErrorString(ce));
-        e->xchg_peers[r] = (unsigned long long*)p;
+        e->xchg_peers[r] = (unsigned long long*)p + kXDescWords;
     }
+    rc = check_peer_layouts(e);
+    if (rc) return rc;
     e->p2p_ready = true;
     return BMTK_OK;
 }
@@ -1673,10 +1827,13 @@ int bmtk_engine_p2p_connect_pointers(bmtk_engine* e, void* const* d_buffers) {
     if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_connect_pointers: no exchange buffer");
     for (int r = 0; r < e->n_ranks; ++r) {
         if (r != e->rank && !d_buffers[r]) return fail(BMTK_E_INVALID, "p2p_connect_pointers: buffer of rank %d is NULL", r);
-        e->xchg_peers[r] = r == e->rank ? e->d_xchg : (unsigned long long*)d_buffers[r];
+        e->xchg_peers[r] = (r == e->rank ? e->d_xchg : (unsigned long long*)d_buffers[r]) + kXDescWords;
     }
-    e->p2p_ready = true;
     e->p2p_by_pointer = true;
+    int rc = set_device(e);
+    if (!rc) rc = check_peer_layouts(e);
+    if (rc) return rc;
+    e->p2p_ready = true;
     return BMTK_OK;
 }
 
@@ -1750,7 +1907,7 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
     e->h_trace.clear();
     // descriptors and exchange words left from steps after the restored one would carry tags that come again
     if (e->d_xchg && e->xp_off)
-        CU(cudaMemset(e->d_xchg + e->xp_off, 0, 8 * xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks))));
+        CU(cudaMemset(e->d_xchg + kXDescWords + e->xp_off, 0, 8 * xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks))));
     if (e->d_pipe_seg) CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap));
     // replayed inputs handed over before the load are re-indexed from the restored step
     return BMTK_OK;
@@ -1803,7 +1960,7 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;
-    else if (k == "pipelined") *out = (e->pipeline && e->pipe_ok && (e->n_ranks == 1 || (e->p2p_ready && !e->has_iext))) ? 1 : 0;
+    else if (k == "pipelined") *out = use_pipelined(e) ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else if (k == "n_pad1") *out = e->n_pad1;
     else if (k == "trials") *out = e->n_trials;

@@ -393,7 +393,12 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     bool clamp_next = false;                                                 \
     if (IEXT && cgi < a.ce_group_end) {                                      \
         const unsigned long long gs = a.ce_group_step[cgi]; /* > start */    \
-        if (gs - start <= (unsigned long long)len) {                         \
+        /* a change that takes effect on the first step AFTER this launch is  \
+           left to the next launch's prologue (applying it here as well      \
+           would add it twice)                                                \
+        */                                                                   \
+        if (gs - start < (unsigned long long)len ||                          \
+            (gs - start == (unsigned long long)len && s + len < a.n_steps)) {\
             len = (uint32_t)(gs - start);                                    \
             clamp_next = true;                                               \
         }                                                                    \

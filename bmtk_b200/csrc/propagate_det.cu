@@ -11,6 +11,7 @@
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
+#include <atomic>
 #include <cstdio>
 #include <string>
 
@@ -80,13 +81,26 @@ __global__ void det_rowlen_kernel(uint32_t n, const unsigned long long* keys, co
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const uint32_t src = (uint32_t)keys[i];
-        len[i] = (uint32_t)(rowptr[src + 1] - rowptr[src]);
+        const unsigned long long l = rowptr[src + 1] - rowptr[src];
+        len[i] = l > 0xffffffffull ? 0xffffffffu : (uint32_t)l;   // a longer row exceeds every capacity on its own
     }
 }
 
-// Publishes the event total of the window (last offset + last length).
-__global__ void det_total_kernel(uint32_t n, const uint32_t* off, const uint32_t* len, Ctl* ctl) {
-    ctl->det_events = n ? off[n - 1] + len[n - 1] : 0u;
+// Publishes the event total of the window. One block; the row lengths are summed in 64 bits and the
+// result saturates at 2^32 - 1, so a list whose rows add up to 2^32 events or more (a source may be
+// listed many times) can never look small to the capacity check that follows. While the total is
+// within a capacity below 2^32, no partial sum of the 32-bit offset scan has wrapped either.
+__global__ void det_total_kernel(uint32_t n, const uint32_t* len, Ctl* ctl) {
+    __shared__ unsigned long long s_sum[256];
+    unsigned long long t = 0ull;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) t += len[i];
+    s_sum[threadIdx.x] = t;
+    __syncthreads();
+    for (uint32_t d = blockDim.x / 2; d > 0; d >>= 1) {
+        if (threadIdx.x < d) s_sum[threadIdx.x] += s_sum[threadIdx.x + d];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) ctl->det_events = s_sum[0] > 0xffffffffull ? 0xffffffffu : (uint32_t)s_sum[0];
 }
 
 // One block per spike row: event j of the row goes to position off + j.
@@ -180,7 +194,7 @@ int propagate_det_window(const PropArgs& a, DetWorkspace& w, cudaStream_t s, uin
         DC(cudaGetLastError());
         tmp = w.cub_tmp_bytes;
         DC(cub::DeviceScan::ExclusiveSum(w.cub_tmp, tmp, w.row_len, w.row_off, (int)n_items, s));
-        det_total_kernel<<<1, 1, 0, s>>>(n_items, w.row_off, w.row_len, a.ctl);
+        det_total_kernel<<<1, 256, 0, s>>>(n_items, w.row_len, a.ctl);
         DC(cudaGetLastError());
         DC(cudaMemcpyAsync(w.h_pinned + 1, &a.ctl->det_events, 4, cudaMemcpyDeviceToHost, s));
         DC(cudaStreamSynchronize(s));
@@ -242,7 +256,9 @@ constexpr size_t kNoAllocBytes = kNaCub + kNoAllocCubBytes;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 constexpr int kNaMaxDevices = 64;
-static unsigned char* g_noalloc_addr[kNaMaxDevices] = {};  // device address of the array, per device
+// device address of the array, per device; atomic so that first calls racing from two host threads are defined
+// (both store the same value)
+static std::atomic<unsigned char*> g_noalloc_addr[kNaMaxDevices];
 
 extern thread_local std::string g_last_error;
 
@@ -289,13 +305,12 @@ int bmtk_propagate_spikes_noalloc(const uint64_t* d_rowptr, const void* d_entrie
     cudaError_t ce = cudaGetDevice(&dev);
     if (ce != cudaSuccess) return na_fail(BMTK_E_CUDA, "cudaGetDevice", ce);
     if (dev < 0 || dev >= kNaMaxDevices) return na_fail(BMTK_E_UNSUPPORTED, "device ordinal beyond 63");
-    if (!g_noalloc_addr[dev]) {
-        unsigned char* p = nullptr;
-        ce = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
-        if (ce != cudaSuccess || !p) return na_fail(BMTK_E_CUDA, "cudaGetSymbolAddress(scratch)", ce);
-        g_noalloc_addr[dev] = p;
+    unsigned char* base = g_noalloc_addr[dev].load(std::memory_order_acquire);
+    if (!base) {
+        ce = cudaGetSymbolAddress((void**)&base, g_noalloc_scratch);
+        if (ce != cudaSuccess || !base) return na_fail(BMTK_E_CUDA, "cudaGetSymbolAddress(scratch)", ce);
+        g_noalloc_addr[dev].store(base, std::memory_order_release);
     }
-    unsigned char* base = g_noalloc_addr[dev];
     cudaStream_t st = (cudaStream_t)stream;
 
     Ctl* ctl = reinterpret_cast<Ctl*>(base + kNaCtl);
@@ -351,7 +366,7 @@ int bmtk_propagate_spikes_noalloc(const uint64_t* d_rowptr, const void* d_entrie
     tmp = kNoAllocCubBytes;
     if ((ce = cub::DeviceScan::ExclusiveSum(cub_tmp, tmp, row_len, row_off, (int)n_spikes, st)) != cudaSuccess)
         return na_fail(BMTK_E_CUDA, "offset scan", ce);
-    det_total_kernel<<<1, 1, 0, st>>>(n_spikes, row_off, row_len, ctl);
+    det_total_kernel<<<1, 256, 0, st>>>(n_spikes, row_len, ctl);
     if ((ce = cudaGetLastError()) != cudaSuccess) return na_fail(BMTK_E_CUDA, "total launch", ce);
     uint32_t n_events = 0;
     if ((ce = cudaMemcpyAsync(&n_events, &ctl->det_events, 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)

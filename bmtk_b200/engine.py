@@ -169,6 +169,34 @@ class Engine(object):
         check(self._lib.bmtk_engine_comm_init(self._h, buf, int(rank), int(n_ranks),
                                               libnccl.encode() if libnccl else None))
 
+    def local_layout(self):
+        """(minimum delay in steps of this rank's edges, neurons of this rank, has clamp changes)."""
+        out = np.zeros(4, dtype=np.uint64)
+        check(self._lib.bmtk_engine_local_layout(self._h, _ptr(out)))
+        return int(out[0]), int(out[1]), bool(out[2])
+
+    def set_global_layout(self, min_delay_steps, max_n_local, any_clamps=False):
+        """Network-wide values every rank must pass identically before finalize: the exchange window,
+        the spike capacity and the offsets inside the exchange buffers follow from them."""
+        a = np.array([int(min_delay_steps), int(max_n_local), int(bool(any_clamps)), 0], dtype=np.uint64)
+        check(self._lib.bmtk_engine_set_global_layout(self._h, _ptr(a)))
+
+    def agree_layout(self):
+        """Several ranks under torch.distributed: all-reduces the three layout values and sets them."""
+        import torch
+        import torch.distributed as dist
+        d, n, c = self.local_layout()
+        dev = torch.device('cuda', self.device) if dist.get_backend() == 'nccl' else torch.device('cpu')
+        t = torch.tensor([-min(d, 2 ** 40), n, int(c)], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        self.set_global_layout(int(-t[0].item()), int(t[1].item()), bool(t[2].item()))
+
+    def exchange_layout(self):
+        """The 16-word description of this rank's exchange layout (after finalize)."""
+        out = np.zeros(16, dtype=np.uint64)
+        check(self._lib.bmtk_engine_exchange_layout(self._h, _ptr(out)))
+        return out
+
     def finalize(self):
         check(self._lib.bmtk_engine_finalize(self._h))
 

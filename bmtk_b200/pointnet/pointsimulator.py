@@ -5,7 +5,9 @@ Same surface as bmtk.simulator.pointnet.PointSimulator (bmtk/simulator/pointnet/
 recurrent edges; run() initialises the modules (virtual cells, clamps, recorders), creates the
 engine, simulates `tstop` and lets the modules write their files.
 With several ranks (torchrun: RANK / WORLD_SIZE / LOCAL_RANK) every rank owns a contiguous block of
-engine ids and the engines exchange spike ids with NCCL; spikes and traces are merged on rank 0.
+engine ids and the engines exchange the spike ids of every min-delay window, by default inside the
+stepping kernel over peer memory (NVLink), with NCCL all-gathers in deterministic mode; spikes and
+traces are merged on rank 0.
 """
 import glob
 import os
@@ -180,6 +182,7 @@ class PointSimulator(object):
             uid = [nccl_unique_id(lib) if rank == 0 else None]
             dist.broadcast_object_list(uid, 0)
             eng.comm_init(uid[0], rank, world, lib)
+            eng.agree_layout()       # exchange window, spike capacity and buffer offsets: the same on every rank
         eng.finalize()
         if world > 1 and not self._engine_options.get('deterministic', 0) and self._engine_options.get('persistent', 1):
             eng.connect_peers()      # spike exchange inside the stepping kernel over peer memory

@@ -406,6 +406,9 @@ def build_engine(net, device=0, deterministic=False, record_spikes=True, record_
         e.set_option(k, v)
     if n_ranks > 1:
         e.comm_init(nccl_uid, rank, n_ranks, libnccl)
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() == n_ranks:
+            e.agree_layout()    # window, spike capacity and buffer offsets must be the same on every rank
     e.finalize()
     if n_ranks > 1 and p2p and not deterministic:
         e.connect_peers()       # spike exchange over peer memory inside the persistent kernel

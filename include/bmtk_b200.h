@@ -163,6 +163,24 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value);
 int bmtk_comm_unique_id(void* uid128, const char* libnccl);
 int bmtk_engine_comm_init(bmtk_engine* e, const void* uid128, int rank, int n_ranks, const char* libnccl);
 
+/* Agreement of the ranks on the exchange layout (no counterpart in the reference: NEST's kernel
+ * agrees on min_delay and its MPI buffer sizes internally when nest.Simulate prepares,
+ * bmtk/simulator/pointnet/pointsimulator.py:166). A sender indexes the receiver's exchange buffer
+ * with its own window, spike capacity and offsets, and the all-gather variant passes its own count to
+ * the collective, so all ranks must derive these from the same numbers. Before finalize each rank
+ * reads local_layout -> out4 = {minimum delay of its edges in steps (2^32-1 without edges), its
+ * neurons, 1 if it has clamp events, 0}, the caller reduces (min, max, or) over the ranks by any means
+ * and hands every rank the same in4 = {network minimum delay, largest block, any clamps, 0} with
+ * set_global_layout. After finalize exchange_layout writes the 16-word description of what the rank's
+ * buffer is laid out for (the same words sit at the head of the buffer); p2p_connect and
+ * p2p_connect_pointers read every peer's words and finalize with an NCCL communicator all-gathers
+ * them, and each returns BMTK_E_INVALID naming the differing quantity before any kernel runs.
+ * exchange_layout_compare is that comparison as a host function. */
+int bmtk_engine_local_layout(bmtk_engine* e, uint64_t* out4);
+int bmtk_engine_set_global_layout(bmtk_engine* e, const uint64_t* in4);
+int bmtk_engine_exchange_layout(bmtk_engine* e, uint64_t* out16);
+int bmtk_exchange_layout_compare(const uint64_t* mine16, const uint64_t* theirs16, int their_rank);
+
 /* Spike exchange inside the stepping kernel, over peer memory (NVLink / NVSwitch) instead of one
  * NCCL all-gather per window: after finalize every rank exports the handle of its exchange buffer
  * (a 64-byte cudaIpcMemHandle_t), the caller distributes the handles, and p2p_connect maps all
@@ -234,9 +252,11 @@ int bmtk_propagate_spikes(const uint64_t* d_rowptr, const void* d_entries, uint3
  * 8.3 MB built into the library, which every GPU that loads the library holds until exit.
  * Limits per call: at most 4096 spikes and 262 144 synaptic events (sum of the listed rows'
  * lengths); a longer spike list is refused with BMTK_E_INVALID, more events with
- * BMTK_E_OVERFLOW, in both cases before the ring is touched.
+ * BMTK_E_OVERFLOW, in both cases before the ring is touched (the event total is formed in 64 bits,
+ * so repeated listings of long rows cannot wrap it into range).
  * The first call on each device looks up the array's device address (with that device current);
- * make that first call before starting any stream capture. All calls share the one array and it
+ * make that first call before starting any stream capture. `stream` must belong to the device
+ * that is current when the call is made: the scratch used is the current device's copy. All calls share the one array and it
  * keeps the previous call's contents (the entry point re-initialises what it needs), so two calls
  * whose GPU work could overlap - different streams, different host threads - race; serialise them.
  * Inputs and outputs are the caller's device memory exactly as for bmtk_propagate_spikes; the

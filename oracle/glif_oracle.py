@@ -9,6 +9,7 @@ with bit for bit.
 Only tests/, __graft_entry__.smoke() and bench.py's cpu-baseline legs may import this module.
 """
 import ctypes as C
+import hashlib
 import os
 import subprocess
 
@@ -119,12 +120,35 @@ def make_params(d):
     return p
 
 
+def _host_tag():
+    """Identifies the CPU the library was compiled for: the recipe uses -march=native, and the built file
+    travels with the tree, so a machine with another instruction set must compile its own."""
+    try:
+        with open('/proc/cpuinfo') as f:
+            for line in f:
+                if line.startswith('flags'):
+                    return hashlib.sha1(line.encode()).hexdigest()
+    except OSError:
+        pass
+    return 'unknown'
+
+
 def build(force=False):
-    """Compile oracle/glif_oracle.c with the recipe in oracle/Makefile."""
+    """Compile oracle/glif_oracle.c with the recipe in oracle/Makefile (again whenever the source is newer
+    or the library was compiled on a CPU with different features)."""
     src = os.path.join(_HERE, 'glif_oracle.c')
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    stamp = _LIB_PATH + '.host'
+    tag = _host_tag()
+    try:
+        same_host = open(stamp).read().strip() == tag
+    except OSError:
+        same_host = False
+    if (force or not same_host or not os.path.exists(_LIB_PATH)
+            or os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(src), os.path.getmtime(os.path.join(_HERE, 'Makefile')))):
         subprocess.check_call(['make', '-C', _HERE, '-B', 'libglif_oracle.so'],
                               stdout=subprocess.DEVNULL)
+        with open(stamp, 'w') as f:
+            f.write(tag)
     return _LIB_PATH
 
 
@@ -134,8 +158,7 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_LIB_PATH):
-            build()
+        build()
         _lib = C.CDLL(_LIB_PATH)
         _lib.orc_run.argtypes = [C.POINTER(RunArgs)]
         _lib.orc_run.restype = C.c_int

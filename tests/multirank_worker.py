@@ -27,18 +27,42 @@ def main():
     dist.broadcast_object_list(uid, 0)
     mode = sys.argv[2] if len(sys.argv) > 2 else 'replay'
     poisson = mode in ('poisson', 'p2p')
-    p2p = mode == 'p2p'
-    net = W.c0(t_stop_ms=300.0, poisson_online=poisson)
+    p2p = mode in ('p2p', 'uneven', 'clamp')
+    exact = mode in ('uneven', 'clamp')   # weights on a 0.25 pA grid: every fp32 sum is exact, whatever the order
+
+    def make():
+        if mode == 'uneven':
+            # blocks of 5000 and 5001 neurons, window 8: the automatic spike capacity (block * window / 8) would be 5000
+            # on one rank and 5004 on the other if each rank sized its own exchange buffer
+            net = W.c2(n=10001, in_degree=100, n_virtual=200, t_stop_ms=150.0, input_weight=90.0)
+        elif mode == 'clamp':
+            # current steps into neurons of rank 0 only: the ranks must still pick the same stepping kernel
+            net = W.c0(t_stop_ms=200.0, poisson_online=False)
+            ids = np.arange(0, 100, dtype=np.uint32)
+            net.clamp_step = np.concatenate([np.full(100, 301), np.full(100, 1501)]).astype(np.uint64)
+            net.clamp_target = np.concatenate([ids, ids])
+            net.clamp_delta = np.concatenate([np.full(100, 80.0), np.full(100, -80.0)]).astype(np.float32)
+        else:
+            net = W.c0(t_stop_ms=300.0, poisson_online=poisson)
+        if exact:
+            net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+        return net
+
+    net = make()
     n = net.n_neurons
     bounds = np.linspace(0, n, world + 1).astype(int)
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
     m = (net.trg >= lo) & (net.trg < hi)
-    part = W.c0(t_stop_ms=300.0, poisson_online=poisson)
+    part = make()
     part.lo, part.hi = lo, hi
     for k in ('src', 'trg', 'weight', 'delay_steps', 'port'):
         setattr(part, k, getattr(net, k)[m])
     eng = W.build_engine(part, device=local, deterministic=not p2p, rank=rank, n_ranks=world, nccl_uid=uid[0],
                          libnccl=libnccl, p2p=p2p, options=dict(chunk_steps=700) if p2p else None)
+    if mode == 'uneven':
+        assert eng.counter('pipelined') == 1 and eng.counter('spike_capacity') == 5004, eng.counter('spike_capacity')
+    if mode == 'clamp':
+        assert eng.counter('pipelined') == 0      # the rank without clamp targets follows the others
     eng.run(net.n_steps)
     st, ids = eng.fetch_spikes()
     tr = eng.fetch_trace()
@@ -59,10 +83,11 @@ def main():
         aprobe = np.concatenate([g[3] for g in gathered])
         ok &= bool(np.array_equal(aprobe, net.probe_ids))
         events = sum(g[4] for g in gathered)
-        if not p2p:
+        if not p2p or exact:
             ok &= bool(np.array_equal(ast, rst) and np.array_equal(aids, rids))
             ok &= bool(np.array_equal(atr.view(np.uint32), rtr.view(np.uint32)))
             ok &= events == ref.counter('events')
+            ok &= len(ast) > 300
         else:
             # atomic sums: identical spikes until fp32 summation order makes the runs part, and exact
             # integer bookkeeping: every spike of every rank was delivered exactly once on every rank

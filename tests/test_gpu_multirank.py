@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize('mode', ['replay', 'poisson', 'p2p'])
+@pytest.mark.parametrize('mode', ['replay', 'poisson', 'p2p', 'uneven', 'clamp'])
 def test_two_ranks_equal_one(cabi, tmp_path, mode):
     import torch
     if torch.cuda.device_count() < 2:
@@ -39,7 +39,7 @@ def test_pointnet_surface_with_two_ranks(cabi, tmp_path):
     from bmtk_b200 import h5io, pointnet, workloads as W
     from bmtk_b200.pointnet.reports import read_membrane_report
     sys.path.insert(0, os.path.join(ROOT, 'tests'))
-    from sonata_fixture import write_project
+    from bmtk_b200.sonata_writer import write_project
     net = W.c0(t_stop_ms=200.0)
     out = {}
     for tag, nproc in (('one', 1), ('two', 2)):

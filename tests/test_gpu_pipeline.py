@@ -76,6 +76,12 @@ def test_pipelined_clamps_and_probes(cabi):
     assert len(a[1]) > 100 and a[3].size > 0
     _same(a, b)
     assert np.array_equal(a[0].state('i_ext').view(np.uint32), b[0].state('i_ext').view(np.uint32))
+    # launches that end exactly on the step a current changes (2001 = round(100 ms / dt) + 1): the change
+    # must be applied once, by the launch that runs that step
+    for kw in (dict(chunk_steps=2001), dict(chunk_steps=4096, pieces=[2001, 1199]), dict(chunk_steps=667)):
+        c = _run(net, pipeline=1, **kw)
+        _same(c, b)
+        assert np.array_equal(c[0].state('i_ext').view(np.uint32), b[0].state('i_ext').view(np.uint32)), kw
 
 
 def test_pipelined_log_overflow_is_reported_and_reserve_is_harmless(cabi):

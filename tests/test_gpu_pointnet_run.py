@@ -8,7 +8,7 @@ import pytest
 from bmtk_b200 import h5io, pointnet, workloads as W
 from bmtk_b200.pointnet.reports import read_membrane_report
 from netutil import oracle_from_network
-from sonata_fixture import write_project
+from bmtk_b200.sonata_writer import write_project
 
 pytestmark = pytest.mark.gpu
 

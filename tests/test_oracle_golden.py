@@ -49,7 +49,7 @@ def test_known_answer_spikes(oracle, idx):
         assert abs(t[0] - exp[0]) < 0.005
 
 
-def test_converted_parameters_match_survey_values():
+def test_converted_parameters_match_hand_computed_values():
     """Values the reference converter (glif_utils.py:259-418) yields for the fixtures."""
     g = _known_answers()
     by = {c['model_template']: c['nest_params'] for c in g['cases']}

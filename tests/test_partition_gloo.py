@@ -59,3 +59,68 @@ def test_two_gloo_ranks_generate_the_same_network():
         p.join(timeout=60)
     assert ok
     assert all(p.exitcode == 0 for p in procs)
+
+
+def _layout_worker(rank, world, port, q):
+    """Each rank describes the exchange layout it would use (window, spike capacity, offsets follow from
+    the minimum delay and the block size it knows), the ranks gather the descriptions over gloo and
+    compare them with the library's own comparison: local values disagree, network-wide values agree."""
+    sys.path.insert(0, ROOT)
+    import ctypes as C
+    from bmtk_b200 import _cabi
+    lib = _cabi.load()
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    n = 100001
+    bounds = np.linspace(0, n, world + 1).astype(int)
+    n_local = int(bounds[rank + 1] - bounds[rank])
+    min_delay = 8 if rank == 0 else 9           # rank 1 happens to hold no 8-step edge
+
+    def describe(window, block):
+        # the engine's rule: capacity = max(4096, block * window / 8) rounded up to 4; 2*16 + 2*ranks*cap words before the
+        # pipelined area
+        cap = (max(4096, block * window // 8) + 3) // 4 * 4
+        d = np.zeros(16, dtype=np.uint64)
+        d[0] = 0x424d544b58444553
+        d[1:7] = [world, window, cap, 2 * 16 + 2 * world * cap, 148, 148]
+        d[9], d[10] = n, 100
+        return d
+
+    import torch
+    out = {}
+    for tag, (w, blk) in (('local', (min_delay, n_local)), ('global', (None, None))):
+        if tag == 'global':
+            t = torch.tensor([-min_delay, n_local], dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            w, blk = int(-t[0]), int(t[1])
+        mine = describe(w, blk)
+        all_d = [None] * world
+        dist.all_gather_object(all_d, mine)
+        other = all_d[1 - rank]
+        rc = lib.bmtk_exchange_layout_compare(mine.ctypes.data_as(C.c_void_p), other.ctypes.data_as(C.c_void_p), 1 - rank)
+        out[tag] = (rc, lib.bmtk_last_error().decode() if rc else '')
+    res = [None] * world
+    dist.gather_object(out, res if rank == 0 else None, 0)
+    if rank == 0:
+        q.put(res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_exchange_layouts_are_refused():
+    from bmtk_b200 import _cabi
+    ctx = mp.get_context('spawn')
+    q = ctx.Queue()
+    port = 29100 + (os.getpid() % 400)
+    procs = [ctx.Process(target=_layout_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+    assert all(p.exitcode == 0 for p in procs)
+    for r in res:
+        assert r['local'][0] == _cabi.E_INVALID and 'set_global_layout' in r['local'][1]
+        assert 'exchange window' in r['local'][1]      # the first differing quantity is named
+        assert r['global'][0] == _cabi.OK

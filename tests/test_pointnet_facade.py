@@ -12,7 +12,7 @@ from bmtk_b200 import pointnet, workloads as W
 from bmtk_b200.pointnet import sim_settings
 from bmtk_b200.pointnet.glif_utils import convert_aibs2nest
 from bmtk_b200.pointnet.modules import IClampMod
-from sonata_fixture import write_project
+from bmtk_b200.sonata_writer import write_project
 
 REF = os.environ.get('BMTK_REFERENCE', '/root/reference')
 needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason='reference tree not mounted')

@@ -58,3 +58,27 @@ def test_noalloc_refuses_what_does_not_fit(cabi, oracle):
     assert call(cabi, 'bmtk_propagate_spikes_noalloc', case, t, src, np.zeros(20, dtype=np.int64), ring, None) == 0
     exp = reference_ring(case, np.zeros(ring.numel()), src, np.zeros(20, dtype=np.int64))
     assert np.allclose(ring.cpu().numpy().astype(np.float64), exp, rtol=1e-4, atol=1e-3)
+
+
+def test_noalloc_event_total_cannot_wrap(cabi):
+    """4096 listings of one row of 1 048 640 entries add up to 2^32 + 262 144 events: formed in 32 bits
+    that total would read 262 144 and pass the capacity check. It must be refused, in both deterministic
+    entry points, with the ring untouched."""
+    import torch
+    from bmtk_b200 import _cabi
+    n_row = 1048640
+    n_pad, tb, S = 64, 6, 4
+    entries = np.empty((n_row, 2), dtype=np.uint32)
+    entries[:, 0] = (1 << (tb + 2)) | (np.arange(n_row, dtype=np.uint32) % 60)     # delay 1, port 0
+    entries[:, 1] = np.float32(1.0).view(np.uint32)
+    case = dict(rowptr=np.array([0, n_row], dtype=np.uint64), entries=entries, tb=tb, n_pad=n_pad, ring_slots=S)
+    t = to_device(case)
+    ring = torch.zeros(S * 4 * n_pad, dtype=torch.float32, device='cuda')
+    src = np.zeros(4096, dtype=np.int64)
+    assert (4096 * n_row) % (1 << 32) == 262144
+    rc = call(cabi, 'bmtk_propagate_spikes_noalloc', case, t, src, src, ring, None)
+    assert rc == _cabi.E_OVERFLOW, cabi.bmtk_last_error()
+    assert float(ring.abs().sum()) == 0.0
+    rc = call(cabi, 'bmtk_propagate_spikes', case, t, src, src, ring, 1, None)
+    assert rc == _cabi.E_OVERFLOW, cabi.bmtk_last_error()
+    assert float(ring.abs().sum()) == 0.0
