@@ -58,9 +58,11 @@ def parse_args():
     ap.add_argument('--no-cpu', action='store_true')
     ap.add_argument('--cpu-slice-ms', type=float, default=250.0)
     ap.add_argument('--step-ms', type=float, default=1000.0, help='simulated ms per bench step (1000 = the configuration)')
-    ap.add_argument('--workload', default='c3', choices=['c3', 'c4'],
+    ap.add_argument('--workload', default='c3', choices=['c0', 'c1', 'c2', 'c3', 'c4'],
                     help='c3: the V1-scale network (the headline line). c4: trial sweep, the 50 000-neuron E/I network as 64 '
-                         'independent trials over one CSR, trials sharded over the ranks, one step = 500 ms')
+                         'independent trials over one CSR, trials sharded over the ranks, one step = 500 ms. c0 / c1 / c2: the '
+                         'small network (3000 ms), the current-clamp sweep (1500 ms) and the mid-scale E/I network (1000 ms; '
+                         'neurons in contiguous blocks with several ranks), one step = the whole configured run')
     ap.add_argument('--trials', type=int, default=64)
     ap.add_argument('--engine-option', action='append', default=[], metavar='KEY=VALUE',
                     help='extra engine option (bmtk_engine_set_option), e.g. pipeline=0 for the two-phase persistent kernel')
@@ -167,6 +169,54 @@ def run_cpu(net, slice_ms, threads, n_slices=1):
     return sim, n_steps, t_setup
 
 
+def parity_check(full_net, st, ids, n_steps, threads, stream=0):
+    """Checker, outside every timed region: the fp64 oracle runs the same network from rest on the same
+    Philox input for `n_steps`, and the engine's recorded spikes of those steps are compared with it:
+    first differing step, every spike of the first 25 ms within one step, share of the first 100 ms's
+    spikes in trains that differ by more, per-type firing rates over the whole span."""
+    from oracle import compare as K
+    from oracle import glif_oracle as O
+    O.build()
+    t0 = time.time()
+    sim = O.OracleSim(full_net.types, full_net.type_index, full_net.dt, n_virtual=full_net.n_virtual, src=full_net.src,
+                      trg=full_net.trg, weight=full_net.weight, delay_steps=full_net.delay_steps, port=full_net.port,
+                      n_threads=threads, canonical_csr=False)
+    steps, srcs = O.poisson_spikes(full_net.poisson_rate_hz, full_net.dt, full_net.poisson_seed, 0, n_steps, stream=stream)
+    sim.set_input_spikes(steps, srcs)
+    r = sim.run(n_steps, spike_cap=max(1 << 20, full_net.n_neurons * 16))
+    ost, oid = r['spike_step'], r['spike_id'].astype(np.int64)
+    st, ids = np.asarray(st, dtype=np.int64), np.asarray(ids, dtype=np.int64)
+    o = np.lexsort((ids, st))
+    st, ids = st[o], ids[o]
+    s25, s100 = int(round(25.0 / full_net.dt)), int(round(100.0 / full_net.dt))
+    strict = K.within_one_step(st, ids, ost, oid, s25, full_net.n_neurons)
+    wide = K.within_one_step(st, ids, ost, oid, s100, full_net.n_neurons)
+    ra = K.rate_agreement(full_net.type_index, len(full_net.types), ids, oid, n_steps * full_net.dt)
+    return {
+        'against': 'fp64 CPU oracle (%d threads), same network and Philox input, from rest, %g ms' % (threads, n_steps * full_net.dt),
+        'spikes_gpu': int(len(st)), 'spikes_oracle': int(len(ost)),
+        'first_divergence_step': K.first_divergence(st, ids, ost, oid),
+        'first_25ms_within_one_step': strict['ok'], 'first_25ms_spikes': strict['n_b'],
+        'first_100ms': {'spikes': wide['n_b'], 'neurons_with_other_count': wide['neurons_with_other_count'],
+                        'spikes_beyond_one_step': wide['spikes_beyond_one_step'],
+                        'share_beyond': (wide['neurons_with_other_count'] + wide['spikes_beyond_one_step']) / max(1, wide['n_b'])},
+        'max_type_rate_rel_err': ra['max_rel_err'], 'rates_within_2pct': ra['within_rel_only'],
+        'ok': bool(strict['ok'] and ra['within_rel_only']),
+        'oracle_wall_s': time.time() - t0,
+    }
+
+
+def gather_spikes(st, ids, world, rank, dist):
+    """All ranks' recorded spikes on rank 0 (None elsewhere)."""
+    if world == 1:
+        return st, ids
+    parts = [None] * world
+    dist.all_gather_object(parts, (np.asarray(st), np.asarray(ids)))
+    if rank != 0:
+        return None, None
+    return np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts])
+
+
 def reference_arm(args):
     """Times the CPU implementation of the path on the host cores. The reference's own engine is
     NEST (third-party C++, not in the reference tree, not installed), so this is the repo's fp64
@@ -260,6 +310,11 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
+    if args.workload in ('c0', 'c1', 'c2'):
+        small_config(args, torch, dist, W, world, rank, local_rank, dev, barrier, reduce, json_fd, fresh_uid, libnccl)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     n_total = int(round(230924 * args.scale))
     bounds = np.linspace(0, n_total, world + 1).astype(np.int64)
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
@@ -275,9 +330,13 @@ def main():
                          libnccl=libnccl, p2p=args.exchange == 'p2p')
     t_build = time.time() - t0
     n_warm = 0
+    first_spikes = None
     for _ in range(args.warmup):
         eng.run(steps_per_bench_step)
-        n_warm = max(n_warm, len(eng.fetch_spikes()[0]))
+        sp = eng.fetch_spikes()
+        if first_spikes is None:
+            first_spikes = (sp[0].copy(), sp[1].copy())     # the first step starts from rest: what the parity check compares
+        n_warm = max(n_warm, len(sp[0]))
     # the timed launches leave their spikes in the host store: pin it before the clock starts
     eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
     torch.cuda.synchronize()
@@ -428,6 +487,15 @@ def main():
         eng.close()
         net.poisson_rate_hz = rates.astype(np.float32)
 
+    # ---------------- parity of the first bench step (from rest) with the oracle, every N, rank 0
+    parity = None
+    if not args.no_cpu and first_spikes is not None:
+        g_st, g_ids = gather_spikes(first_spikes[0], first_spikes[1], world, rank, dist)
+        if rank == 0:
+            full = net if world == 1 else make_network(args.scale)
+            parity = parity_check(full, g_st, g_ids, steps_per_bench_step, os.cpu_count() or 1)
+            del full
+
     # ---------------- CPU baseline (rank 0, N = 1 only)
     cpu = None
     if world == 1 and not args.no_cpu:
@@ -459,7 +527,7 @@ def main():
                        'l2': 'state + ring (~80 MB) are re-read every step; the 560 MB CSR exceeds L2',
                        'mean_rate_hz': spikes / n_total / (STEP_MS * 1e-3 * args.steps)},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline, 'cpu_baseline': cpu,
-            'wall_ms_per_step': wall_ms / args.steps, 'setup_s': {'generate': t_gen, 'build_engine': t_build},
+            'parity': parity, 'wall_ms_per_step': wall_ms / args.steps, 'setup_s': {'generate': t_gen, 'build_engine': t_build},
         }
         os.write(json_fd, (json.dumps(line) + '\n').encode())
     else:
@@ -483,9 +551,15 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
                          options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000, **extra_options(args)))
     MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
     n_warm = 0
+    first_trial = None
     for _ in range(args.warmup):
         eng.run(n_steps)
-        n_warm = max(n_warm, len(eng.fetch_spikes()[0]))
+        sp = eng.fetch_spikes()
+        if first_trial is None and rank == 0:
+            n_pad1 = eng.counter('n_pad1')
+            m = sp[1] < n_pad1                  # local trial 0 of rank 0 = Philox stream 0, from rest
+            first_trial = (sp[0][m].copy(), sp[1][m].copy())
+        n_warm = max(n_warm, len(sp[0]))
     eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
     torch.cuda.synchronize()
     barrier()
@@ -521,6 +595,10 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
     eng.close()
     peak, peak_kind = peaks()
     alg_bytes = BYTES_PER_NEURON_STEP * n_pad * world * n_steps * args.steps + BYTES_PER_EVENT * events
+    parity = None
+    if rank == 0 and not args.no_cpu and first_trial is not None:
+        parity = parity_check(net, first_trial[0], first_trial[1], n_steps, os.cpu_count() or 1, stream=0)
+        parity['trial'] = 'trial 0 of %d (Philox stream 0)' % T
     if rank == 0:
         line = {
             'metric': 'synaptic_events_per_sec', 'value': events / (dev_ms * 1e-3), 'unit': 'events/s', 'n_gpus': world,
@@ -542,11 +620,123 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
                          'achieved': alg_bytes / world / (dev_ms * 1e6), 'peak': peak, 'unit': 'GB/s',
                          'frac': alg_bytes / world / (dev_ms * 1e6) / peak, 'traffic': None, 'peak_kind': peak_kind,
                          'note': 'algorithmic bytes per GPU = 128 B per neuron-step + 16 B per event, over the whole timed region'},
-            'cpu_baseline': None,
+            'cpu_baseline': None, 'parity': parity,
         }
         os.write(json_fd, (json.dumps(line) + '\n').encode())
     else:
         reduce(d2h, SUM)
+
+
+def small_config(args, torch, dist, W, world, rank, local_rank, dev, barrier, reduce, json_fd, fresh_uid, libnccl):
+    """Workloads c0, c1, c2 at their configured size: one bench step = one whole run from rest (a fresh state
+    is loaded from a checkpoint before every step, outside the timed region), so every step does the same
+    work. CPU baseline = the oracle's full run of the same configuration."""
+    import tempfile as _tf
+    name = args.workload
+    make = {'c0': lambda **kw: W.c0(poisson_online=True), 'c1': lambda **kw: W.c1(), 'c2': lambda **kw: W.c2(**kw)}[name]
+    full = make()
+    n_total = full.n_neurons
+    if world > 1 and name != 'c2':
+        raise SystemExit('%s runs on one GPU (its windows are too small to be worth an exchange); use c2, c3 or c4 with --gpus' % name)
+    bounds = np.linspace(0, n_total, world + 1).astype(np.int64)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    net = full if world == 1 else make(lo=lo, hi=hi)
+    n_steps = net.n_steps
+    MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
+    eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
+                         options=dict(chunk_steps=n_steps, **extra_options(args)), rank=rank, n_ranks=world,
+                         nccl_uid=fresh_uid(), libnccl=libnccl, p2p=args.exchange == 'p2p')
+    ck = os.path.join(_tf.mkdtemp(), 'rest_%d.ck' % rank)
+    eng.save_state(ck)
+    first = None
+    for _ in range(max(1, args.warmup)):
+        eng.load_state(ck)
+        eng.run(n_steps)
+        sp = eng.fetch_spikes()
+        if first is None:
+            first = (sp[0].copy(), sp[1].copy())
+    eng.set_option('spike_store_reserve', int(len(first[0]) * 1.25 + 1e5))
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    dev_ms, wall_ms, events, spikes, launches, d2h = 0.0, 0.0, 0, 0, 0, 0
+    for _ in range(args.steps):
+        eng.load_state(ck)
+        torch.cuda.synchronize()
+        barrier()
+        ev0, sp0, l0 = eng.counter('events'), eng.counter('spikes'), eng.counter('launches')
+        eng.mark(0)
+        t0 = time.time()
+        eng.run(n_steps)
+        eng.mark(1)
+        dev_ms += reduce(eng.elapsed_ms(0, 1), MAX)
+        st, _ids = eng.fetch_spikes()               # end to end: the run plus its spike list on the host
+        wall_ms += reduce((time.time() - t0) * 1e3, MAX)
+        d2h += 8 * len(st)
+        events += eng.counter('events') - ev0
+        spikes += eng.counter('spikes') - sp0
+        launches += eng.counter('launches') - l0
+    clocks = sampler.stop() if sampler else None
+    events, spikes, launches = reduce(events, SUM), reduce(spikes, SUM), reduce(launches, SUM)
+    n_pad, pipelined, window = eng.counter('n_pad'), bool(eng.counter('pipelined')), eng.counter('window')
+    eng.close()
+    os.unlink(ck)
+    peak, peak_kind = peaks()
+    g_st, g_ids = gather_spikes(first[0], first[1], world, rank, dist)
+    if rank != 0:
+        return
+    neuron_steps = float(n_total) * n_steps * args.steps
+    # c1 has no synapses: its unit of work is the neuron-step
+    metric, unit, value = ('synaptic_events_per_sec', 'events/s', events / (dev_ms * 1e-3)) if name != 'c1' else \
+                          ('neuron_steps_per_sec', 'neuron-steps/s', neuron_steps / (dev_ms * 1e-3))
+    e2e_value = (events if name != 'c1' else neuron_steps) / (wall_ms * 1e-3)
+    alg = BYTES_PER_NEURON_STEP * n_pad * world * n_steps * args.steps + BYTES_PER_EVENT * events
+    cpu = parity = None
+    if not args.no_cpu:
+        from oracle import glif_oracle as O
+        threads = os.cpu_count() or 1
+        sim = O.OracleSim(full.types, full.type_index, full.dt, n_virtual=full.n_virtual, src=full.src, trg=full.trg,
+                          weight=full.weight, delay_steps=full.delay_steps, port=full.port, n_threads=threads, canonical_csr=False)
+        if full.poisson_rate_hz is not None:
+            sim.set_input_spikes(*O.poisson_spikes(full.poisson_rate_hz, full.dt, full.poisson_seed, 0, n_steps))
+        if len(full.clamp_step):
+            sim.set_clamp_events(full.clamp_step, full.clamp_target, full.clamp_delta.astype(np.float64))
+        t0 = time.time()
+        r = sim.run(n_steps, spike_cap=max(1 << 20, n_total * 400))
+        t_cpu = time.time() - t0
+        cpu = {'value': (r['n_events'] if name != 'c1' else float(n_total) * n_steps) / t_cpu, 'unit': unit, 'cores': threads,
+               'kind': 'port', 'sim_ms_per_wall_ms': n_steps * full.dt / (t_cpu * 1e3),
+               'sample': 'the whole configured run (%g ms, %d spikes, %.2f s), fp64 oracle, OpenMP' % (n_steps * full.dt, r['n_spikes'], t_cpu)}
+        from oracle import compare as K
+        o = np.lexsort((np.asarray(g_ids, dtype=np.int64), np.asarray(g_st, dtype=np.int64)))
+        gst, gid = np.asarray(g_st, dtype=np.int64)[o], np.asarray(g_ids, dtype=np.int64)[o]
+        ost, oid = r['spike_step'], r['spike_id'].astype(np.int64)
+        s100 = int(round((200.0 if name == 'c1' else 100.0) / full.dt))    # c1: the first 100 ms of the current step
+        w1 = K.within_one_step(gst, gid, ost, oid, s100, n_total)
+        ra = K.rate_agreement(full.type_index, len(full.types), gid, oid, n_steps * full.dt)
+        parity = {'against': 'fp64 CPU oracle, whole run', 'spikes_gpu': int(len(gst)), 'spikes_oracle': int(len(ost)),
+                  'first_divergence_step': K.first_divergence(gst, gid, ost, oid),
+                  'first_100ms': w1, 'max_type_rate_rel_err': ra['max_rel_err'], 'rates_within_2pct': ra['within_rel_only']}
+    line = {
+        'metric': metric, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': dev_ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
+        'data': 'synthetic', 'sim_ms_per_wall_ms': n_steps * full.dt * args.steps / dev_ms,
+        'config': {'workload': '%s: %d neurons, %d synapses, %d virtual cells, dt %g ms' % (name, n_total, full.n_edges if world == 1 else -1, full.n_virtual, full.dt),
+                   'step': 'the whole configured run from rest: %g ms = %d update steps' % (n_steps * full.dt, n_steps),
+                   'partition': 'single GPU' if world == 1 else 'neurons in %d contiguous blocks, exchange inside the stepping kernel' % world,
+                   'l2': 'the working set fits L2; every step starts from a reloaded state', 'window_steps': window,
+                   'kernel': 'pipelined' if pipelined else 'two-phase persistent',
+                   'mean_rate_hz': spikes / n_total / (n_steps * full.dt * 1e-3 * args.steps)},
+        'clocks': clocks,
+        'e2e': {'value': e2e_value, 'unit': unit, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': int(d2h / args.steps),
+                'timing': 'wall clock around run + fetch_spikes; inputs are device-generated (Poisson cells / clamp table)'},
+        'gpu_launches': int(launches),
+        'roofline': {'kernel': 'pipelined_kernel' if pipelined else 'persistent_kernel', 'bound': 'hbm',
+                     'achieved': alg / world / (dev_ms * 1e6), 'peak': peak, 'unit': 'GB/s', 'frac': alg / world / (dev_ms * 1e6) / peak,
+                     'traffic': None, 'peak_kind': peak_kind,
+                     'note': 'algorithmic bytes per GPU = 128 B per neuron-step + 16 B per event over the timed launches; at this '
+                             'size the launch is bound by the per-phase hand-over, not by HBM'},
+        'cpu_baseline': cpu, 'parity': parity,
+    }
+    os.write(json_fd, (json.dumps(line, default=lambda x: x.tolist() if hasattr(x, 'tolist') else str(x)) + '\n').encode())
 
 
 def reduce_edges(net, world, dist, dev):

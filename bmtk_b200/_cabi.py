@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 MAX_PORTS = 4
-MODEL_GLIF_PSC, MODEL_IAF_PSC_ALPHA = 0, 1
+MODEL_GLIF_PSC, MODEL_IAF_PSC_ALPHA, MODEL_IAF_PSC_DELTA = 0, 1, 2
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'lib', 'libbmtk_b200.so')
 
 OK, E_INVALID, E_CUDA, E_OVERFLOW, E_UNSUPPORTED, E_COMM, E_DELAY = 0, -1, -2, -3, -4, -5, -6

@@ -35,7 +35,7 @@ struct __align__(16) TypeConsts {
     float asc_decay[2], asc_coeff[2];
     float asc_refr[2], asc_amps[2];
     float P33, P30, th_inf, i_e;
-    float v_reset, E_L, inv_G, pad_f;
+    float v_reset, E_L, inv_G, delta_gain;   // delta_gain: 1 for iaf_psc_delta (ring input is a voltage jump), else 0
     float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction;
     float reset_add, phi, abpara, theta_voltage_decay;
     int32_t n_ref;

@@ -60,7 +60,9 @@ static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& 
     const double tau = p.C_m / p.g;
     c.P33 = (float)std::exp(-h / tau);
     c.P30 = (float)(-std::expm1(-h / tau) / p.g);
-    for (int k = 0; k < p.n_ports; ++k) {
+    const bool delta = p.model == BMTK_MODEL_IAF_PSC_DELTA;
+    c.delta_gain = delta ? 1.f : 0.f;
+    for (int k = 0; k < (delta ? 0 : p.n_ports); ++k) {
         const double ts = p.tau_syn[k];
         if (!(ts > 0)) return fail(BMTK_E_INVALID, "tau_syn must be positive");
         const double a = 1.0 / ts, b = 1.0 / tau, d = b - a, x = d * h;
@@ -104,9 +106,9 @@ static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& 
     c.n_ref = n;
     c.flags = (p.spike_dependent_threshold ? 1 : 0) | (p.adapting_threshold ? 2 : 0);
     c.i_e = (float)p.I_e;
-    if (p.model == BMTK_MODEL_IAF_PSC_ALPHA) {
+    if (p.model == BMTK_MODEL_IAF_PSC_ALPHA || p.model == BMTK_MODEL_IAF_PSC_DELTA) {
         if (p.spike_dependent_threshold || p.adapting_threshold || p.after_spike_currents)
-            return fail(BMTK_E_INVALID, "iaf_psc_alpha has no threshold dynamics or after-spike currents");
+            return fail(BMTK_E_INVALID, "iaf_psc_alpha / iaf_psc_delta have no threshold dynamics or after-spike currents");
         c.flags |= 4 | 8;
         c.n_ref = (int)std::llround(p.t_ref / h);
         if (c.n_ref < 1) c.n_ref = 1;  // a spike always costs the step it happens in

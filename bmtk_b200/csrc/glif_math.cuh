@@ -83,6 +83,8 @@ struct Neuron4 {
             float u_int = v_old * c.P33 + drive * c.P30;
 #pragma unroll
             for (int p = 0; p < kPorts; ++p) u_int += c.P31[p] * y1[p].v[j] + c.P32[p] * y2[p].v[j];
+            // iaf_psc_delta: what arrives in this step is a jump of V (its ports have P31 = P32 = psc_init = 0)
+            u_int += c.delta_gain * ((in[0].v[j] + in[1].v[j]) + (in[2].v[j] + in[3].v[j]));
             float th = c.th_inf;
             float ths_int = ths.v[j], thv_int = thv.v[j];
             if (THETA) {

@@ -40,6 +40,29 @@ def iaf_psc_alpha_params(d):
     return p
 
 
+# NEST's iaf_psc_delta defaults
+IAF_PSC_DELTA_DEFAULTS = dict(V_m=-70.0, E_L=-70.0, C_m=250.0, tau_m=10.0, t_ref=2.0, V_th=-55.0, V_reset=-70.0,
+                              I_e=0.0, V_min=None, refractory_input=False)
+
+
+def iaf_psc_delta_params(d):
+    """NEST iaf_psc_delta parameter dict -> GlifParams with model = iaf_psc_delta: g = C_m/tau_m, a
+    synaptic weight is a jump of V_m in mV, every receptor port adds to the same jump."""
+    unknown = set(d) - set(IAF_PSC_DELTA_DEFAULTS)
+    if unknown:
+        raise ValueError('unknown iaf_psc_delta parameter(s): %s' % ', '.join(sorted(unknown)))
+    q = dict(IAF_PSC_DELTA_DEFAULTS)
+    q.update(d)
+    if q['V_min'] is not None and np.isfinite(q['V_min']):
+        raise ValueError('iaf_psc_delta: a finite V_min is not supported')
+    if q['refractory_input']:
+        raise ValueError('iaf_psc_delta: refractory_input = True is not supported')
+    p = glif_params(dict(V_m=q['V_m'], E_L=q['E_L'], C_m=q['C_m'], g=q['C_m'] / q['tau_m'], t_ref=q['t_ref'],
+                         V_th=q['V_th'], V_reset=q['V_reset'], tau_syn=(1.0,), I_e=q['I_e']))
+    p.model = _cabi.MODEL_IAF_PSC_DELTA
+    return p
+
+
 def glif_params(d):
     """NEST-format glif_psc parameter dict -> GlifParams (unknown keys are rejected). A dict with
     key 'model': 'iaf_psc_alpha' is taken as iaf_psc_alpha parameters."""
@@ -47,6 +70,8 @@ def glif_params(d):
         return d
     if d.get('model') == 'iaf_psc_alpha':
         return iaf_psc_alpha_params({k: v for k, v in d.items() if k != 'model'})
+    if d.get('model') == 'iaf_psc_delta':
+        return iaf_psc_delta_params({k: v for k, v in d.items() if k != 'model'})
     d = {k: v for k, v in d.items() if k != 'model'}
     unknown = set(d) - set(GLIF_PSC_DEFAULTS)
     if unknown:

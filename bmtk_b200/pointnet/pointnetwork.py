@@ -321,12 +321,12 @@ class PointNetwork(object):
             dp.setdefault('spike_dependent_threshold', r)
             dp.setdefault('after_spike_currents', a)
             dp.setdefault('adapting_threshold', v)
-        elif model == 'iaf_psc_alpha':
-            dp['model'] = 'iaf_psc_alpha'
+        elif model in ('iaf_psc_alpha', 'iaf_psc_delta'):
+            dp['model'] = model
         elif model != 'glif_psc':
             self.io.log_exception('node type {} of population {}: model_template "{}" is not supported by this '
                                   'engine (supported: nest:glif_psc, the nest:glif_lif*_psc variants and '
-                                  'nest:iaf_psc_alpha)'.format(type_id, pop.name, mt))
+                                  'nest:iaf_psc_alpha, nest:iaf_psc_delta)'.format(type_id, pop.name, mt))
         dp.pop('type', None)
         return {k: (np.asarray(v).tolist() if isinstance(v, np.ndarray) else v) for k, v in dp.items()}
 
@@ -421,8 +421,15 @@ class PointNetwork(object):
             iaf = self._type_is_iaf()[self.type_index[trg]] if n else np.zeros(0, dtype=bool)
             if np.any(iaf):
                 ports = np.where(iaf, (weight < 0).astype(np.uint8), ports).astype(np.uint8)
+            # iaf_psc_delta targets have one receptor: weights of either sign are jumps of V_m
+            delta = self._type_is_delta()[self.type_index[trg]] if n else np.zeros(0, dtype=bool)
+            if np.any(delta):
+                ports = np.where(delta, 0, ports).astype(np.uint8)
             yield dict(src=src_lookup(epop.source_node_ids[m]), trg=trg, weight=weight, delay=delay, port=ports,
                        edge_type_id=int(t), population=epop.name)
+
+    def _type_is_delta(self):
+        return np.array([t.get('model') == 'iaf_psc_delta' for t in self.types], dtype=bool)
 
     def _type_is_iaf(self):
         return np.array([t.get('model') == 'iaf_psc_alpha' for t in self.types], dtype=bool)

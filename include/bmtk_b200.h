@@ -51,7 +51,7 @@ typedef struct bmtk_glif_params {
     int32_t after_spike_currents;       /* "ASC" */
     int32_t adapting_threshold;         /* "A" */
     double I_e;                         /* constant input current, pA */
-    int32_t model;                      /* BMTK_MODEL_GLIF_PSC or BMTK_MODEL_IAF_PSC_ALPHA */
+    int32_t model;                      /* BMTK_MODEL_GLIF_PSC, _IAF_PSC_ALPHA or _IAF_PSC_DELTA */
     int32_t reserved;
 } bmtk_glif_params;
 
@@ -63,6 +63,10 @@ typedef struct bmtk_glif_params {
  * and fires on V >= V_th. */
 #define BMTK_MODEL_GLIF_PSC 0
 #define BMTK_MODEL_IAF_PSC_ALPHA 1
+/* NEST iaf_psc_delta (examples/point_120cells/network/cortex_node_types.csv:2-3): a weight is a jump of
+ * the membrane potential in mV applied in the step the spike arrives; input that arrives while the
+ * neuron is refractory is discarded; tau_syn and the receptor ports are unused (all ports add up). */
+#define BMTK_MODEL_IAF_PSC_DELTA 2
 
 typedef struct bmtk_engine bmtk_engine;
 

@@ -55,7 +55,7 @@ typedef struct {
     int32_t n_ports;
     int32_t spike_dependent_threshold, after_spike_currents, adapting_threshold;
     double I_e;
-    int32_t model;      /* 0 glif_psc, 1 iaf_psc_alpha */
+    int32_t model;      /* 0 glif_psc, 1 iaf_psc_alpha, 2 iaf_psc_delta */
     int32_t reserved;
 } orc_glif_params;
 
@@ -73,8 +73,8 @@ typedef struct {
     int32_t n_ref;                     /* update steps from spike to reset, inclusive */
     int32_t n_ports, has_theta_spike, has_asc, has_theta_voltage;
     double I_e;
-    int32_t iaf;                       /* iaf_psc_alpha conventions: reset in the spike step, >= test */
-    int32_t pad;
+    int32_t iaf;                       /* iaf_psc_alpha / iaf_psc_delta conventions: reset in the spike step, >= test */
+    int32_t delta;                     /* iaf_psc_delta: arriving weights are jumps of V, no PSC states */
 } orc_glif_consts;
 
 /* x + expm1(-x), accurate for small |x| (the numerator of the alpha-kernel/membrane cross term). */
@@ -143,7 +143,15 @@ void orc_glif_consts_init(const orc_glif_params* p, double h, orc_glif_consts* c
     c->v_reset = p->V_reset - p->E_L;
     c->n_ref = refractory_steps(p->t_ref, h);
     c->I_e = p->I_e;
-    c->iaf = p->model == 1;
+    c->iaf = p->model == 1 || p->model == 2;
+    c->delta = p->model == 2;
+    if (c->delta) {
+        /* NEST iaf_psc_delta: y3 <- P30 (y0 + I_e) + P33 y3 + spikes.get_value(lag) while not refractory; input
+         * that arrives during the refractory period is read and dropped (refractory_input = false);
+         * one receptor, excitatory and inhibitory weights share it. Used by
+         * examples/point_120cells/network/cortex_node_types.csv:2-3. */
+        c->n_ports = 0;
+    }
     if (c->iaf) {
         /* NEST iaf_psc_alpha: RefractoryCounts = Time(ms(t_ref)).get_steps(); V is set to V_reset in
          * the spike step and not integrated for that many following steps; spike when V >= V_th. */
@@ -302,6 +310,11 @@ int orc_run(orc_run_args* a)
                 U = v_old * c->P33 + (I + asc_sum) * c->P30;
                 for (int p = 0; p < c->n_ports; ++p)
                     U += c->P31[p] * a->y1[p * N + i] + c->P32[p] * a->y2[p * N + i];
+                if (c->delta) {
+                    double jump = 0.0;
+                    for (int p = 0; p < ORC_MAX_PORTS; ++p) jump += a->ring[(slot * ORC_MAX_PORTS + p) * N + i];
+                    U += jump;
+                }
                 if (c->has_theta_voltage) {
                     const double beta = (I + asc_sum) / c->G;
                     const double d = c->phi * (v_old - beta);
@@ -325,6 +338,8 @@ int orc_run(orc_run_args* a)
                 a->y1[p * N + i] = c->P11[p] * y1 + c->psc_init[p] * (*cell);
                 *cell = 0.0;
             }
+            if (c->delta)
+                for (int p = 0; p < ORC_MAX_PORTS; ++p) a->ring[(slot * ORC_MAX_PORTS + p) * N + i] = 0.0;
         }
         /* record + deliver, in ascending neuron id then virtual sources */
         for (int64_t i = 0; i < N; ++i) {

@@ -89,7 +89,8 @@ _IAF_DEFAULTS = dict(V_m=-70.0, E_L=-70.0, C_m=250.0, tau_m=10.0, t_ref=2.0, V_t
 
 def make_params(d):
     """dict with NEST glif_psc key names -> GlifParams; {'model': 'iaf_psc_alpha', ...} with NEST
-    iaf_psc_alpha names is mapped to g = C_m/tau_m, tau_syn = (tau_syn_ex, tau_syn_in), model = 1."""
+    iaf_psc_alpha names is mapped to g = C_m/tau_m, tau_syn = (tau_syn_ex, tau_syn_in), model = 1;
+    {'model': 'iaf_psc_delta', ...} likewise with model = 2 (no synaptic time constants)."""
     if d.get('model') == 'iaf_psc_alpha':
         q = dict(_IAF_DEFAULTS)
         q.update({k: v for k, v in d.items() if k in _IAF_DEFAULTS})
@@ -97,6 +98,13 @@ def make_params(d):
                              V_th=q['V_th'], V_reset=q['V_reset'], tau_syn=(q['tau_syn_ex'], q['tau_syn_in']),
                              I_e=q['I_e']))
         p.model = 1
+        return p
+    if d.get('model') == 'iaf_psc_delta':
+        q = dict(_IAF_DEFAULTS)
+        q.update({k: v for k, v in d.items() if k in _IAF_DEFAULTS})
+        p = make_params(dict(V_m=q['V_m'], E_L=q['E_L'], C_m=q['C_m'], g=q['C_m'] / q['tau_m'], t_ref=q['t_ref'],
+                             V_th=q['V_th'], V_reset=q['V_reset'], tau_syn=(1.0,), I_e=q['I_e']))
+        p.model = 2
         return p
     q = dict(_DEFAULTS)
     q.update({k: v for k, v in d.items() if k in _DEFAULTS})

@@ -408,6 +408,94 @@ def test_reference_example_network_glif_and_iaf_cells(cabi, deterministic):
     assert np.all(np.abs(rg - rc) <= 0.02 * rc + 0.05), (rg, rc)
 
 
+def _stored_example(name, n_steps, probes):
+    import json as _json
+    from bmtk_b200.engine import time_to_stamp
+    z = np.load(os.path.join(os.path.dirname(__file__), 'golden', name + '_network.npz'))
+    net = W.Network(name, 0.1, n_steps)
+    net.types = _json.loads(str(z['types_json']))
+    net.type_names = ['%s_%d' % tuple(x) for x in _json.loads(str(z['type_labels']))]
+    net.type_is_inh = np.zeros(len(net.types), dtype=bool)
+    net.type_index = z['type_index'].astype(np.uint16)
+    net.lo, net.hi = 0, len(net.type_index)
+    net.n_virtual = int(z['n_virtual'])
+    net.src, net.trg, net.weight, net.port = z['src'], z['trg'], z['weight'], z['port']
+    net.delay_steps = np.round(z['delay_ms'] / net.dt).astype(np.uint16)
+    net.in_virt = z['in_virt']
+    net.in_stamp = time_to_stamp(z['in_time_ms'], net.dt).astype(np.uint32)
+    net.probe_ids = np.array(probes, dtype=np.uint32)
+    return net
+
+
+@pytest.mark.parametrize('deterministic', [True, False])
+def test_reference_example_point_120cells_iaf_psc_delta(cabi, deterministic):
+    """examples/point_120cells (120 iaf_psc_delta cells with NEST's default parameters, 2.0 / -1.5 mV recurrent
+    and 4.2 mV thalamic jumps, 1.5 ms delays) for 1000 ms at dt = 0.1 ms. All weights are multiples of 0.1 mV
+    sums of a few of them, so fp32 follows the fp64 oracle closely: spikes within one step over the first
+    100 ms, traces until the lists part, rates within 2 %."""
+    net = _stored_example('point_120cells', 10000, [0, 20, 60, 80, 100])
+    assert all(t.get('model') == 'iaf_psc_delta' for t in net.types) and net.n_neurons == 120
+    eng, st, ids, tr = _run_engine(net, deterministic=deterministic)
+    r = oracle_from_network(net).run(net.n_steps)
+    assert r['n_spikes'] > 200
+    ok, bad = _spikes_within_one_step(st, ids, r['spike_step'], r['spike_id'], 1000)
+    assert ok, bad
+    ok, bad = _spikes_within_one_step(r['spike_step'], r['spike_id'], st, ids, 1000)
+    assert ok, bad
+    div = _first_divergence(st, ids, r['spike_step'], r['spike_id'])
+    _trace_check(tr, r['trace'], min(div - 1, net.n_steps))
+    t_ms = net.n_steps * net.dt
+    rg, rc = rates_by_type(net, ids, t_ms), rates_by_type(net, r['spike_id'], t_ms)
+    assert np.all(np.abs(rg - rc) <= 0.02 * rc), (rg, rc)
+
+
+def test_iaf_psc_delta_cells(cabi):
+    """iaf_psc_delta conventions: a weight is a jump of V_m applied in the step the spike arrives, input that
+    arrives during the refractory period is dropped, V >= V_th fires and resets in the same step, every
+    receptor port feeds the same jump. 600 cells of two parameter sets under current steps plus
+    excitatory and inhibitory virtual input on all four ports."""
+    rng = np.random.default_rng(31)
+    n, nv = 600, 40
+    net = W.Network('delta', 0.1, 3000)
+    net.types = [dict(model='iaf_psc_delta'),
+                 dict(model='iaf_psc_delta', I_e=120.0, tau_m=7.0, C_m=80.0, t_ref=1.05, E_L=-65.0, V_th=-50.0, V_reset=-60.0, V_m=-63.0)]
+    net.type_names = ['delta_default', 'delta_fast']
+    net.type_is_inh = np.array([False, True])
+    net.type_index = np.repeat([0, 1], n // 2).astype(np.uint16)
+    net.lo, net.hi = 0, n
+    net.n_virtual = nv
+    k = 8000
+    net.src = (n + rng.integers(0, nv, k)).astype(np.uint32)
+    net.trg = rng.integers(0, n, k).astype(np.uint32)
+    net.weight = (np.round(rng.normal(0.6, 1.5, k) * 8.0) / 8.0).astype(np.float32)    # mV jumps
+    net.port = rng.integers(0, 4, k).astype(np.uint8)
+    net.delay_steps = rng.integers(1, 20, k).astype(np.uint16)
+    net.in_virt, net.in_stamp = W._poisson_trains(np.random.default_rng(32), np.full(nv, 60.0), 300.0, net.dt)
+    ids = np.arange(n, dtype=np.uint32)
+    amp = rng.uniform(200.0, 600.0, n).astype(np.float32)
+    net.clamp_step = np.concatenate([np.full(n, 201), np.full(n, 2501)]).astype(np.uint64)
+    net.clamp_target = np.concatenate([ids, ids])
+    net.clamp_delta = np.concatenate([amp, -amp])
+    net.probe_ids = np.array([0, 150, 299, 300, 450, 599], dtype=np.uint32)
+    for det in (True, False):
+        eng, st, sid, tr = _run_engine(net, deterministic=det)
+        r = oracle_from_network(net).run(net.n_steps)
+        assert r['n_spikes'] > 3000
+        cg, co = np.bincount(sid, minlength=n), np.bincount(r['spike_id'], minlength=n)
+        assert np.abs(cg - co).max() <= 1 and np.count_nonzero(cg != co) <= 6
+        same = cg == co
+        og, oc = np.lexsort((st, sid)), np.lexsort((r['spike_step'], r['spike_id']))
+        a_s, a_i, b_s, b_i = st[og], sid[og], r['spike_step'][oc], r['spike_id'][oc]
+        d = np.abs(a_s[same[a_i]] - b_s[same[b_i]])
+        assert np.mean(d <= 1) > 0.99 and np.mean(d == 0) > 0.9
+        for q, i in enumerate(net.probe_ids.astype(np.int64)):
+            a, b = st[sid == i], r['spike_step'][r['spike_id'] == i]
+            m = min(len(a), len(b))
+            neq = np.nonzero(a[:m] != b[:m])[0]
+            upto = (min(a[neq[0]], b[neq[0]]) - 1) if len(neq) else (net.n_steps if len(a) == len(b) else (a if len(a) > m else b)[m] - 1)
+            _trace_check(tr[:, q:q + 1], r['trace'][:, q:q + 1], upto)
+
+
 def test_iaf_psc_alpha_cells(cabi):
     """iaf_psc_alpha conventions (reset in the spike step, refractory for round(t_ref/dt) steps,
     V >= V_th fires, weight sign picks the excitatory / inhibitory alpha current): 600 cells of the

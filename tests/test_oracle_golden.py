@@ -181,3 +181,41 @@ def test_empty_and_input_only_networks(oracle):
     assert np.allclose(sim.v_m(), -78.85)
     sim = oracle.OracleSim([p], np.zeros(0, dtype=int), 0.1)
     assert sim.run(10)['n_spikes'] == 0
+
+
+def test_iaf_psc_delta_oracle_against_closed_forms(oracle):
+    """iaf_psc_delta restatement: (1) under a constant current the first threshold crossing is the first grid
+    point at which E_L + I R (1 - exp(-t/tau)) >= V_th, and the neuron then repeats with period
+    crossing + t_ref (reset in the spike step, t_ref/dt refractory steps); (2) a weight arriving through a
+    synapse of d steps from a spike emitted in step n is a jump of exactly that many mV in step n + d;
+    (3) a jump that arrives while the neuron is refractory is dropped."""
+    dt = 0.1
+    p = dict(model='iaf_psc_delta', I_e=400.0, tau_m=10.0, C_m=250.0, t_ref=2.0, E_L=-70.0, V_th=-55.0, V_reset=-70.0)
+    sim = oracle.OracleSim([p], np.zeros(1, dtype=np.uint16), dt)
+    sim.set_probes([0], 1)
+    r = sim.run(1000)
+    R = p['tau_m'] / p['C_m'] * 1e3          # MOhm * pA = uV -> mV: tau/C in ms/pF = GOhm
+    vinf = p['I_e'] * p['tau_m'] / p['C_m']   # mV above E_L
+    k = np.arange(1, 2000)
+    first = int(k[vinf * (1.0 - np.exp(-k * dt / p['tau_m'])) >= p['V_th'] - p['E_L']][0])
+    assert r['spike_step'][0] == first
+    period = first + int(round(p['t_ref'] / dt))
+    assert np.all(np.diff(r['spike_step']) == period) and len(r['spike_step']) == (1000 - first) // period + 1
+    del R
+    # (2), (3): one virtual cell -> neuron, weight 3.25 mV, delay 7 steps; no current
+    q = dict(p, I_e=0.0)
+    sim = oracle.OracleSim([q], np.zeros(1, dtype=np.uint16), dt, n_virtual=1, src=[1], trg=[0], weight=[3.25],
+                           delay_steps=[7], port=[2])
+    sim.set_probes([0], 1)
+    sim.set_input_spikes([10], [0])           # emitted in step 10 -> jump in step 17
+    tr = sim.run(40)['trace'][:, 0]
+    assert np.all(tr[:17] == -70.0) and tr[17] == -70.0 + 3.25
+    assert tr[18] == pytest.approx(-70.0 + 3.25 * np.exp(-dt / 10.0), abs=1e-12)
+    big = dict(q)
+    sim = oracle.OracleSim([big], np.zeros(1, dtype=np.uint16), dt, n_virtual=1, src=[1], trg=[0], weight=[16.0],
+                           delay_steps=[1], port=[0])
+    sim.set_probes([0], 1)
+    sim.set_input_spikes([5, 10, 40], [0, 0, 0])   # 16 mV > 15 mV: fires in step 6; the jump of step 11 falls in the refractory period
+    r = sim.run(60)
+    assert r['spike_step'].tolist() == [7, 42]
+    assert np.all(r['trace'][6:26, 0] == -70.0)
