@@ -761,6 +761,15 @@ class WFile(WGroup):
             self._closed = True
             _Serializer(self).write(self.filename)
 
+    def __del__(self):
+        # like h5py, a file that was never closed is still written when the object goes away (the
+        # reference's write_sonata leaves its file to the garbage collector,
+        # bmtk/utils/reports/spike_trains/spikes_file_writers.py:52-71)
+        try:
+            self.close()
+        except Exception:
+            pass
+
 
 class _Serializer(object):
     LEAF_K = 32       # a symbol table node holds up to 2K entries

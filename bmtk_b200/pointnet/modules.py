@@ -128,7 +128,9 @@ class SpikesMod(SimulatorMod):
             st = SpikeTrains()
             if len(gids):
                 node_ids, pops = sim.net.gid_pool.get_node_ids(gids)
-                t = stamps.astype(np.float64) * sim.dt
+                # the decimal value of stamp x dt (NEST writes spike times as decimal text, which the reference reads
+                # back: 215 x 0.1 is 21.5 there, not 21.500000000000004)
+                t = np.round(stamps.astype(np.float64) * sim.dt, 6)
                 for p in pd.unique(pops):
                     m = pops == p
                     st.add_spikes(node_ids[m], t[m], p)

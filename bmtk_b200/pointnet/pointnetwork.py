@@ -360,8 +360,8 @@ class PointNetwork(object):
         """Per edge type: weight, delay, port (sonata_adaptors.py:268-357). Yields dict batches with
         sources already mapped by `src_lookup` and targets mapped to engine ids."""
         nsyns_col, w_col, d_col = epop.column('nsyns'), epop.column('syn_weight'), epop.column('delay')
-        _, first = np.unique(epop.edge_type_ids, return_index=True)
-        for t in epop.edge_type_ids[np.sort(first)]:
+        # batches in ascending edge_type_id, the order of the reference's groupby('etid') (sonata_adaptors.py:298)
+        for t in np.unique(epop.edge_type_ids):
             row = epop.types_table[t]
             m = np.nonzero(epop.edge_type_ids == t)[0]
             n = len(m)
