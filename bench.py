@@ -183,7 +183,9 @@ def parity_check(full_net, st, ids, n_steps, threads, stream=0):
                       n_threads=threads, canonical_csr=False)
     steps, srcs = O.poisson_spikes(full_net.poisson_rate_hz, full_net.dt, full_net.poisson_seed, 0, n_steps, stream=stream)
     sim.set_input_spikes(steps, srcs)
+    t_setup = time.time() - t0
     r = sim.run(n_steps, spike_cap=max(1 << 20, full_net.n_neurons * 16))
+    t_run = time.time() - t0 - t_setup
     ost, oid = r['spike_step'], r['spike_id'].astype(np.int64)
     st, ids = np.asarray(st, dtype=np.int64), np.asarray(ids, dtype=np.int64)
     o = np.lexsort((ids, st))
@@ -202,7 +204,7 @@ def parity_check(full_net, st, ids, n_steps, threads, stream=0):
                         'share_beyond': (wide['neurons_with_other_count'] + wide['spikes_beyond_one_step']) / max(1, wide['n_b'])},
         'max_type_rate_rel_err': ra['max_rel_err'], 'rates_within_2pct': ra['within_rel_only'],
         'ok': bool(strict['ok'] and ra['within_rel_only']),
-        'oracle_wall_s': time.time() - t0,
+        'oracle_wall_s': {'setup': t_setup, 'run': t_run, 'compare': time.time() - t0 - t_setup - t_run},
     }
 
 
@@ -493,7 +495,7 @@ def main():
         g_st, g_ids = gather_spikes(first_spikes[0], first_spikes[1], world, rank, dist)
         if rank == 0:
             full = net if world == 1 else make_network(args.scale)
-            parity = parity_check(full, g_st, g_ids, steps_per_bench_step, os.cpu_count() or 1)
+            parity = parity_check(full, g_st, g_ids, steps_per_bench_step, len(os.sched_getaffinity(0)) or 1)
             del full
 
     # ---------------- CPU baseline (rank 0, N = 1 only)

@@ -311,6 +311,9 @@ struct bmtk_engine {
 
     // persistent stepping (single rank, atomic delivery)
     bool persistent = true, phase_timers = false, ring_prefetch = false;
+    uint32_t tune = 0;
+    uint32_t pipe_blocks_opt = 0;   // option pipeline_blocks: fewer blocks than SMs (a small network needs few update warps,
+                                    // and a hand-over over fewer blocks is cheaper)
     int persist_blocks = 0;
     bool persist_resident = false;
     uint4* d_pipe_seg = nullptr;
@@ -831,6 +834,7 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.trace_cap = e->trace_cap;
     a.profile = e->phase_timers ? 1u : 0u;
     a.ring_prefetch = e->ring_prefetch ? 1u : 0u;
+    a.tune = e->tune;
     a.n_ranks = (uint32_t)e->n_ranks;
     a.rank = (uint32_t)e->rank;
     a.xchg_cap = e->send_cap;
@@ -1132,6 +1136,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
+    if (k == "tune") { e->tune = (uint32_t)value; return BMTK_OK; }
     if (k == "chunk_steps") {
         if (value < 1) return fail(BMTK_E_INVALID, "chunk_steps must be positive");
         e->chunk_steps = (uint64_t)value;
@@ -1146,6 +1151,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     }
     else if (k == "trial_base") e->trial_base = (uint32_t)value;
     else if (k == "window") e->window_opt = (uint32_t)value;
+    else if (k == "pipeline_blocks") e->pipe_blocks_opt = (uint32_t)value;
     else if (k == "spike_capacity") e->spike_cap_opt = (uint64_t)value;
     else if (k == "log_capacity") e->log_cap = std::max<uint64_t>(1024, (uint64_t)value);
     else if (k == "event_capacity") e->event_cap = std::max<uint64_t>(1024, (uint64_t)value);
@@ -1413,7 +1419,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
         if (!coop || blocks > 512) e->persist_blocks = 0;
         if (e->persist_blocks > 0 && e->n_trials == 1 && e->window >= 2 && e->n_edges < (1ull << 32)) {
-            const int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt));
+            int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt));
+            if (pb > 0 && e->pipe_blocks_opt) pb = std::min<int>(pb, (int)e->pipe_blocks_opt);
             if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
                 // chunks of 32 groups are dealt round-robin to the update warps of the blocks
                 const uint64_t chunks = ((uint64_t)(e->n_pad / 4) + 31) / 32;

@@ -183,6 +183,21 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
     }
 }
 
+// CSR entries are read once per spike and never again soon: loaded with an evict-first L2 policy they do not
+// push the ring slots and chunk lists, which every step re-reads, out of L2.
+__device__ __forceinline__ uint2 ld_entry_stream(const uint2* p, unsigned long long policy) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.u32 {%0, %1}, [%2], %3;"
+                 : "=r"(v.x), "=r"(v.y)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ unsigned long long evict_first_policy() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
 // Streams one chunk into the ring with one warp: up to kInFlight entries per lane in flight.
 __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d, uint32_t lane) {
     // a descriptor that does not describe a piece of the CSR is not followed (it would mean a list was read
@@ -194,9 +209,16 @@ __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
     uint2 e[kInFlight];
+    if (a.tune & 1u) {
+        const unsigned long long pol = evict_first_policy();
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u)
-        if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
+        for (int u = 0; u < kInFlight; ++u)
+            if (lane + 32u * u < d.y) e[u] = ld_entry_stream(&a.entries[d.x + lane + 32u * u], pol);
+    } else {
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+            if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
+    }
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
         if (lane + 32u * u < d.y) {
@@ -251,53 +273,64 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
 }
 
 // Several ranks: what block b of every other rank emitted in the phase with index k mod 4 and tag `tag` is
-// delivered by block b here (chunk warp w takes entries w, w + n_cw, ...): the warp waits (bounded) for
-// the tagged count word of that block and for each entry's tag, looks up the row of the spiking neuron
-// in THIS rank's CSR (all sources have a row, the targets are local) and streams it chunk by chunk.
+// delivered by block b here. Lane r of every chunk warp waits (bounded) for the tagged count word of rank r, so
+// the waits on the different ranks overlap; the ranks' entries then form ONE list (rank 0's, rank 1's, ...) that
+// is dealt round-robin to the block's chunk warps - a rank contributes one or two spikes per block and phase, and
+// dealing every rank's entries separately would leave warp 0 with a row of every rank and the others idle. For
+// its entry the warp waits for the entry's tag (its store may trail the count word), looks up the row of the
+// spiking neuron in THIS rank's CSR (all sources have a row, the targets are local) and streams it.
 __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, uint32_t k, uint32_t tag, uint32_t prev_slot,
                                                uint32_t w, uint32_t n_cw, uint32_t lane, DeliveryTotals& tot, bool& dead) {
     unsigned long long events = 0ull;
-    // lane r waits for rank r's count word: the waits on the different ranks overlap
-    u64 my_cw = 0;
+    uint32_t my_n = 0;
     if (lane < a.n_ranks && lane != a.rank && !dead) {
         const u64* p = xp_cnt(xp, k, lane, blockIdx.x);
         unsigned int spins = 0;
-        while ((uint32_t)((my_cw = ld_word(p)) >> 32) != tag) {
+        u64 cw;
+        while ((uint32_t)((cw = ld_word(p)) >> 32) != tag) {
             if (++spins > kWaitSpins) {
                 atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
                 dead = true;
                 break;
             }
-            __nanosleep(100);
+            __nanosleep(50);
         }
+        if ((uint32_t)(cw >> 32) == tag) my_n = min((uint32_t)cw, kXPipeSeg);
     }
-    for (uint32_t r = 0; r < a.n_ranks; ++r) {
-        if (r == a.rank) continue;
-        const u64 cw = __shfl_sync(0xffffffffu, my_cw, r);
-        if ((uint32_t)(cw >> 32) != tag) continue;   // timed out (uniform over the warp)
-        const uint32_t n = min((uint32_t)cw, kXPipeSeg);
-        const u64* ent = xp_ent(xp, k, r, blockIdx.x, a.n_ranks, gridDim.x);
-        for (uint32_t i = w; i < n; i += n_cw) {
-            u64 e = 0;
-            if (lane == 0) {
-                unsigned int spins = 0;
-                while ((uint32_t)((e = ld_word(ent + i)) >> 32) != tag) {   // its store may trail the count word
-                    if (++spins > kWaitSpins) {
-                        atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
-                        break;
-                    }
-                    __nanosleep(100);
+    dead = __any_sync(0xffffffffu, dead);
+    // exclusive prefix of the ranks' counts over the lanes
+    uint32_t incl = my_n;
+#pragma unroll
+    for (int dlt = 1; dlt < 32; dlt <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, dlt);
+        if (lane >= (uint32_t)dlt) incl += t;
+    }
+    const uint32_t my_off = incl - my_n;
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    for (uint32_t j = w; j < total; j += n_cw) {
+        const uint32_t owner = __ballot_sync(0xffffffffu, my_n != 0u && my_off <= j && j < my_off + my_n);
+        const int r = __ffs(owner) - 1;   // exactly one lane holds j
+        const uint32_t i = j - __shfl_sync(0xffffffffu, my_off, r);
+        const u64* ent = xp_ent(xp, k, (uint32_t)r, blockIdx.x, a.n_ranks, gridDim.x);
+        u64 e = 0;
+        if (lane == 0) {
+            unsigned int spins = 0;
+            while ((uint32_t)((e = ld_word(ent + i)) >> 32) != tag) {
+                if (++spins > kWaitSpins) {
+                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                    break;
                 }
+                __nanosleep(50);
             }
-            e = __shfl_sync(0xffffffffu, e, 0);
-            if ((uint32_t)(e >> 32) != tag) continue;
-            const uint32_t src = (uint32_t)e & kSrcMask;
-            const unsigned long long rb = a.rowptr[src], re = a.rowptr[src + 1];
-            const uint32_t slot0 = wrap_slot(prev_slot + ((uint32_t)e >> kSrcBits), a.ring_slots);
-            events += re - rb;
-            for (unsigned long long c = rb; c < re; c += kChunk)
-                stream_chunk(a, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
         }
+        e = __shfl_sync(0xffffffffu, e, 0);
+        if ((uint32_t)(e >> 32) != tag) continue;
+        const uint32_t src = (uint32_t)e & kSrcMask;
+        const unsigned long long rb = a.rowptr[src], re = a.rowptr[src + 1];
+        const uint32_t slot0 = wrap_slot(prev_slot + ((uint32_t)e >> kSrcBits), a.ring_slots);
+        events += re - rb;
+        for (unsigned long long c = rb; c < re; c += kChunk)
+            stream_chunk(a, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
     }
     if (lane == 0) tot.events += events;
 }
@@ -447,6 +480,14 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     F4 in[kPorts];
 #pragma unroll
                     for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
+                    if ((a.tune & 2u) && (threadIdx.x & 7u) == 0u) {
+                        // the next step's slot (of the next phase when this is the phase's last step): deliveries may
+                        // still be adding to it in L2, which is where this brings its lines; one request per 128 bytes
+                        const float* nxt = a.ring + (size_t)wrap_slot(sl + 1u, S) * kPorts * a.n_pad + i0;
+#pragma unroll
+                        for (int pt = 0; pt < kPorts; ++pt)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt + (size_t)pt * a.n_pad));
+                    }
                     mask = nr.step(types, in);
                     if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
                     const F4 zero = {{0.f, 0.f, 0.f, 0.f}};

@@ -149,6 +149,20 @@ class NodeSet(object):
         return out
 
 
+def balanced_bounds(load, parts):
+    """Bounds b[0..parts] of contiguous blocks of len(load) items whose load sums are as equal as contiguous cuts
+    allow: cut k lies where the running sum first reaches k/parts of the total (items without load count 1 so that
+    unconnected neurons still spread). Every block gets at least one item when there are enough."""
+    w = np.maximum(np.asarray(load, dtype=np.int64), 1)
+    c = np.concatenate([[0], np.cumsum(w)])
+    n = len(w)
+    b = np.searchsorted(c, c[-1] * np.arange(parts + 1) / float(parts), side='left').astype(np.int64)
+    b[0], b[-1] = 0, n
+    for k in range(1, parts):               # strictly increasing while items are left
+        b[k] = min(max(b[k], b[k - 1] + (1 if n >= parts else 0)), n)
+    return b
+
+
 class PointNetwork(object):
     def __init__(self, **properties):
         self._components = {}
@@ -162,6 +176,8 @@ class PointNetwork(object):
         self.types = []               # one NEST glif_psc dict per node-type batch
         self.type_labels = []         # (population, node_type_id)
         self.type_index = np.zeros(0, dtype=np.uint16)
+        self.target_block = None      # (lo, hi) engine ids whose incoming edges this rank expands; None = all
+        self.block_bounds = None
         self.edge_batches = []        # dict(src, trg, weight, delay, port) in engine ids, recurrent
         self.virtual_index = {}       # population -> (sorted node_ids, virtual index)
         self.n_virtual = 0
@@ -356,14 +372,38 @@ class PointNetwork(object):
         self.type_index = np.concatenate(type_index) if type_index else np.zeros(0, dtype=np.uint16)
         self._nodes_built = True
 
+    # ---- several ranks: contiguous blocks of engine ids, balanced by in-degree
+    def partition(self, rank, world):
+        """Cuts the engine ids into `world` contiguous blocks whose in-degree sums (recurrent and virtual
+        edges) are as equal as contiguous cuts allow, and makes this network expand only the edges that end
+        in block `rank`: a rank then never holds the other ranks' weight, delay and port arrays. Returns the
+        block bounds (world + 1 engine ids). Call before build_recurrent_edges / add_spike_trains."""
+        if not self._nodes_built:
+            self.build_nodes()
+        n = len(self._gid_pool)
+        indeg = np.zeros(n, dtype=np.int64)
+        for epop in self._edge_populations:
+            tp = epop.target_population
+            if tp not in self._node_populations or self._node_populations[tp].is_virtual:
+                continue
+            indeg += np.bincount(self._gid_pool.get_nestids(tp, epop.target_node_ids), minlength=n)
+        self.block_bounds = balanced_bounds(indeg, world)
+        self.target_block = (int(self.block_bounds[rank]), int(self.block_bounds[rank + 1]))
+        return self.block_bounds
+
     def _expand_edges(self, epop, src_lookup, trg_pop_name):
         """Per edge type: weight, delay, port (sonata_adaptors.py:268-357). Yields dict batches with
         sources already mapped by `src_lookup` and targets mapped to engine ids."""
         nsyns_col, w_col, d_col = epop.column('nsyns'), epop.column('syn_weight'), epop.column('delay')
+        local = None
+        if self.target_block is not None:
+            # with several ranks only the edges that end in this rank's block are expanded
+            trg_all = self._gid_pool.get_nestids(trg_pop_name, epop.target_node_ids)
+            local = (trg_all >= self.target_block[0]) & (trg_all < self.target_block[1])
         # batches in ascending edge_type_id, the order of the reference's groupby('etid') (sonata_adaptors.py:298)
         for t in np.unique(epop.edge_type_ids):
             row = epop.types_table[t]
-            m = np.nonzero(epop.edge_type_ids == t)[0]
+            m = np.nonzero(epop.edge_type_ids == t if local is None else (epop.edge_type_ids == t) & local)[0]
             n = len(m)
             model = row.get('model_template')
             if model not in (None, 'static_synapse'):
@@ -440,6 +480,8 @@ class PointNetwork(object):
             return
         if not self._nodes_built:
             self.build_nodes()
+        if self.io.mpi_size > 1 and self.target_block is None:
+            self.partition(self.io.mpi_rank, self.io.mpi_size)
         for epop in self._edge_populations:
             sp, tp = epop.source_population, epop.target_population
             if sp not in self._node_populations or tp not in self._node_populations:

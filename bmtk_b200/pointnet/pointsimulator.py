@@ -134,8 +134,14 @@ class PointSimulator(object):
         net = self._graph
         n = len(net.gid_pool)
         rank, world = io.mpi_rank, io.mpi_size
-        bounds = np.linspace(0, n, world + 1).astype(np.int64)
-        lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+        if world > 1:
+            # blocks balanced by in-degree; the network has expanded only this rank's incoming edges
+            if net.target_block is None:
+                io.log_exception('the network was built before the ranks were known: call PointNetwork.partition(rank, '
+                                 'world) before build() or let build_recurrent_edges do it (RANK / WORLD_SIZE set)')
+            lo, hi = net.target_block
+        else:
+            lo, hi = 0, n
         self._block = (lo, hi)
         device = int(os.environ.get('LOCAL_RANK', '0'))
         eng = Engine(self._dt, device=device)

@@ -345,3 +345,45 @@ def test_weight_function_is_called_per_edge_type(project, tmp_path):
         lines[1] = lines[1].replace('scaled_by_target', 'not_registered')
         tf.write_text('\n'.join(lines) + '\n')
         pointnet.PointNetwork.from_config(conf).build()
+
+
+def test_partition_by_in_degree_expands_only_the_local_edges(project):
+    """Several ranks: blocks of engine ids are cut where the running in-degree sum passes k/N of the total, and
+    a rank expands only the edges that end in its block; the ranks' edge lists together are the whole list."""
+    from bmtk_b200.pointnet.pointnetwork import balanced_bounds
+    net, info = project
+    conf = pointnet.Config.from_json(info['config'])
+    whole = pointnet.PointNetwork.from_config(conf)
+    whole.dt = 0.1
+    whole.build()
+    whole.add_spike_trains(pointnet.SpikeTrains.load(conf.inputs[list(conf.inputs)[0]]['input_file']), 'lgn'
+                           if 'lgn' in [p.name for p in whole.node_populations] else [p.name for p in whole.node_populations if p.is_virtual][0])
+    src, trg, w, d, port = whole.edge_arrays()
+    n = len(whole.gid_pool)
+    indeg = np.bincount(trg, minlength=n)
+    world = 3
+    parts, bounds = [], None
+    for rank in range(world):
+        g = pointnet.PointNetwork.from_config(conf)
+        g.dt = 0.1
+        b = g.partition(rank, world)
+        assert bounds is None or np.array_equal(b, bounds)
+        bounds = b
+        g.build()
+        g.add_spike_trains(pointnet.SpikeTrains.load(conf.inputs[list(conf.inputs)[0]]['input_file']),
+                           [p.name for p in g.node_populations if p.is_virtual][0])
+        s2, t2, w2, d2, p2 = g.edge_arrays()
+        lo, hi = g.target_block
+        assert len(t2) and t2.min() >= lo and t2.max() < hi
+        m = (trg >= lo) & (trg < hi)
+        assert np.array_equal(s2, src[m]) and np.array_equal(t2, trg[m]) and np.array_equal(w2, w[m])
+        assert np.array_equal(d2, d[m]) and np.array_equal(p2, port[m])
+        parts.append(len(t2))
+    assert sum(parts) == len(src) and bounds[0] == 0 and bounds[-1] == n and np.all(np.diff(bounds) > 0)
+    # balanced by in-degree: every block within one neuron's in-degree of the ideal share
+    share = np.array([indeg[bounds[k]:bounds[k + 1]].sum() for k in range(world)])
+    assert np.abs(share - len(src) / world).max() <= indeg.max() + 1
+    # the helper on its own: unconnected items still spread, more parts than items does not crash
+    assert balanced_bounds(np.zeros(10), 2).tolist() == [0, 5, 10]
+    assert balanced_bounds(np.array([5, 1, 1, 1, 1, 1]), 2).tolist() == [0, 1, 6]
+    assert balanced_bounds(np.ones(2), 4)[-1] == 2
