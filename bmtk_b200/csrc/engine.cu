@@ -319,6 +319,7 @@ struct bmtk_engine {
     uint4* d_pipe_seg = nullptr;
     uint32_t* d_pipe_sync = nullptr;     // pipelined kernel: the two phase counters
     uint32_t* d_log_seg_cnt = nullptr;   // pipelined kernel: spikes each block logged in the last launch
+    unsigned long long* d_blk_prof = nullptr;   // pipelined kernel: per-block busy / wait sums (option phase_timers)
     bool log_segmented = false;          // the device log of the current chunk is in per-block segments
     bool pipeline = true;     // option: use the pipelined kernel where it applies
     bool pipe_ok = false;     // resident state, one trial, min delay >= 2 steps
@@ -853,6 +854,7 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
         a.log_seg_cnt = e->d_log_seg_cnt;
         e->log_segmented = e->record_spikes;
         a.upd_warps = e->pipe_upd_warps;
+        a.blk_prof = e->phase_timers ? e->d_blk_prof : nullptr;
         // input warps: one thread per 2 Poisson cells of the block's share, at most half of the non-update warps;
         // replayed spikes alone get one warp
         {
@@ -982,6 +984,7 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_xchg);
     cudaFree(e->d_pipe_seg);
     cudaFree(e->d_log_seg_cnt);
+    cudaFree(e->d_blk_prof);
     cudaFree(e->d_pipe_sync);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     for (uint32_t* p : e->h_spk_blocks) cudaFreeHost(p);
@@ -1437,6 +1440,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 if (e->pipe_ok) {
                     CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
                     CU(cudaMalloc(&e->d_pipe_sync, 32));
+                    CU(cudaMalloc(&e->d_blk_prof, 32 * (size_t)pb + 8 * 96));
+                    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)pb + 8 * 96));
                     CU(cudaMalloc(&e->d_log_seg_cnt, 4 * (size_t)pb));
                     CU(cudaMemset(e->d_log_seg_cnt, 0, 4 * (size_t)pb));
                     // a descriptor is valid by its tag (first step of its phase + 1): none is at rest
@@ -1919,6 +1924,20 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path) {
         CU(cudaMemset(e->d_xchg + kXDescWords + e->xp_off, 0, 8 * xpipe_words((uint32_t)e->n_ranks, (uint32_t)std::max(e->persist_blocks, e->pipe_blocks))));
     if (e->d_pipe_seg) CU(cudaMemset(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap));
     // replayed inputs handed over before the load are re-indexed from the restored step
+    return BMTK_OK;
+}
+
+int bmtk_engine_block_profile(bmtk_engine* e, uint64_t cap_blocks, uint64_t* out4, uint64_t* n_blocks) {
+    if (!e || !e->finalized || !n_blocks) return fail(BMTK_E_INVALID, "block_profile: engine missing, not finalized, or NULL");
+    *n_blocks = e->d_blk_prof ? (uint64_t)e->pipe_blocks : 0;
+    if (!e->d_blk_prof || !out4) return BMTK_OK;
+    if (cap_blocks < *n_blocks + 24) return fail(BMTK_E_INVALID, "block_profile: room for %llu blocks, %llu needed",
+                                            (unsigned long long)cap_blocks, (unsigned long long)*n_blocks);
+    int rc = set_device(e);
+    if (rc) return rc;
+    CU(cudaStreamSynchronize(e->stream));
+    CU(cudaMemcpy(out4, e->d_blk_prof, 32 * (size_t)e->pipe_blocks + 8 * 96, cudaMemcpyDeviceToHost));
+    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)e->pipe_blocks + 8 * 96));
     return BMTK_OK;
 }
 

@@ -70,9 +70,9 @@ struct PersistArgs {
     uint32_t trace_cap;
     uint32_t profile;
     uint32_t ring_prefetch;    // RESIDENT: copy the next step's ring slot to shared memory while this step computes
-    uint32_t tune;             // pipelined kernel: bit 0 CSR entries are loaded with an evict-first L2 policy (they are used
-                               // once; the ring and the lists should stay), bit 1 the update warps ask L2 for the next
-                               // step's ring slot while they compute this one
+    unsigned long long* blk_prof;   // pipelined kernel, option phase_timers: per block {producing side busy ns, its hand-over wait ns,
+                               // delivering side busy ns, its hand-over wait ns}, summed over the launch
+    uint32_t tune;             // pipelined kernel: experiment switches (none in use)
     // Spike exchange between ranks over peer memory (n_ranks > 1). Every rank owns an exchange
     // buffer of 64-bit words laid out as  counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
     // peers[r] is rank r's buffer as mapped into this process (peers[rank] is the local one).

@@ -129,6 +129,14 @@ __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mi
     asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
 }
 
+// Option phase_timers: every warp adds the time from the start of its phase to the moment it reaches the hand-over
+// to a histogram of its role (0 update, 1 input, 2 chunk warps): 32 bins of 250 ns behind the per-block sums.
+__device__ __forceinline__ void hist_add(const PersistArgs& a, uint32_t role, unsigned long long ns) {
+    if (!a.blk_prof) return;
+    const unsigned long long b = ns / 250ull;
+    atomicAdd(a.blk_prof + 4ull * gridDim.x + 32ull * role + (b < 31ull ? b : 31ull), 1ull);
+}
+
 struct DeliveryTotals {
     unsigned long long events, inputs, spikes;
 };
@@ -183,21 +191,6 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
     }
 }
 
-// CSR entries are read once per spike and never again soon: loaded with an evict-first L2 policy they do not
-// push the ring slots and chunk lists, which every step re-reads, out of L2.
-__device__ __forceinline__ uint2 ld_entry_stream(const uint2* p, unsigned long long policy) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.u32 {%0, %1}, [%2], %3;"
-                 : "=r"(v.x), "=r"(v.y)
-                 : "l"(p), "l"(policy));
-    return v;
-}
-__device__ __forceinline__ unsigned long long evict_first_policy() {
-    unsigned long long pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
 // Streams one chunk into the ring with one warp: up to kInFlight entries per lane in flight.
 __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d, uint32_t lane) {
     // a descriptor that does not describe a piece of the CSR is not followed (it would mean a list was read
@@ -209,16 +202,9 @@ __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
     uint2 e[kInFlight];
-    if (a.tune & 1u) {
-        const unsigned long long pol = evict_first_policy();
 #pragma unroll
-        for (int u = 0; u < kInFlight; ++u)
-            if (lane + 32u * u < d.y) e[u] = ld_entry_stream(&a.entries[d.x + lane + 32u * u], pol);
-    } else {
-#pragma unroll
-        for (int u = 0; u < kInFlight; ++u)
-            if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
-    }
+    for (int u = 0; u < kInFlight; ++u)
+        if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
         if (lane + 32u * u < d.y) {
@@ -241,7 +227,9 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
     uint4 d = make_uint4(0u, 0u, 0u, 0u);
     if (lane >= 1 && lane < kSpill && lane < G) {
         const uint32_t src = (blockIdx.x + G - lane) % G;
-        d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + kDW * lane + w);
+        // a neighbour's spill-over is taken from the far end of the warps: its chunk kDW r + i goes to warp kDW-1-i of
+        // block b + r, whose own chunks fill its warps from 0 upwards, so the two rarely meet in one warp
+        d = __ldcg(a.pipe_seg + ((size_t)L * G + src) * a.pipe_seg_cap + kDW * lane + (kDW - 1u - w));
     }
     unsigned long long events = 0ull;
     if (w < min(sh.chunks[L], a.pipe_seg_cap)) {
@@ -335,6 +323,32 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
     if (lane == 0) tot.events += events;
 }
 
+// The block's neuron spikes of the phase with parity `par` (collected in sh.pend by the update warps) are turned
+// into chunk descriptors, and with several ranks sent to the other ranks, by the input threads (`n_thr` of them,
+// this is thread `t`), one spike per thread. The row of a neuron is kept in sh.rows under the index of the update
+// thread that owns it: group g of four neurons belongs to chunk g / 32 = warp x gridDim.x + block.
+template <bool MULTI>
+__device__ __forceinline__ void queue_block_spikes(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t par,
+                                                   uint32_t slot, uint32_t t, uint32_t n_thr, uint32_t xk) {
+    const uint32_t n = min(sh.count[par], kPendP);
+    for (uint32_t k = t; k < n; k += n_thr) {
+        const uint32_t ent = sh.pend[par][k];
+        const uint32_t local = (ent & kSrcMask) - a.lo, grp = local >> 2;
+        const uint32_t thr = ((grp >> 5) / gridDim.x) * 32u + (grp & 31u);
+        const uint2 r = sh.rows[thr * kNeuronsPerThread + (local & 3u)];
+        if (MULTI) {
+            if (k < kXPipeSeg) {
+                for (uint32_t rk = 0; rk < a.n_ranks; ++rk)
+                    if (rk != a.rank)
+                        st_word(xp_ent(a.peers[rk] + a.xp_off, xk, a.rank, blockIdx.x, a.n_ranks, gridDim.x) + k, tag, ent);
+            } else {
+                atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+            }
+        }
+        push_chunks(a, sh, L, tag, r.x, r.y, wrap_slot(slot + (ent >> kSrcBits), a.ring_slots));
+    }
+}
+
 // Spike log of the phase whose list has parity q (stamps count from prev_start); one warp. Every block
 // logs into its own segment [blockIdx.x * log_seg_cap, ...) of the log arrays at a position the warp
 // carries in a register (`pos`, same on all lanes): no atomic, no round trip. The segments are laid end
@@ -352,6 +366,17 @@ __device__ __forceinline__ void write_log(const PersistArgs& a, PipeShared& sh, 
         }
     }
     pos = min(pos + n_rec, a.log_seg_cap);
+}
+
+__device__ __forceinline__ void log_previous_phase(const PersistArgs& a, PipeShared& sh, uint32_t lane, uint32_t q,
+                                                   unsigned long long prev_start, uint32_t& log_pos, DeliveryTotals& tot) {
+    const uint32_t n_rec = min(sh.count[q], kPendP);
+    if (a.log_stamp && n_rec) write_log(a, sh, lane, n_rec, q, prev_start, log_pos);
+    __syncwarp();
+    if (lane == 0) {
+        sh.count[q] = 0u;    // the update warps append to it again in the next phase
+        tot.spikes += n_rec;
+    }
 }
 
 template <bool THETA, bool IEXT, bool MULTI>
@@ -392,8 +417,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     const uint32_t my_group = ((threadIdx.x >> 5) * gridDim.x + blockIdx.x) * 32u + (threadIdx.x & 31u);
     const uint32_t i0 = my_group * kNeuronsPerThread;
     const bool mine = is_upd && my_group < n_groups;
-    const bool timer_u = a.profile && blockIdx.x == 0 && threadIdx.x == 0;
-    const bool timer_d = a.profile && blockIdx.x == 0 && threadIdx.x == kUT;
+    const bool timer_u = a.profile && threadIdx.x == 0;      // every block times itself; block 0's sums also go to the control block
+    const bool timer_d = a.profile && threadIdx.x == kUT;
 
     // clamp changes already in force at the first step of this launch
     uint32_t cgi = a.ce_group_begin;
@@ -468,6 +493,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
+            const unsigned long long t_warp = a.profile ? gtimer() : 0ull;
             if (IEXT && clamp_now) {
                 if (mine) nr.iex = ld4cg(a.st.i_ext + i0);
                 clamp_now = false;
@@ -480,14 +506,6 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     F4 in[kPorts];
 #pragma unroll
                     for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
-                    if ((a.tune & 2u) && (threadIdx.x & 7u) == 0u) {
-                        // the next step's slot (of the next phase when this is the phase's last step): deliveries may
-                        // still be adding to it in L2, which is where this brings its lines; one request per 128 bytes
-                        const float* nxt = a.ring + (size_t)wrap_slot(sl + 1u, S) * kPorts * a.n_pad + i0;
-#pragma unroll
-                        for (int pt = 0; pt < kPorts; ++pt)
-                            asm volatile("prefetch.global.L2 [%0];" ::"l"(nxt + (size_t)pt * a.n_pad));
-                    }
                     mask = nr.step(types, in);
                     if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
                     const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
@@ -518,6 +536,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                             const uint32_t ent = (j << kSrcBits) | (a.lo + i0 + jj);
                             if (pos < kPendP) sh.pend[par][pos] = ent;
                             else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+                            // with input warps in the block the spike is queued by them at the end of the phase
+                            // (queue_block_spikes): done here, by the one firing lane with the warp's state in
+                            // registers around it, it held the whole warp up for more than a microsecond
+                            if (a.input_warps) continue;
                             if (multi) {
                                 // the other ranks deliver this spike to their own targets: plain peer stores
                                 if (pos < kXPipeSeg) {
@@ -537,7 +559,12 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 sl = wrap_slot(sl + 1u, S);
             }
             // done with phase p; the next one needs the chunk warps of phase p finished everywhere (ring slots final)
+            if (a.input_warps) asm volatile("barrier.arrive 3, %0;" ::"r"(n_prod_threads) : "memory");   // this phase's spikes are in sh.pend
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
+            if (a.profile && (threadIdx.x & 31u) == 0u) {
+                const unsigned long long now = gtimer();
+                hist_add(a, 0u, now - t_warp);
+            }
             side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
                           threadIdx.x == 0, s + len < a.n_steps, sync_dead, (a.seq0 + p) & 3u, &sh.count[par], tag, multi);
             if (timer_u) {
@@ -557,9 +584,15 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         if (mine) nr.store(a.st, a.n_pad, i0);
         if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->step_base = step_base + a.n_steps;
         if (timer_u) {
-            a.ctl->t_update_ns += acc_work;
-            a.ctl->t_sync1_ns += acc_wait;
-            a.ctl->n_windows += p;
+            if (blockIdx.x == 0) {
+                a.ctl->t_update_ns += acc_work;
+                a.ctl->t_sync1_ns += acc_wait;
+                a.ctl->n_windows += p;
+            }
+            if (a.blk_prof) {
+                a.blk_prof[4 * blockIdx.x + 0] += acc_work - acc_wait;
+                a.blk_prof[4 * blockIdx.x + 1] += acc_wait;
+            }
         }
     } else {
         // ================= delivery warps
@@ -581,11 +614,17 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
+            const unsigned long long t_warp = a.profile ? gtimer() : 0ull;
             const uint32_t q = par ^ 1u;
             unsigned long long t_rows = 0ull;
             if (input_role) {
                 // this phase's input spikes, from the start of the phase
                 prepare_inputs(a, sh, L, tag, cc, start, slot, len, it, n_it, tot);
+                // the spike log of the previous phase, while the update warps are still at work
+                if (dwarp == log_warp && p > 0) log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
+                // then, once every update warp of the block has finished the phase, the block's own spikes
+                asm volatile("barrier.sync 3, %0;" ::"r"(n_prod_threads) : "memory");
+                queue_block_spikes<MULTI>(a, sh, L, tag, par, slot, it, n_it, (a.seq0 + p) & 3u);
             } else {
                 if (dtid == 0) sh.chunks[(p + 1u) % 3u] = 0u;   // the list of the NEXT phase was last read one phase ago
                 if (p > 0) {
@@ -603,20 +642,12 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     }
                 }
             }
-            // The spike log of the previous phase is kept off the chunk warps' path when there are input warps
-            // (they are done early). Otherwise chunk warp 0 has it.
-            if (dwarp == log_warp && p > 0) {
-                const uint32_t n_rec = min(sh.count[q], kPendP);
-                if (a.log_stamp && n_rec) write_log(a, sh, lane, n_rec, q, prev_start, log_pos);
-                __syncwarp();
-                if (lane == 0) {
-                    sh.count[q] = 0u;    // the update warps append to it again in the next phase
-                    tot.spikes += n_rec;
-                }
-            }
+            // Without input warps chunk warp 0 writes the spike log of the previous phase.
+            if (!a.input_warps && dwarp == 0u && p > 0) log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
             // input warps belong to the producing side (their chunks go into this phase's lists); the chunk warps'
             // next phase - and their last pass after the loop - needs the producing side of this phase finished
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
+            if (a.profile && lane == 0u) hist_add(a, input_role ? 1u : 2u, gtimer() - t_warp);
             if (input_role)
                 side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads, false,
                               s + len < a.n_steps, sync_dead);
@@ -656,9 +687,15 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             if (log_pos) atomicAdd(&a.ctl->log_count, log_pos);
         }
         if (timer_d) {
-            a.ctl->t_prop_ns += acc_work;
-            a.ctl->t_sync2_ns += acc_wait;
-            a.ctl->t_rows_ns += acc_rows;
+            if (blockIdx.x == 0) {
+                a.ctl->t_prop_ns += acc_work;
+                a.ctl->t_sync2_ns += acc_wait;
+                a.ctl->t_rows_ns += acc_rows;
+            }
+            if (a.blk_prof) {
+                a.blk_prof[4 * blockIdx.x + 2] += acc_work - acc_wait;
+                a.blk_prof[4 * blockIdx.x + 3] += acc_wait;
+            }
         }
         if (tot.events) atomicAdd(&a.ctl->n_events, tot.events);
         if (tot.inputs) atomicAdd(&a.ctl->n_input_spikes, tot.inputs);

@@ -311,6 +311,17 @@ class Engine(object):
         """Resume from a checkpoint written for the same network, partition and dt."""
         check(self._lib.bmtk_engine_load_state(self._h, str(path).encode()))
 
+    def block_profile(self):
+        """uint64[blocks, 4] {producing busy, producing wait, delivering busy, delivering wait} ns per block of the
+        pipelined kernel since the last call (option phase_timers); empty when the kernel is not in use."""
+        n = C.c_uint64()
+        check(self._lib.bmtk_engine_block_profile(self._h, 0, None, C.byref(n)))
+        out = np.zeros((n.value + 24, 4), dtype=np.uint64)
+        if n.value:
+            check(self._lib.bmtk_engine_block_profile(self._h, n.value + 24, _ptr(out), C.byref(n)))
+        self.warp_histograms = out[n.value:].reshape(3, 32)     # update / input / chunk warps, bins of 250 ns
+        return out[:n.value]
+
     def mark(self, slot):
         """Records a CUDA event on the engine's stream in slot 0..7."""
         check(self._lib.bmtk_engine_mark(self._h, int(slot)))

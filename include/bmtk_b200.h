@@ -283,6 +283,16 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path);
  * event; bench and microbench report the delivery kernels against it. */
 int bmtk_probe_scatter_reductions(int device, uint64_t n_cells, uint64_t n_ops, int repeats, double* ms_per_pass);
 
+/* Per-block phase profile of the pipelined stepping kernel (no counterpart in the reference). With option
+ * phase_timers = 1 every block sums, with the device timer, how long its producing side (update and input warps)
+ * and its delivering side (chunk warps) were busy and how long each waited in the hand-over at the end of a phase.
+ * out4 receives 4 values per block {producing busy, producing wait, delivering busy, delivering wait} in ns since
+ * the last call and the sums are cleared; n_blocks receives the block count (0 when the kernel is not in use; pass
+ * out4 = NULL to ask for it). Behind the blocks' values follow three histograms of 32 bins of 250 ns (96 values): how
+ * long after the start of a phase a warp reached the hand-over, for update, input and chunk warps; cap_blocks must
+ * therefore be at least n_blocks + 24. Shows whether a phase is long because one block is slow or because the hand-over is. */
+int bmtk_engine_block_profile(bmtk_engine* e, uint64_t cap_blocks, uint64_t* out4, uint64_t* n_blocks);
+
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
  * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
  * and returns the device time between two marks. */
