@@ -393,6 +393,21 @@ def main():
         if pipelined:
             phases['phase_us'] = pu * 1e-3           # both sides span the whole phase
             phases['row_streaming_us'] = eng.counter('phase_rows_ns') / nw * 1e-3
+            if world > 1:
+                # of the row streaming time of block 0's first chunk warp: waiting for the other ranks' count words of
+                # the phase, then fetching their spikes and streaming those rows (the rest is this rank's own chunks)
+                phases['remote_count_wait_us'] = eng.counter('phase_remote_wait_ns') / nw * 1e-3
+                phases['remote_rows_us'] = eng.counter('phase_remote_rows_ns') / nw * 1e-3
+                phases['local_rows_us'] = phases['row_streaming_us'] - phases['remote_count_wait_us'] - phases['remote_rows_us']
+
+    # ---------------- latency of the exchange primitive between ranks 0 and 1 (what a phase cannot go below)
+    if world > 1 and args.exchange == 'p2p' and phases is not None:
+        barrier()
+        if rank < 2:
+            lat = eng.p2p_pingpong(1 - rank, rank == 0, 2000)
+            if rank == 0:
+                phases['peer_word_one_way_us'] = lat * 1e-3
+        barrier()
 
     # ---------------- profiled pass: per-launch CUDA events around both kernels
     prof_steps = min(steps_per_bench_step, 800)

@@ -83,6 +83,7 @@ _SIGNATURES = {
     'bmtk_probe_scatter_reductions': (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_int, C.POINTER(C.c_double)]),
     'bmtk_engine_save_state': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_load_state': (C.c_int, [_P, C.c_char_p]),
+    'bmtk_engine_p2p_pingpong': (C.c_int, [_P, C.c_int, C.c_int, C.c_uint32, C.POINTER(C.c_double)]),
     'bmtk_engine_block_profile': (C.c_int, [_P, C.c_uint64, _P, C.POINTER(C.c_uint64)]),
     'bmtk_engine_mark': (C.c_int, [_P, C.c_int]),
     'bmtk_engine_elapsed_ms': (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),

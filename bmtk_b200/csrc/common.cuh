@@ -63,7 +63,9 @@ struct Ctl {
     unsigned long long t_update_ns, t_prop_ns, n_windows;
     unsigned long long t_sync1_ns, t_sync2_ns;   // of which: waiting in the two grid barriers (block 0's view)
     unsigned long long t_rows_ns;                // pipelined kernel: of the delivery warps' busy time, streaming rows
-    unsigned long long pad2[3];
+    unsigned long long t_remote_wait_ns;         // pipelined kernel, several ranks: of t_rows_ns, waiting for the other ranks' count words
+    unsigned long long t_remote_rows_ns;         // ... and fetching + streaming the rows of their spikes
+    unsigned long long pad2[1];
 };
 
 // Trial batching: T independent copies ("trials") of one network share its CSR. Cell c of trial t has

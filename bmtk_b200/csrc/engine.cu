@@ -341,6 +341,7 @@ struct bmtk_engine {
     bool peers_pipe_ok = true;   // every rank can run the pipelined kernel
     bool any_iext = false;       // some rank has clamp changes (the pipelined exchange has no clamp schedule)
     uint32_t xchg_seq = 0;                      // windows exchanged so far
+    uint32_t pingpong_calls = 0;
     uint32_t xp_off = 0;                        // pipelined kernel: start of its exchange area (64-bit words)
     int32_t* d_probe_slot = nullptr;
     unsigned long long* d_ce_group_step = nullptr;
@@ -348,7 +349,7 @@ struct bmtk_engine {
     std::vector<uint64_t> ce_group_step;
     size_t ce_group_next = 0;
     double phase_update_ns = 0, phase_prop_ns = 0, phase_sync1_ns = 0, phase_sync2_ns = 0;
-    double phase_rows_ns = 0;
+    double phase_rows_ns = 0, phase_remote_wait_ns = 0, phase_remote_rows_ns = 0;
     double drain_wait_ns = 0, drain_sort_ns = 0;   // host clock: waiting for the chunk's kernels; sorting + copying its spike log
     uint64_t phase_windows = 0;
 
@@ -676,6 +677,8 @@ static int drain(bmtk_engine* e) {
         e->phase_sync1_ns += (double)h.t_sync1_ns;
         e->phase_sync2_ns += (double)h.t_sync2_ns;
         e->phase_rows_ns += (double)h.t_rows_ns;
+        e->phase_remote_wait_ns += (double)h.t_remote_wait_ns;
+        e->phase_remote_rows_ns += (double)h.t_remote_rows_ns;
         CU(cudaMemsetAsync(&e->d_ctl->t_update_ns, 0, sizeof(Ctl) - offsetof(Ctl, t_update_ns), e->stream));
     }
     if (h.step_base != e->step)
@@ -861,9 +864,9 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
             const uint32_t free_warps = pipelined_warps() - e->pipe_upd_warps;
             uint32_t iw = 0;
             if (e->has_poisson) iw = (uint32_t)((e->n_virtual / e->pipe_blocks + 63) / 64);
-            if (e->d_in_ptr) iw = std::max(iw, 1u);
-            if (e->has_poisson) iw = std::max(iw, 1u);
-            a.input_warps = std::min(iw, free_warps / 2);
+            // always at least one: the input warps also queue the block's own spikes and write the spike log
+            iw = std::max(iw, 1u);
+            a.input_warps = std::max(1u, std::min(iw, free_warps / 2));
         }
         CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
     } else {
@@ -1440,8 +1443,8 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                 if (e->pipe_ok) {
                     CU(cudaMalloc(&e->d_pipe_seg, sizeof(uint4) * 3 * (size_t)pb * kPipeSegCap));
                     CU(cudaMalloc(&e->d_pipe_sync, 32));
-                    CU(cudaMalloc(&e->d_blk_prof, 32 * (size_t)pb + 8 * 96));
-                    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)pb + 8 * 96));
+                    CU(cudaMalloc(&e->d_blk_prof, 32 * (size_t)pb + 8 * 160 + 128 * (size_t)pb));
+                    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)pb + 8 * 160 + 128 * (size_t)pb));
                     CU(cudaMalloc(&e->d_log_seg_cnt, 4 * (size_t)pb));
                     CU(cudaMemset(e->d_log_seg_cnt, 0, 4 * (size_t)pb));
                     // a descriptor is valid by its tag (first step of its phase + 1): none is at rest
@@ -1829,6 +1832,53 @@ int bmtk_engine_p2p_connect(bmtk_engine* e, const void* handles) {
     return BMTK_OK;
 }
 
+// One thread per side bounces a tagged 8-byte word between two ranks' exchange buffers `rounds` times: plain peer
+// store, polling load on the own buffer, the same primitives the stepping kernels exchange spikes with.
+__global__ void pingpong_kernel(unsigned long long* my_inbox, unsigned long long* peer_inbox, int initiator, uint32_t rounds,
+                                uint32_t base, unsigned long long* out_ns, uint32_t* timed_out) {
+    unsigned long long t0 = 0ull;
+    for (uint32_t i = 1; i <= rounds + 8u; ++i) {      // 8 untimed rounds first
+        const uint32_t tag = base + i;
+        if (i == 9u) t0 = gtimer();
+        if (initiator) st_word(peer_inbox, tag, i);
+        unsigned int spins = 0;
+        while ((uint32_t)(ld_word(my_inbox) >> 32) != tag) {
+            if (++spins > 40000000u) {   // a few seconds: the peer never answered
+                *timed_out = 1u;
+                return;
+            }
+        }
+        if (!initiator) st_word(peer_inbox, tag, i);
+    }
+    *out_ns = gtimer() - t0;
+}
+
+int bmtk_engine_p2p_pingpong(bmtk_engine* e, int peer_rank, int initiator, uint32_t rounds, double* one_way_ns) {
+    if (!e || !e->finalized || !one_way_ns) return fail(BMTK_E_INVALID, "p2p_pingpong: engine missing, not finalized, or NULL");
+    if (!e->p2p_ready || peer_rank < 0 || peer_rank >= e->n_ranks || peer_rank == e->rank || rounds < 1)
+        return fail(BMTK_E_INVALID, "p2p_pingpong: peers are not connected, or bad peer / round count");
+    int rc = set_device(e);
+    if (rc) return rc;
+    unsigned long long* d_out = nullptr;
+    CU(cudaMalloc(&d_out, 16));
+    CU(cudaMemsetAsync(d_out, 0, 16, e->stream));
+    // words 13 (ping) and 14 (pong) of the layout descriptor at the head of an exchange buffer are free for this
+    unsigned long long* mine = e->d_xchg + (initiator ? 14 : 13);
+    unsigned long long* theirs = e->xchg_peers[peer_rank] - kXDescWords + (initiator ? 13 : 14);
+    e->pingpong_calls += 1;
+    pingpong_kernel<<<1, 1, 0, e->stream>>>(mine, theirs, initiator, rounds, e->pingpong_calls << 20, d_out,
+                                            reinterpret_cast<uint32_t*>(d_out + 1));
+    unsigned long long h[2] = {0, 0};
+    cudaError_t ce = cudaGetLastError();
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(h, d_out, 16, cudaMemcpyDeviceToHost, e->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+    cudaFree(d_out);
+    if (ce != cudaSuccess) return fail(BMTK_E_CUDA, "p2p_pingpong: %s", cudaGetErrorString(ce));
+    if ((uint32_t)h[1]) return fail(BMTK_E_COMM, "p2p_pingpong: rank %d did not answer within a few seconds", peer_rank);
+    *one_way_ns = (double)h[0] / (2.0 * rounds);
+    return BMTK_OK;
+}
+
 int bmtk_engine_p2p_buffer(bmtk_engine* e, void** d_buffer) {
     if (!e || !e->finalized || !d_buffer) return fail(BMTK_E_INVALID, "p2p_buffer: engine missing, not finalized, or NULL");
     if (!e->d_xchg) return fail(BMTK_E_UNSUPPORTED, "p2p_buffer: no exchange buffer (one rank, or cooperative launch unavailable)");
@@ -1931,13 +1981,13 @@ int bmtk_engine_block_profile(bmtk_engine* e, uint64_t cap_blocks, uint64_t* out
     if (!e || !e->finalized || !n_blocks) return fail(BMTK_E_INVALID, "block_profile: engine missing, not finalized, or NULL");
     *n_blocks = e->d_blk_prof ? (uint64_t)e->pipe_blocks : 0;
     if (!e->d_blk_prof || !out4) return BMTK_OK;
-    if (cap_blocks < *n_blocks + 24) return fail(BMTK_E_INVALID, "block_profile: room for %llu blocks, %llu needed",
+    if (cap_blocks < *n_blocks * 5 + 40) return fail(BMTK_E_INVALID, "block_profile: room for %llu blocks, %llu needed",
                                             (unsigned long long)cap_blocks, (unsigned long long)*n_blocks);
     int rc = set_device(e);
     if (rc) return rc;
     CU(cudaStreamSynchronize(e->stream));
-    CU(cudaMemcpy(out4, e->d_blk_prof, 32 * (size_t)e->pipe_blocks + 8 * 96, cudaMemcpyDeviceToHost));
-    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)e->pipe_blocks + 8 * 96));
+    CU(cudaMemcpy(out4, e->d_blk_prof, 32 * (size_t)e->pipe_blocks + 8 * 160 + 128 * (size_t)e->pipe_blocks, cudaMemcpyDeviceToHost));
+    CU(cudaMemset(e->d_blk_prof, 0, 32 * (size_t)e->pipe_blocks + 8 * 160 + 128 * (size_t)e->pipe_blocks));
     return BMTK_OK;
 }
 
@@ -1985,6 +2035,8 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "drain_wait_ns") *out = (uint64_t)e->drain_wait_ns;
     else if (k == "drain_sort_ns") *out = (uint64_t)e->drain_sort_ns;
     else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
+    else if (k == "phase_remote_wait_ns") *out = (uint64_t)e->phase_remote_wait_ns;
+    else if (k == "phase_remote_rows_ns") *out = (uint64_t)e->phase_remote_rows_ns;
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;

@@ -58,6 +58,11 @@ struct __align__(16) PipeShared {
 };
 static_assert(sizeof(PipeShared) % 16 == 0, "the type table behind it is read with 128-bit loads");
 
+// Warps of a block that stream chunks: all but the update and input warps and, with several ranks, the sender warp.
+__device__ __forceinline__ uint32_t chunk_warps(const PersistArgs& a) {
+    return kWarps - a.upd_warps - a.input_warps - (a.n_ranks > 1u ? 1u : 0u);
+}
+
 __device__ __forceinline__ uint32_t wrap_slot(uint32_t slot, uint32_t n) { return slot >= n ? slot - n : slot; }
 
 // Adds the CSR row [begin, begin + len), emitted at ring slot slot0, to this block's segment of list L.
@@ -66,7 +71,7 @@ __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh
     const uint32_t n = (len + kChunk - 1) / kChunk;
     if (n == 0) return;
     const uint32_t pos = atomicAdd(&sh.chunks[L], n);
-    const uint32_t kDW = kWarps - a.upd_warps - a.input_warps;   // warps that stream chunks
+    const uint32_t kDW = chunk_warps(a);
     uint4* seg = a.pipe_seg + ((size_t)L * gridDim.x + blockIdx.x) * a.pipe_seg_cap;
     for (uint32_t c = 0; c < n; ++c) {
         const uint4 d = make_uint4(begin + c * kChunk, min(kChunk, len - c * kChunk), slot0, tag);
@@ -94,22 +99,13 @@ constexpr unsigned int kSyncSpins = 32000000u;   // far longer than the bounded 
 // the barrier is cumulative: it covers the stores and reductions of all threads that arrived.
 template <bool MULTI>
 __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mine, const uint32_t* other, uint32_t target,
-                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead,
-                                              uint32_t xk = 0, const uint32_t* x_count = nullptr, uint32_t x_tag = 0,
-                                              bool x_publish = false) {
+                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead) {
     // barrier.sync, not bar.sync (= barrier.sync.aligned): the leader reaches the second barrier long after the
     // other lanes of its warp
     asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
     if (leader) {
         // release: cumulative over what the threads that arrived at the barrier have written (a full
         // fence here would also hold up the other role's warps, which are in the middle of their loads)
-        if (MULTI && x_publish) {
-            // several ranks, producing side: this block's spike count of the phase goes to block b of every
-            // other rank as one tagged word (the spikes went out the same way); no fence crosses the link
-            const uint32_t n_sent = min(*reinterpret_cast<const volatile uint32_t*>(x_count), kXPipeSeg);   // final: read after the barrier
-            for (uint32_t r = 0; r < a.n_ranks; ++r)
-                if (r != a.rank) st_word(xp_cnt(a.peers[r] + a.xp_off, xk, a.rank, blockIdx.x), x_tag, n_sent);
-        }
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
         if (wait && !dead) {
             // plain polling loads (an acquire load per poll would invalidate the SM's L1 under the other
@@ -139,6 +135,8 @@ __device__ __forceinline__ void hist_add(const PersistArgs& a, uint32_t role, un
 
 struct DeliveryTotals {
     unsigned long long events, inputs, spikes;
+    unsigned long long remote_wait_ns, remote_rows_ns;   // option phase_timers, several ranks: this warp's time waiting for the
+                                                         // other ranks' count words / fetching and streaming their spikes' rows
 };
 
 // Input spikes of the phase [start, start + len) whose first step uses ring slot `slot`: Poisson
@@ -221,7 +219,7 @@ __device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d
 // chunks beyond kDW * kSpill. Called by whole warps.
 __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t w,
                                              uint32_t lane, DeliveryTotals& tot) {
-    const uint32_t G = gridDim.x, kDW = kWarps - a.upd_warps - a.input_warps;   // warps that stream chunks
+    const uint32_t G = gridDim.x, kDW = chunk_warps(a);
     // the neighbours' descriptors are requested first, then this block's own chunk (descriptor in shared
     // memory) is streamed while they are on their way
     uint4 d = make_uint4(0u, 0u, 0u, 0u);
@@ -271,6 +269,7 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
                                                uint32_t w, uint32_t n_cw, uint32_t lane, DeliveryTotals& tot, bool& dead) {
     unsigned long long events = 0ull;
     uint32_t my_n = 0;
+    const unsigned long long t_in = a.profile ? gtimer() : 0ull;
     if (lane < a.n_ranks && lane != a.rank && !dead) {
         const u64* p = xp_cnt(xp, k, lane, blockIdx.x);
         unsigned int spins = 0;
@@ -286,6 +285,7 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
         if ((uint32_t)(cw >> 32) == tag) my_n = min((uint32_t)cw, kXPipeSeg);
     }
     dead = __any_sync(0xffffffffu, dead);
+    const unsigned long long t_counts = a.profile ? gtimer() : 0ull;
     // exclusive prefix of the ranks' counts over the lanes
     uint32_t incl = my_n;
 #pragma unroll
@@ -295,7 +295,8 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
     }
     const uint32_t my_off = incl - my_n;
     const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    for (uint32_t j = w; j < total; j += n_cw) {
+    // (dealt from the LAST chunk warp downwards: the block's own chunks fill the warps from the first upwards)
+    for (uint32_t j = n_cw - 1u - w; j < total; j += n_cw) {
         const uint32_t owner = __ballot_sync(0xffffffffu, my_n != 0u && my_off <= j && j < my_off + my_n);
         const int r = __ffs(owner) - 1;   // exactly one lane holds j
         const uint32_t i = j - __shfl_sync(0xffffffffu, my_off, r);
@@ -321,30 +322,23 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
             stream_chunk(a, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
     }
     if (lane == 0) tot.events += events;
+    if (a.profile && lane == 0) {
+        tot.remote_wait_ns += t_counts - t_in;
+        tot.remote_rows_ns += gtimer() - t_counts;
+    }
 }
 
 // The block's neuron spikes of the phase with parity `par` (collected in sh.pend by the update warps) are turned
-// into chunk descriptors, and with several ranks sent to the other ranks, by the input threads (`n_thr` of them,
-// this is thread `t`), one spike per thread. The row of a neuron is kept in sh.rows under the index of the update
+// into chunk descriptors by the input threads (`n_thr` of them, this is thread `t`), one spike per thread. The row of a neuron is kept in sh.rows under the index of the update
 // thread that owns it: group g of four neurons belongs to chunk g / 32 = warp x gridDim.x + block.
-template <bool MULTI>
 __device__ __forceinline__ void queue_block_spikes(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t par,
-                                                   uint32_t slot, uint32_t t, uint32_t n_thr, uint32_t xk) {
+                                                   uint32_t slot, uint32_t t, uint32_t n_thr) {
     const uint32_t n = min(sh.count[par], kPendP);
     for (uint32_t k = t; k < n; k += n_thr) {
         const uint32_t ent = sh.pend[par][k];
         const uint32_t local = (ent & kSrcMask) - a.lo, grp = local >> 2;
         const uint32_t thr = ((grp >> 5) / gridDim.x) * 32u + (grp & 31u);
         const uint2 r = sh.rows[thr * kNeuronsPerThread + (local & 3u)];
-        if (MULTI) {
-            if (k < kXPipeSeg) {
-                for (uint32_t rk = 0; rk < a.n_ranks; ++rk)
-                    if (rk != a.rank)
-                        st_word(xp_ent(a.peers[rk] + a.xp_off, xk, a.rank, blockIdx.x, a.n_ranks, gridDim.x) + k, tag, ent);
-            } else {
-                atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
-            }
-        }
         push_chunks(a, sh, L, tag, r.x, r.y, wrap_slot(slot + (ent >> kSrcBits), a.ring_slots));
     }
 }
@@ -399,8 +393,12 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     const TypeConsts* types = use_smem ? s_types : a.types;
 
     const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
-    const uint32_t kCW = kDW - a.input_warps;   // delivery warps that stream chunks; the others prepare input spikes
+    // delivery warps: kCW stream chunks, then the input warps, then (several ranks) the sender warp
+    const uint32_t kCW = kDW - a.input_warps - (MULTI ? 1u : 0u);
     const uint32_t n_prod_threads = kUT + 32u * a.input_warps, n_cons_threads = 32u * kCW;
+    // named barrier 3: the update warps arrive when their phase is done; the input warps (which queue the block's
+    // spikes) and the sender warp wait on it
+    const uint32_t n_bar3 = n_prod_threads + (MULTI ? 32u : 0u);
     constexpr bool multi = MULTI;   // several ranks: a separate instantiation keeps the exchange out of the one-rank kernel
     uint32_t* const cnt_prod = a.pipe_sync;        // [4] blocks of this rank whose update + input warps finished phase p (index p mod 4)
     uint32_t* const cnt_cons = a.pipe_sync + 4;    // [4] blocks of this rank whose chunk warps finished phase p
@@ -515,6 +513,14 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                         if (nz) st4(ring + (size_t)pt * a.n_pad, zero);   // most cells are still zero
                     }
                 }
+                if (a.profile && j + 1 == len) {
+                    const bool any = __any_sync(0xffffffffu, mask != 0u);
+                    if ((threadIdx.x & 31u) == 0u) {
+                        const unsigned long long dt_ = gtimer() - t_warp;
+                        hist_add(a, any ? 4u : 3u, dt_);
+                        if (a.blk_prof) a.blk_prof[4ull * gridDim.x + 160ull + 16ull * blockIdx.x + (threadIdx.x >> 5)] += dt_;
+                    }
+                }
                 if (a.probe_slot) {
                     if (pctr == 0) {
                         if (mine && sample < a.trace_cap) {
@@ -536,37 +542,23 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                             const uint32_t ent = (j << kSrcBits) | (a.lo + i0 + jj);
                             if (pos < kPendP) sh.pend[par][pos] = ent;
                             else atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
-                            // with input warps in the block the spike is queued by them at the end of the phase
-                            // (queue_block_spikes): done here, by the one firing lane with the warp's state in
-                            // registers around it, it held the whole warp up for more than a microsecond
-                            if (a.input_warps) continue;
-                            if (multi) {
-                                // the other ranks deliver this spike to their own targets: plain peer stores
-                                if (pos < kXPipeSeg) {
-                                    for (uint32_t r = 0; r < a.n_ranks; ++r)
-                                        if (r != a.rank)
-                                            st_word(xp_ent(a.peers[r] + a.xp_off, (a.seq0 + p) & 3u, a.rank, blockIdx.x, a.n_ranks, gridDim.x) + pos,
-                                                    tag, ent);
-                                } else {
-                                    atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
-                                }
-                            }
-                            const uint2 r = sh.rows[threadIdx.x * kNeuronsPerThread + jj];
-                            push_chunks(a, sh, L, tag, r.x, r.y, sl);
+                            // the input warps queue the spike at the end of the phase (queue_block_spikes): done here, by
+                            // the one firing lane with the warp's state in registers around it, it cost the whole warp more
+                            // than a microsecond (registers spilled around a path that is rarely taken miss every cache)
                         }
                     }
                 }
                 sl = wrap_slot(sl + 1u, S);
             }
             // done with phase p; the next one needs the chunk warps of phase p finished everywhere (ring slots final)
-            if (a.input_warps) asm volatile("barrier.arrive 3, %0;" ::"r"(n_prod_threads) : "memory");   // this phase's spikes are in sh.pend
+            asm volatile("barrier.arrive 3, %0;" ::"r"(n_bar3) : "memory");   // this phase's spikes are in sh.pend
             const unsigned long long t_work = timer_u ? gtimer() : 0ull;
             if (a.profile && (threadIdx.x & 31u) == 0u) {
                 const unsigned long long now = gtimer();
                 hist_add(a, 0u, now - t_warp);
             }
             side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
-                          threadIdx.x == 0, s + len < a.n_steps, sync_dead, (a.seq0 + p) & 3u, &sh.count[par], tag, multi);
+                          threadIdx.x == 0, s + len < a.n_steps, sync_dead);
             if (timer_u) {
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
@@ -597,13 +589,14 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     } else {
         // ================= delivery warps
         const uint32_t lane = dtid & 31u, dwarp = dtid >> 5;
-        const bool input_role = dwarp >= kCW;
-        const uint32_t log_warp = a.input_warps ? kCW : 0u;   // the first input warp, else chunk warp 0
+        const bool input_role = dwarp >= kCW && dwarp < kCW + a.input_warps;
+        const bool sender_role = MULTI && dwarp == kCW + a.input_warps;
+        const uint32_t log_warp = kCW;   // the first input warp (a block always has one)
         uint32_t log_pos = 0;   // entries this block has logged in this launch
         const uint32_t it = dtid - 32u * kCW, n_it = 32u * a.input_warps;   // input thread index / count
         unsigned long long prev_start = step_base;
         uint32_t prev_slot = slot;   // ring slot of the previous phase's first step
-        DeliveryTotals tot = {0ull, 0ull, 0ull};
+        DeliveryTotals tot = {0ull, 0ull, 0ull, 0ull, 0ull};
         CachedCell cc = {make_uint4(0u, 0u, 0u, 0u), 0u, 0u};
         if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual) {
             const uint32_t v0 = it * gridDim.x + blockIdx.x;
@@ -611,6 +604,34 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             const unsigned long long b0 = a.rowptr[a.n_global + v0], b1 = a.rowptr[a.n_global + v0 + 1];
             cc.begin = (uint32_t)b0;
             cc.len = (uint32_t)(b1 - b0);
+        }
+        if (sender_role) {
+            // ---- several ranks: this warp alone talks to the other GPUs. It takes the block's spikes of a phase as soon
+            // as the update warps are done with it and stores them, then the tagged count word, into the exchange buffer
+            // of every other rank (plain peer stores, fire and forget). It joins neither hand-over: the release with
+            // which a side publishes its phase waits for the writes of the threads that met at the side's barrier, and
+            // a write that has to cross NVLink and be acknowledged would hold every phase up by a round trip.
+            while (s < a.n_steps) {
+                PIPE_PHASE_BEGIN()
+                asm volatile("barrier.sync 3, %0;" ::"r"(n_bar3) : "memory");
+                const uint32_t n_all = min(sh.count[par], kPendP), n_send = min(n_all, kXPipeSeg);
+                if (n_all > kXPipeSeg && lane == 0) atomicOr(&a.ctl->error_flags, kErrSpikeListFull);
+                const uint32_t xk = (a.seq0 + p) & 3u;
+                for (uint32_t k = lane; k < n_send; k += 32u) {
+                    const uint32_t ent = sh.pend[par][k];
+                    for (uint32_t rk = 0; rk < a.n_ranks; ++rk)
+                        if (rk != a.rank)
+                            st_word(xp_ent(a.peers[rk] + a.xp_off, xk, a.rank, blockIdx.x, a.n_ranks, gridDim.x) + k, tag, ent);
+                }
+                __syncwarp();
+                if (lane < a.n_ranks && lane != a.rank) st_word(xp_cnt(a.peers[lane] + a.xp_off, xk, a.rank, blockIdx.x), tag, n_send);
+                // the list of this phase is written to the spike log and emptied one phase from now: not before this
+                if (s + len < a.n_steps) asm volatile("barrier.arrive 4, 64;" ::: "memory");
+                slot = (uint32_t)((slot + len) % S);
+                s += len;
+                ++p;
+            }
+            return;
         }
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
@@ -621,10 +642,14 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 // this phase's input spikes, from the start of the phase
                 prepare_inputs(a, sh, L, tag, cc, start, slot, len, it, n_it, tot);
                 // the spike log of the previous phase, while the update warps are still at work
-                if (dwarp == log_warp && p > 0) log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
+                if (dwarp == log_warp && p > 0) {
+                    // (the sender warp reads the same list: it has arrived here once it is done with it)
+                    if (MULTI) asm volatile("barrier.sync 4, 64;" ::: "memory");
+                    log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
+                }
                 // then, once every update warp of the block has finished the phase, the block's own spikes
-                asm volatile("barrier.sync 3, %0;" ::"r"(n_prod_threads) : "memory");
-                queue_block_spikes<MULTI>(a, sh, L, tag, par, slot, it, n_it, (a.seq0 + p) & 3u);
+                asm volatile("barrier.sync 3, %0;" ::"r"(n_bar3) : "memory");
+                queue_block_spikes(a, sh, L, tag, par, slot, it, n_it);
             } else {
                 if (dtid == 0) sh.chunks[(p + 1u) % 3u] = 0u;   // the list of the NEXT phase was last read one phase ago
                 if (p > 0) {
@@ -642,8 +667,6 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                     }
                 }
             }
-            // Without input warps chunk warp 0 writes the spike log of the previous phase.
-            if (!a.input_warps && dwarp == 0u && p > 0) log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
             // input warps belong to the producing side (their chunks go into this phase's lists); the chunk warps'
             // next phase - and their last pass after the loop - needs the producing side of this phase finished
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
@@ -691,6 +714,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 a.ctl->t_prop_ns += acc_work;
                 a.ctl->t_sync2_ns += acc_wait;
                 a.ctl->t_rows_ns += acc_rows;
+                a.ctl->t_remote_wait_ns += tot.remote_wait_ns;
+                a.ctl->t_remote_rows_ns += tot.remote_rows_ns;
             }
             if (a.blk_prof) {
                 a.blk_prof[4 * blockIdx.x + 2] += acc_work - acc_wait;

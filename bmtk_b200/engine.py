@@ -311,15 +311,23 @@ class Engine(object):
         """Resume from a checkpoint written for the same network, partition and dt."""
         check(self._lib.bmtk_engine_load_state(self._h, str(path).encode()))
 
+    def p2p_pingpong(self, peer_rank, initiator, rounds=2000):
+        """One-way latency (ns) of a tagged 8-byte word between this rank and `peer_rank` over peer memory; both
+        ranks call it together, one as initiator."""
+        ns = C.c_double()
+        check(self._lib.bmtk_engine_p2p_pingpong(self._h, int(peer_rank), int(bool(initiator)), int(rounds), C.byref(ns)))
+        return ns.value
+
     def block_profile(self):
         """uint64[blocks, 4] {producing busy, producing wait, delivering busy, delivering wait} ns per block of the
         pipelined kernel since the last call (option phase_timers); empty when the kernel is not in use."""
         n = C.c_uint64()
         check(self._lib.bmtk_engine_block_profile(self._h, 0, None, C.byref(n)))
-        out = np.zeros((n.value + 24, 4), dtype=np.uint64)
+        out = np.zeros((n.value * 5 + 40, 4), dtype=np.uint64)
         if n.value:
-            check(self._lib.bmtk_engine_block_profile(self._h, n.value + 24, _ptr(out), C.byref(n)))
-        self.warp_histograms = out[n.value:].reshape(3, 32)     # update / input / chunk warps, bins of 250 ns
+            check(self._lib.bmtk_engine_block_profile(self._h, n.value * 5 + 40, _ptr(out), C.byref(n)))
+        self.update_warp_ns = out[n.value + 40:].reshape(n.value, 16)   # per block and update warp: time to the end of its last step
+        self.warp_histograms = out[n.value:n.value + 40].reshape(5, 32)     # bins of 250 ns: update, input, chunk warps at the hand-over; update warps after the step, without / with a spike
         return out[:n.value]
 
     def mark(self, slot):

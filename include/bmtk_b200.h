@@ -283,14 +283,23 @@ int bmtk_engine_load_state(bmtk_engine* e, const char* path);
  * event; bench and microbench report the delivery kernels against it. */
 int bmtk_probe_scatter_reductions(int device, uint64_t n_cells, uint64_t n_ops, int repeats, double* ms_per_pass);
 
+/* One-way latency of the spike exchange's primitive between two connected ranks (no counterpart in the reference): a
+ * single thread on each of the two GPUs bounces a tagged 8-byte word `rounds` times with a plain peer store and a
+ * polling load, as the stepping kernels do. Both ranks call it at the same time, one with initiator = 1 and one with
+ * initiator = 0, each naming the other as peer_rank; one_way_ns receives half the mean round trip (meaningful on the
+ * initiator). Every wait is bounded (a few seconds), after which the call returns BMTK_E_COMM. A phase of the
+ * stepping kernel with several ranks cannot be shorter than this latency plus the work that depends on it. */
+int bmtk_engine_p2p_pingpong(bmtk_engine* e, int peer_rank, int initiator, uint32_t rounds, double* one_way_ns);
+
 /* Per-block phase profile of the pipelined stepping kernel (no counterpart in the reference). With option
  * phase_timers = 1 every block sums, with the device timer, how long its producing side (update and input warps)
  * and its delivering side (chunk warps) were busy and how long each waited in the hand-over at the end of a phase.
  * out4 receives 4 values per block {producing busy, producing wait, delivering busy, delivering wait} in ns since
  * the last call and the sums are cleared; n_blocks receives the block count (0 when the kernel is not in use; pass
- * out4 = NULL to ask for it). Behind the blocks' values follow three histograms of 32 bins of 250 ns (96 values): how
- * long after the start of a phase a warp reached the hand-over, for update, input and chunk warps; cap_blocks must
- * therefore be at least n_blocks + 24. Shows whether a phase is long because one block is slow or because the hand-over is. */
+ * out4 = NULL to ask for it). Behind the blocks' values follow five histograms of 32 bins of 250 ns (160 values): how
+ * long after the start of a phase a warp reached the hand-over, for update, input and chunk warps, and how long after it
+ * an update warp had finished its last step, for warps without and with a spike; cap_blocks must therefore be at least
+ * n_blocks + 40. Shows whether a phase is long because one block is slow or because the hand-over is. */
 int bmtk_engine_block_profile(bmtk_engine* e, uint64_t cap_blocks, uint64_t* out4, uint64_t* n_blocks);
 
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
