@@ -13,6 +13,9 @@ MAX_PORTS = 4
 MODEL_GLIF_PSC, MODEL_IAF_PSC_ALPHA, MODEL_IAF_PSC_DELTA = 0, 1, 2
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'lib', 'libbmtk_b200.so')
 
+# recorder variables (BMTK_VAR_*), by the names NEST's glif_psc gives its recordables
+RECORDABLES = {'V_m': 0, 'I_syn': 1, 'ASCurrents_sum': 2, 'threshold': 3, 'threshold_spike': 4, 'threshold_voltage': 5, 'I': 6}
+
 OK, E_INVALID, E_CUDA, E_OVERFLOW, E_UNSUPPORTED, E_COMM, E_DELAY = 0, -1, -2, -3, -4, -5, -6
 
 
@@ -57,6 +60,7 @@ _SIGNATURES = {
     'bmtk_engine_set_clamp_events': (C.c_int, [_P, C.c_uint64, _P, _P, _P]),
     'bmtk_engine_record_spikes': (C.c_int, [_P, C.c_int]),
     'bmtk_engine_record_vm': (C.c_int, [_P, C.c_uint64, _P, C.c_uint32]),
+    'bmtk_engine_record_state': (C.c_int, [_P, C.c_uint64, _P, C.c_uint32, C.c_int32, _P]),
     'bmtk_engine_set_option': (C.c_int, [_P, C.c_char_p, C.c_int64]),
     'bmtk_comm_unique_id': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_comm_init': (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_char_p]),

@@ -42,7 +42,7 @@ struct __align__(16) TypeConsts {
     // bit0 spike-dependent threshold, bit1 adapting threshold, bit2 reset in the spike step
     // (iaf_psc_alpha), bit3 threshold test is >= (iaf_psc_alpha)
     int32_t flags;
-    int32_t pad_i[2];
+    float asc_rec[2];   // asc_coeff / asc_decay: recovers the step mean the latest integrating step used from the current value
 };
 static_assert(sizeof(TypeConsts) % 16 == 0, "TypeConsts is copied word-wise and read with 128-bit loads");
 

@@ -86,6 +86,7 @@ static int compute_type_consts(const bmtk_glif_params& p, double h, TypeConsts& 
             c.asc_coeff[j] = (float)(-std::expm1(-k * h) / (k * h));
             c.asc_refr[j] = (float)(p.asc_r[j] * std::exp(-k * p.t_ref));
             c.asc_amps[j] = (float)p.asc_amps[j];
+            c.asc_rec[j] = (float)(-std::expm1(-k * h) / (k * h) / std::exp(-k * h));
         } else {
             c.asc_decay[j] = 1.f;
             c.asc_coeff[j] = 0.f;
@@ -160,8 +161,8 @@ __global__ void apply_clamp_kernel(float* i_ext, const uint32_t* target, const f
 // V_m probe: after the step that ends at a multiple of `interval`, writes V_m = U + E_L of the
 // probed neurons into trace[sample][q].
 __global__ void snapshot_kernel(Ctl* ctl, uint32_t step_in_window, uint32_t interval, const uint32_t* ids,
-                                uint32_t n_ids, const float* U, const uint16_t* type, const TypeConsts* types,
-                                float* trace, uint32_t cap_samples) {
+                                uint32_t n_ids, StateSoA st, uint32_t n_pad, const TypeConsts* types,
+                                float* trace, uint32_t cap_samples, uint32_t n_vars, uint32_t vars) {
     const unsigned long long done = ctl->step_base + step_in_window + 1ull;
     if (done % interval) return;
     const unsigned long long sample = done / interval - 1ull - ctl->sample_base;
@@ -169,7 +170,24 @@ __global__ void snapshot_kernel(Ctl* ctl, uint32_t step_in_window, uint32_t inte
     const uint32_t stride = gridDim.x * blockDim.x;
     for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < n_ids; q += stride) {
         const uint32_t i = ids[q];
-        trace[(size_t)sample * n_ids + q] = U[i] + types[type[i]].E_L;
+        const TypeConsts& c = types[st.type[i]];
+        for (uint32_t v = 0; v < n_vars; ++v) {
+            float x;
+            switch ((vars >> (4u * v)) & 15u) {   // the same expressions as Neuron4::probe_value
+                case BMTK_VAR_I_SYN:
+                    x = ((st.y2[i] + st.y2[(size_t)n_pad + i]) + st.y2[2 * (size_t)n_pad + i]) + st.y2[3 * (size_t)n_pad + i];
+                    break;
+                case BMTK_VAR_ASC_SUM: x = c.asc_rec[0] * st.asc0[i] + c.asc_rec[1] * st.asc1[i]; break;
+                case BMTK_VAR_THRESHOLD:
+                    x = (c.th_inf + (st.th_spike ? st.th_spike[i] : 0.f) + (st.th_voltage ? st.th_voltage[i] : 0.f)) + c.E_L;
+                    break;
+                case BMTK_VAR_TH_SPIKE: x = st.th_spike ? st.th_spike[i] : 0.f; break;
+                case BMTK_VAR_TH_VOLTAGE: x = st.th_voltage ? st.th_voltage[i] : 0.f; break;
+                case BMTK_VAR_I: x = (st.i_ext ? st.i_ext[i] : 0.f) + c.i_e; break;
+                default: x = st.U[i] + c.E_L;
+            }
+            trace[((size_t)sample * n_vars + v) * n_ids + q] = x;
+        }
     }
 }
 
@@ -279,6 +297,7 @@ struct bmtk_engine {
     // probes
     std::vector<uint32_t> probe_ids;
     uint32_t probe_interval = 1;
+    uint32_t n_probe_vars = 1, probe_vars = BMTK_VAR_V_M;   // recorded variables, 4 bits per code
     uint32_t* d_probe_ids = nullptr;
     float* d_trace = nullptr;
     uint32_t trace_cap = 0;
@@ -514,8 +533,8 @@ static int enqueue_window(bmtk_engine* e, uint32_t w, bool capturing) {
         if (!e->probe_ids.empty()) {
             const uint32_t n_ids = (uint32_t)e->probe_ids.size();
             const int blocks = (int)std::min<uint32_t>((n_ids + 255) / 256, 148 * 4);
-            snapshot_kernel<<<blocks, 256, 0, e->stream>>>(e->d_ctl, s, e->probe_interval, e->d_probe_ids, n_ids,
-                                                           e->st.U, e->d_type, e->d_types, e->d_trace, e->trace_cap);
+            snapshot_kernel<<<blocks, 256, 0, e->stream>>>(e->d_ctl, s, e->probe_interval, e->d_probe_ids, n_ids, e->st, e->n_pad,
+                                                           e->d_types, e->d_trace, e->trace_cap, e->n_probe_vars, e->probe_vars);
             CU(cudaGetLastError());
             ++e->launches;
         }
@@ -763,7 +782,7 @@ static int drain(bmtk_engine* e) {
         const uint64_t have = e->step / e->probe_interval;
         const uint64_t n_new = have - e->samples_drained;
         if (n_new) {
-            const size_t n_ids = e->probe_ids.size(), n0 = e->h_trace.size();
+            const size_t n_ids = e->probe_ids.size() * e->n_probe_vars, n0 = e->h_trace.size();   // values per sample
             e->h_trace.resize(n0 + n_new * n_ids);
             CU(cudaMemcpyAsync(e->h_trace.data() + n0, e->d_trace, 4 * n_new * n_ids, cudaMemcpyDeviceToHost, e->stream));
             e->samples_drained = have;
@@ -834,6 +853,8 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
     a.probe_slot = e->probe_ids.empty() ? nullptr : e->d_probe_slot;
     a.n_probe = (uint32_t)e->probe_ids.size();
     a.probe_interval = e->probe_interval;
+    a.n_probe_vars = e->n_probe_vars;
+    a.probe_vars = e->probe_vars;
     a.trace = e->d_trace;
     a.trace_cap = e->trace_cap;
     a.profile = e->phase_timers ? 1u : 0u;
@@ -1102,6 +1123,22 @@ int bmtk_engine_record_spikes(bmtk_engine* e, int enable) {
     return BMTK_OK;
 }
 
+int bmtk_engine_record_state(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps, int32_t n_vars,
+                             const int32_t* vars) {
+    if (!e || e->finalized) return fail(BMTK_E_INVALID, "record_state: engine missing or already finalized");
+    if (n_vars < 1 || n_vars > 8 || !vars) return fail(BMTK_E_INVALID, "record_state: 1..8 variables");
+    uint32_t packed = 0;
+    for (int32_t v = 0; v < n_vars; ++v) {
+        if (vars[v] < 0 || vars[v] > BMTK_VAR_I) return fail(BMTK_E_INVALID, "record_state: unknown variable code %d", vars[v]);
+        packed |= (uint32_t)vars[v] << (4 * v);
+    }
+    const int rc = bmtk_engine_record_vm(e, n_ids, ids, interval_steps);
+    if (rc) return rc;
+    e->n_probe_vars = (uint32_t)n_vars;
+    e->probe_vars = packed;
+    return BMTK_OK;
+}
+
 int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps) {
     if (!e || e->finalized) return fail(BMTK_E_INVALID, "record_vm: engine missing or already finalized");
     if (interval_steps < 1) return fail(BMTK_E_INVALID, "record_vm: interval must be at least one step");
@@ -1112,6 +1149,8 @@ int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, u
     e->probe_ids.resize(n_ids);
     for (uint64_t i = 0; i < n_ids; ++i) e->probe_ids[i] = ids[i] - (uint32_t)e->lo;
     e->probe_interval = interval_steps;
+    e->n_probe_vars = 1;
+    e->probe_vars = BMTK_VAR_V_M;
     return BMTK_OK;
 }
 
@@ -1377,14 +1416,14 @@ int bmtk_engine_finalize(bmtk_engine* e) {
     }
     // probes
     if (!e->probe_ids.empty()) {
-        const size_t n_ids = e->probe_ids.size();
+        const size_t n_ids = e->probe_ids.size(), n_vals = n_ids * e->n_probe_vars;
         // at most 256 MiB of trace between drains, at least 64 samples
-        uint64_t cap_s = std::max<uint64_t>(64, (256ull << 20) / (4 * n_ids));
+        uint64_t cap_s = std::max<uint64_t>(64, (256ull << 20) / (4 * n_vals));
         cap_s = std::min<uint64_t>(cap_s, 1u << 20);
         e->trace_cap = (uint32_t)cap_s;
         CU(cudaMalloc(&e->d_probe_ids, 4 * n_ids));
         CU(cudaMemcpy(e->d_probe_ids, e->probe_ids.data(), 4 * n_ids, cudaMemcpyHostToDevice));
-        CU(cudaMalloc(&e->d_trace, 4 * n_ids * cap_s));
+        CU(cudaMalloc(&e->d_trace, 4 * n_vals * cap_s));
     }
     // persistent stepping: second spike lists, clamp groups, probe map, grid size
     {
@@ -1572,13 +1611,13 @@ int bmtk_engine_fetch_spikes(bmtk_engine* e, uint64_t cap, uint32_t* stamp_step,
 
 int bmtk_engine_trace_samples(bmtk_engine* e, uint64_t* n_samples) {
     if (!e || !n_samples) return fail(BMTK_E_INVALID, "NULL argument");
-    *n_samples = e->probe_ids.empty() ? 0 : e->h_trace.size() / e->probe_ids.size();
+    *n_samples = e->probe_ids.empty() ? 0 : e->h_trace.size() / (e->probe_ids.size() * e->n_probe_vars);
     return BMTK_OK;
 }
 
 int bmtk_engine_fetch_trace(bmtk_engine* e, uint64_t cap_samples, float* vm, uint64_t* n_out) {
     if (!e || !n_out) return fail(BMTK_E_INVALID, "NULL argument");
-    const size_t n_ids = e->probe_ids.size();
+    const size_t n_ids = e->probe_ids.size() * e->n_probe_vars;   // values per sample: [variable][id]
     const size_t n = n_ids ? e->h_trace.size() / n_ids : 0;
     if (cap_samples < n) return fail(BMTK_E_INVALID, "fetch_trace: capacity too small");
     if (n) std::memcpy(vm, e->h_trace.data(), 4 * n * n_ids);

@@ -62,6 +62,19 @@ struct Neuron4 {
         }
     }
 
+    // Recordable `code` (BMTK_VAR_*) of neuron j after a step.
+    __device__ __forceinline__ float probe_value(const TypeConsts& c, int j, uint32_t code) const {
+        switch (code) {
+            case BMTK_VAR_I_SYN: return ((y2[0].v[j] + y2[1].v[j]) + y2[2].v[j]) + y2[3].v[j];
+            case BMTK_VAR_ASC_SUM: return c.asc_rec[0] * a0.v[j] + c.asc_rec[1] * a1.v[j];
+            case BMTK_VAR_THRESHOLD: return (c.th_inf + ths.v[j] + thv.v[j]) + c.E_L;
+            case BMTK_VAR_TH_SPIKE: return ths.v[j];
+            case BMTK_VAR_TH_VOLTAGE: return thv.v[j];
+            case BMTK_VAR_I: return iex.v[j] + c.i_e;
+            default: return U.v[j] + c.E_L;
+        }
+    }
+
     // One step for the four neurons with ring input in[port]. Returns the spike mask (bit j).
     // Written without branches: both the refractory and the integrating update are evaluated and
     // the result selected, so that the four neurons' dependency chains (and their loads of the

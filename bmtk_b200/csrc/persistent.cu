@@ -151,7 +151,10 @@ __device__ __forceinline__ void do_group(const PersistArgs& a, BlockShared& sh, 
             if (sample < a.trace_cap) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (pslot[j] >= 0) a.trace[(size_t)sample * a.n_probe + pslot[j]] = nr.U.v[j] + types[nr.ty[j]].E_L;
+                    if (pslot[j] >= 0)
+                        for (uint32_t v = 0; v < a.n_probe_vars; ++v)
+                            a.trace[((size_t)sample * a.n_probe_vars + v) * a.n_probe + pslot[j]] =
+                                nr.probe_value(types[nr.ty[j]], j, (a.probe_vars >> (4u * v)) & 15u);
             }
         }
     }

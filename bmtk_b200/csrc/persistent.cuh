@@ -66,6 +66,8 @@ struct PersistArgs {
     // V_m probes: probe_slot[i] = trace column of local neuron i or -1
     const int32_t* probe_slot;
     uint32_t n_probe, probe_interval;
+    uint32_t n_probe_vars, probe_vars;   // recorded variables: count and their BMTK_VAR_* codes, 4 bits each; a trace
+                                         // sample is [variable][probe]
     float* trace;
     uint32_t trace_cap;
     uint32_t profile;

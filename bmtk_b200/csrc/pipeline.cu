@@ -527,7 +527,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
 #pragma unroll
                             for (int jj = 0; jj < 4; ++jj)
                                 if (pslot[jj] >= 0)
-                                    a.trace[(size_t)sample * a.n_probe + pslot[jj]] = nr.U.v[jj] + types[nr.ty[jj]].E_L;
+                                    for (uint32_t v = 0; v < a.n_probe_vars; ++v)
+                                        a.trace[((size_t)sample * a.n_probe_vars + v) * a.n_probe + pslot[jj]] =
+                                            nr.probe_value(types[nr.ty[jj]], jj, (a.probe_vars >> (4u * v)) & 15u);
                         }
                         ++sample;
                     }

@@ -185,6 +185,16 @@ class Engine(object):
         ids = _arr(ids, np.uint32)
         check(self._lib.bmtk_engine_record_vm(self._h, len(ids), _ptr(ids), int(interval_steps)))
         self.n_probe = len(ids)
+        self.n_probe_vars = 1
+
+    def record_state(self, ids, interval_steps=1, variables=('V_m',)):
+        """Multimeter on `ids` for the named recordables (keys of _cabi.RECORDABLES); fetch_trace then returns
+        [samples, variables, ids]."""
+        ids = _arr(ids, np.uint32)
+        codes = np.array([_cabi.RECORDABLES[v] for v in variables], dtype=np.int32)
+        check(self._lib.bmtk_engine_record_state(self._h, len(ids), _ptr(ids), int(interval_steps), len(codes), _ptr(codes)))
+        self.n_probe = len(ids)
+        self.n_probe_vars = len(codes)
 
     def set_option(self, key, value):
         check(self._lib.bmtk_engine_set_option(self._h, key.encode(), int(value)))
@@ -271,13 +281,15 @@ class Engine(object):
         return st[:out.value], ids[:out.value]
 
     def fetch_trace(self):
-        """float32[samples, n_probe] of V_m; drains the store."""
+        """float32[samples, n_probe] of V_m ([samples, variables, n_probe] after record_state with several
+        variables); drains the store."""
         n = C.c_uint64()
         check(self._lib.bmtk_engine_trace_samples(self._h, C.byref(n)))
-        tr = np.empty((n.value, self.n_probe), dtype=np.float32)
+        nv = getattr(self, 'n_probe_vars', 1)
+        tr = np.empty((n.value, nv, self.n_probe), dtype=np.float32)
         out = C.c_uint64()
         check(self._lib.bmtk_engine_fetch_trace(self._h, n.value, _ptr(tr), C.byref(out)))
-        return tr[:out.value]
+        return tr[:out.value, 0] if nv == 1 else tr[:out.value]
 
     def state(self, var):
         """One trial: n_local values. Several trials: n_trials * n_pad1 values, trial-major."""

@@ -148,8 +148,9 @@ class SpikesMod(SimulatorMod):
 
 
 class MultimeterMod(SimulatorMod):
-    """Membrane report of a node set (modules/multimeter_reporter.py:68-167): V_m every `interval`
-    (default dt); sample k is the state at k*interval, k >= 1; one element per node."""
+    """Report of a node set (modules/multimeter_reporter.py:68-167): `variable_name` (V_m, I_syn, ASCurrents_sum,
+    threshold, threshold_spike, threshold_voltage, I) every `interval` (default dt); sample k is the state at
+    k*interval, k >= 1; one element per node."""
 
     def __init__(self, tmp_dir, file_name, variable_name, cells, tstart=None, tstop=None, interval=None, to_h5=True,
                  delete_dat=True, **opts):
@@ -162,9 +163,11 @@ class MultimeterMod(SimulatorMod):
         self._population = None
 
     def initialize(self, sim):
+        from .._cabi import RECORDABLES
         for v in self._variables:
-            if v != 'V_m':
-                io.log_exception('MultimeterMod: variable "{}" cannot be recorded (only V_m)'.format(v))
+            if v not in RECORDABLES:
+                io.log_exception('MultimeterMod: variable "{}" cannot be recorded (available: {})'.format(
+                    v, ', '.join(sorted(RECORDABLES))))
         node_set = sim.net.get_node_set(self._node_set)
         self._gids = sorted(set(node_set.gids()))
         self._population = node_set.population_names()[0] if node_set.population_names() else None
@@ -174,10 +177,14 @@ class MultimeterMod(SimulatorMod):
         steps = int(round(self._interval / sim.dt))
         if steps < 1 or abs(steps * sim.dt - self._interval) > 1e-9 * max(1.0, self._interval):
             io.log_exception('MultimeterMod: interval {} is not a multiple of dt {}'.format(self._interval, sim.dt))
-        self._handle = sim.add_vm_recorder(self._gids, steps)
+        self._handle = sim.add_vm_recorder(self._gids, steps, self._variables)
 
     def finalize(self, sim):
-        gids, data = sim.recorded_vm(self._handle)         # [samples, n_gids], rank 0 has all columns
+        gids, by_var = sim.recorded_vm(self._handle)       # per variable [samples, n_gids], rank 0 has all columns
+        # The reference creates ONE report named after the first variable and writes every listed variable's values
+        # into the same block, one after the other (multimeter_reporter.py:130-157): what stays in the file are the
+        # values of the LAST variable under the name of the first. Reproduced as it is.
+        data = by_var[self._variables[-1]]
         if io.mpi_rank == 0 and self._to_h5:
             k0 = int(np.floor(self._tstart / self._interval + 1e-9))          # samples with t <= tstart are dropped
             k1 = int(np.floor(self._tstop / self._interval + 1e-9))
@@ -188,5 +195,6 @@ class MultimeterMod(SimulatorMod):
                 m = pops == p
                 out[p] = (node_ids[m], data[:, m])
             reports.write_membrane_report(self._file, out, self._tstart, self._tstart + data.shape[0] * self._interval,
-                                          self._interval, variable=self._variables[0], units='mV')
+                                          self._interval, variable=self._variables[0],
+                                          units='mV' if self._variables[0] in ('V_m', 'threshold', 'threshold_spike', 'threshold_voltage') else 'pA')
         io.barrier()

@@ -36,7 +36,7 @@ class PointSimulator(object):
         self._sg_params = {'precise_times': True}
         self._record_spikes = False
         self._clamps = []            # (times, values, gids)
-        self._vm_recorders = []      # (gids, interval_steps)
+        self._vm_recorders = []      # (gids, interval_steps, variable names)
         self._engine = None
         self._engine_options = {}
         self._spikes = (np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.int64))
@@ -100,8 +100,8 @@ class PointSimulator(object):
     def add_current_clamp(self, times, values, gids):
         self._clamps.append((list(times), list(values), np.asarray(list(gids), dtype=np.int64)))
 
-    def add_vm_recorder(self, gids, interval_steps):
-        self._vm_recorders.append((np.asarray(gids, dtype=np.int64), int(interval_steps)))
+    def add_vm_recorder(self, gids, interval_steps, variables=('V_m',)):
+        self._vm_recorders.append((np.asarray(gids, dtype=np.int64), int(interval_steps), list(variables)))
         return len(self._vm_recorders) - 1
 
     def recorded_spikes(self):
@@ -169,11 +169,14 @@ class PointSimulator(object):
         # one device recorder serves all membrane reports: union of cells at the finest interval
         self._probe_gids = np.zeros(0, dtype=np.int64)
         if self._vm_recorders:
-            allg = np.unique(np.concatenate([g for g, _ in self._vm_recorders]))
-            self._probe_interval = int(np.gcd.reduce([s for _, s in self._vm_recorders]))
+            allg = np.unique(np.concatenate([g for g, _, _ in self._vm_recorders]))
+            self._probe_interval = int(np.gcd.reduce([s for _, s, _ in self._vm_recorders]))
+            self._probe_vars = []
+            for _, _, names in self._vm_recorders:
+                self._probe_vars.extend(v for v in names if v not in self._probe_vars)
             self._probe_gids = allg[(allg >= lo) & (allg < hi)]
             if len(self._probe_gids):
-                eng.record_vm(self._probe_gids, self._probe_interval)
+                eng.record_state(self._probe_gids, self._probe_interval, self._probe_vars)
         for k, v in self._engine_options.items():
             eng.set_option(k, v)
         if world > 1:
@@ -200,7 +203,10 @@ class PointSimulator(object):
         if self._record_spikes:
             s, g = eng.fetch_spikes()
             stamps, gids = s.astype(np.int64), g.astype(np.int64)
-        trace = eng.fetch_trace() if len(self._probe_gids) else np.zeros((0, 0), dtype=np.float32)
+        n_vars = len(getattr(self, '_probe_vars', [])) or 1
+        trace = eng.fetch_trace() if len(self._probe_gids) else np.zeros((0, n_vars, 0), dtype=np.float32)
+        if trace.ndim == 2:
+            trace = trace[:, None, :]           # [samples, variables, cells]
         probe = self._probe_gids
         if io.mpi_size > 1:
             import torch.distributed as dist
@@ -213,15 +219,16 @@ class PointSimulator(object):
                 stamps, gids = stamps[o], gids[o]
                 have = [p for p in parts if len(p[2])]
                 probe = np.concatenate([p[2] for p in have]) if have else probe
-                trace = np.concatenate([p[3] for p in have], axis=1) if have else trace
+                trace = np.concatenate([p[3] for p in have], axis=2) if have else trace
         self._spikes = (stamps, gids)
-        for h, (g, steps) in enumerate(self._vm_recorders):
+        for h, (g, steps, names) in enumerate(self._vm_recorders):
             if len(probe) == 0:
-                self._traces[h] = (g, np.zeros((0, len(g))))
+                self._traces[h] = (g, {v: np.zeros((0, len(g))) for v in names})
                 continue
             cols = np.searchsorted(probe, g)
             stride = steps // self._probe_interval
-            self._traces[h] = (g, trace[stride - 1::stride][:, cols].astype(np.float64))
+            sub = trace[stride - 1::stride]
+            self._traces[h] = (g, {v: sub[:, self._probe_vars.index(v)][:, cols].astype(np.float64) for v in names})
 
     def run(self, tstop=None):
         """pointsimulator.py:144-174."""

@@ -127,6 +127,22 @@ int bmtk_engine_record_spikes(bmtk_engine* e, int enable);
  * this engine's block; sample k (k >= 1) is V_m after the step that ends at k*interval. */
 int bmtk_engine_record_vm(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps);
 
+/* The same multimeter with other `record_from` names (multimeter_reporter.py:103-115 hands any name to NEST).
+ * vars[n_vars] are BMTK_VAR_* codes, at most 8; record_vm is record_state with {BMTK_VAR_V_M}. A trace sample then
+ * holds n_vars rows of n_ids values, [sample][variable][id], in the order of `vars`. I_syn is the sum of the ports'
+ * post-synaptic currents (pA); ASCurrents_sum the step mean of the after-spike currents that the latest
+ * integrating step used (it differs from NEST's held value in the one sample at which the refractory period ends);
+ * threshold is V_th + spike + voltage component (mV, absolute). */
+#define BMTK_VAR_V_M 0
+#define BMTK_VAR_I_SYN 1
+#define BMTK_VAR_ASC_SUM 2
+#define BMTK_VAR_THRESHOLD 3
+#define BMTK_VAR_TH_SPIKE 4
+#define BMTK_VAR_TH_VOLTAGE 5
+#define BMTK_VAR_I 6
+int bmtk_engine_record_state(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids, uint32_t interval_steps, int32_t n_vars,
+                             const int32_t* vars);
+
 /* Options (before finalize unless noted):
  *  "deterministic"  0|1  sorted segmented reduction instead of atomics in spike delivery
  *  "trials"         T >= 1 independent copies of the network that share the CSR (one rank, atomic

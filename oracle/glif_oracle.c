@@ -210,9 +210,16 @@ typedef struct {
     int32_t n_probe;
     const int32_t* probe_ids;
     int32_t probe_interval;             /* steps */
-    double* trace;                      /* [samples][n_probe], V_m = U + E_L after the step ending at k*interval */
+    double* trace;                      /* [samples][n_probe_vars][n_probe], after the step ending at k*interval */
     int64_t* n_samples;                 /* in/out running count */
     int64_t* n_events;                  /* in/out: synaptic events delivered */
+    /* recorded variables (NEST multimeter `record_from`, bmtk/simulator/pointnet/modules/multimeter_reporter.py:103-115):
+     * count (0 = V_m only) and codes, 4 bits each: 0 V_m, 1 I_syn = sum of the ports' PSCs y2, 2 ASCurrents_sum = the
+     * step mean sum_j c_j ASC_j the latest integrating step used, stated from the current values as
+     * sum_j (c_j / decay_j) ASC_j (exact except in the sample at which the refractory period ends), 3 threshold =
+     * V_th + spike + voltage component (absolute mV), 4 threshold_spike, 5 threshold_voltage, 6 I = I_e + clamp current */
+    int32_t n_probe_vars;
+    uint32_t probe_vars;
 } orc_run_args;
 
 int64_t orc_state_ring_slots(int32_t max_delay) { return (int64_t)max_delay + 1; }
@@ -378,10 +385,28 @@ int orc_run(orc_run_args* a)
             }
         }
         if (a->n_probe > 0 && a->probe_interval > 0 && (n + 1) % a->probe_interval == 0) {
-            double* row = a->trace + (*a->n_samples) * a->n_probe;
-            for (int q = 0; q < a->n_probe; ++q) {
-                const int32_t i = a->probe_ids[q];
-                row[q] = a->U[i] + C[a->type_index[i]].E_L;
+            const int nv = a->n_probe_vars > 0 ? a->n_probe_vars : 1;
+            double* row = a->trace + (*a->n_samples) * a->n_probe * nv;
+            for (int v = 0; v < nv; ++v) {
+                const uint32_t code = a->n_probe_vars > 0 ? (a->probe_vars >> (4 * v)) & 15u : 0u;
+                for (int q = 0; q < a->n_probe; ++q) {
+                    const int32_t i = a->probe_ids[q];
+                    const orc_glif_consts* c = &C[a->type_index[i]];
+                    double x;
+                    switch (code) {
+                        case 1: x = 0.0; for (int p = 0; p < c->n_ports; ++p) x += a->y2[p * N + i]; break;
+                        case 2:
+                            x = c->has_asc ? c->asc_stable_coeff[0] / c->asc_decay_rate[0] * a->asc[i]
+                                             + c->asc_stable_coeff[1] / c->asc_decay_rate[1] * a->asc[N + i] : 0.0;
+                            break;
+                        case 3: x = c->th_inf + a->th_spike[i] + a->th_voltage[i] + c->E_L; break;
+                        case 4: x = a->th_spike[i]; break;
+                        case 5: x = a->th_voltage[i]; break;
+                        case 6: x = a->i_ext[i] + c->I_e; break;
+                        default: x = a->U[i] + c->E_L;
+                    }
+                    row[v * a->n_probe + q] = x;
+                }
             }
             ++*a->n_samples;
         }

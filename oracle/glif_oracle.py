@@ -72,6 +72,7 @@ class RunArgs(C.Structure):
         ('spike_cap', C.c_int64), ('n_spikes', _p), ('spike_step', _p), ('spike_id', _p),
         ('n_probe', C.c_int32), ('probe_ids', _p), ('probe_interval', C.c_int32),
         ('trace', _p), ('n_samples', _p), ('n_events', _p),
+        ('n_probe_vars', C.c_int32), ('probe_vars', C.c_uint32),
     ]
 
 
@@ -303,6 +304,7 @@ class OracleSim:
         self.ce_step = np.zeros(0, dtype=np.int64); self.ce_target = np.zeros(0, dtype=np.int32)
         self.ce_delta = np.zeros(0, dtype=np.float64)
         self.probe_ids = np.zeros(0, dtype=np.int32); self.probe_interval = 1
+        self.probe_vars = [0]
         self.n_events = np.zeros(1, dtype=np.int64)
         a = self._args(0)
         self.L.orc_init_state(C.byref(a))
@@ -321,9 +323,12 @@ class OracleSim:
         self.ce_target = np.ascontiguousarray(np.asarray(target)[o], dtype=np.int32)
         self.ce_delta = np.ascontiguousarray(np.asarray(delta)[o], dtype=np.float64)
 
-    def set_probes(self, ids, interval_steps=1):
+    def set_probes(self, ids, interval_steps=1, variables=None):
+        """Recorded cells; `variables` are recorder codes (0 V_m, 1 I_syn, 2 ASCurrents_sum, 3 threshold,
+        4 threshold_spike, 5 threshold_voltage, 6 I). With more than one the trace is [sample, variable, cell]."""
         self.probe_ids = np.ascontiguousarray(ids, dtype=np.int32)
         self.probe_interval = int(interval_steps)
+        self.probe_vars = [int(v) for v in (variables or [0])]
 
     def _args(self, n_steps):
         a = RunArgs()
@@ -358,7 +363,10 @@ class OracleSim:
         a.spike_step = _ptr(sp_step) if record_spikes else None
         a.spike_id = _ptr(sp_id)
         n_samp_max = n_steps // max(1, self.probe_interval) + 1
-        trace = np.zeros((n_samp_max, max(1, len(self.probe_ids))))
+        nv = len(self.probe_vars)
+        trace = np.zeros((n_samp_max, nv, max(1, len(self.probe_ids))))
+        a.n_probe_vars = nv
+        a.probe_vars = sum(v << (4 * k) for k, v in enumerate(self.probe_vars))
         n_samples = np.zeros(1, dtype=np.int64)
         a.n_probe = len(self.probe_ids); a.probe_ids = _ptr(self.probe_ids)
         a.probe_interval = self.probe_interval; a.trace = _ptr(trace); a.n_samples = _ptr(n_samples)
@@ -372,7 +380,8 @@ class OracleSim:
         self.step = end
         k = int(n_spikes[0]) if record_spikes else 0
         return dict(spike_step=sp_step[:k].copy(), spike_id=sp_id[:k].copy(),
-                    trace=trace[:int(n_samples[0]), :len(self.probe_ids)].copy(),
+                    trace=(trace[:int(n_samples[0]), 0, :len(self.probe_ids)] if nv == 1
+                           else trace[:int(n_samples[0]), :, :len(self.probe_ids)]).copy(),
                     n_spikes=int(n_spikes[0]), n_events=int(self.n_events[0]) - ev0)
 
     def v_m(self):

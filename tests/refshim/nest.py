@@ -258,21 +258,21 @@ def _build_engine():
     if steps:
         eng.set_clamp_events(np.concatenate(steps), np.concatenate(targets), np.concatenate(deltas))
     eng.record_spikes(any(_K.nodes[r]['model'] in ('spike_recorder', 'spike_detector') for r, _ in _K.recorder_links))
-    probes, interval = [], None
+    probes, interval, variables = [], None, []
     for r, ids in _K.recorder_links:
         nd = _K.nodes[r]
         if nd['model'] != 'multimeter':
             continue
         rf = nd['params'].get('record_from')
-        if list(rf) != ['V_m']:
-            raise NotImplementedError('multimeter record_from %r' % (rf,))
+        variables.extend(v for v in ([rf] if isinstance(rf, str) else list(rf)) if v not in variables)
         k = int(round(float(nd['params'].get('interval', dt)) / dt))
         interval = k if interval is None else int(np.gcd(interval, k))
         probes.extend(eng_of[i] for i in ids)
     _K.probe_ids = np.array(sorted(set(probes)), dtype=np.uint32)
     _K.probe_interval = interval or 1
+    _K.probe_vars = variables
     if len(_K.probe_ids):
-        eng.record_vm(_K.probe_ids, _K.probe_interval)
+        eng.record_state(_K.probe_ids, _K.probe_interval, variables)
     eng.finalize()
     _K.engine, _K.net = eng, net
 
@@ -313,19 +313,24 @@ def _write_recorders():
                     f.write('%d\t%.3f\n' % (s, t))
         elif nd['model'] == 'multimeter':
             if trace is None:
-                trace = eng.fetch_trace()            # [samples at multiples of probe_interval, probes]
+                trace = eng.fetch_trace()            # [samples at multiples of probe_interval, (variables,) probes]
+                if trace.ndim == 2:
+                    trace = trace[:, None, :]
+            rf = nd['params']['record_from']
+            rf = [rf] if isinstance(rf, str) else list(rf)
+            vcols = [_K.probe_vars.index(v) for v in rf]
             k = int(round(float(nd['params'].get('interval', dt)) / dt)) // _K.probe_interval
             t0, t1 = float(nd['params'].get('start', 0.0)), float(nd['params'].get('stop', np.inf))
             cols = np.searchsorted(_K.probe_ids, np.array([net['neurons'].index(i) for i in watched]))
             n_done = getattr(_K, 'samples_written', {}).get(r, 0)
             with open(path, mode) as f:
                 if mode == 'w':
-                    f.write(header + 'sender\ttime_ms\t' + '\t'.join(nd['params']['record_from']) + '\n')
+                    f.write(header + 'sender\ttime_ms\t' + '\t'.join(rf) + '\n')
                 for j in range(k - 1, trace.shape[0], k):
                     t = (n_done + j + 1) * _K.probe_interval * dt
                     if t <= t0 + 1e-9 or t > t1 + 1e-9:
                         continue
                     for i, c in zip(watched, cols):
-                        f.write('%d\t%.3f\t%r\n' % (i, t, float(trace[j, c])))
+                        f.write('%d\t%.3f\t%s\n' % (i, t, '\t'.join(repr(float(trace[j, v, c])) for v in vcols)))
             _K.__dict__.setdefault('samples_written', {})[r] = n_done + trace.shape[0]
         _K.__dict__.setdefault('files_started', set()).add(path)

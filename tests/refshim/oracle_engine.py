@@ -53,6 +53,12 @@ class OracleEngine(object):
         self._probes = (np.asarray(ids, dtype=np.uint32), int(interval_steps))
         self.n_probe = len(ids)
 
+    def record_state(self, ids, interval_steps=1, variables=('V_m',)):
+        from bmtk_b200._cabi import RECORDABLES
+        self._probes = (np.asarray(ids, dtype=np.uint32), int(interval_steps))
+        self._vars = [RECORDABLES[v] for v in variables]
+        self.n_probe = len(ids)
+
     def set_option(self, key, value):
         self.options[key] = value
 
@@ -66,7 +72,7 @@ class OracleEngine(object):
         if self._clamps is not None:
             self.sim.set_clamp_events(self._clamps[0], self._clamps[1], self._clamps[2].astype(np.float64))
         if len(self._probes[0]):
-            self.sim.set_probes(self._probes[0], self._probes[1])
+            self.sim.set_probes(self._probes[0], self._probes[1], getattr(self, '_vars', [0]))
 
     def connect_peers(self):
         pass
@@ -85,7 +91,9 @@ class OracleEngine(object):
         return st, ids
 
     def fetch_trace(self):
-        tr = np.concatenate(self._trace) if self._trace else np.zeros((0, len(self._probes[0])), dtype=np.float32)
+        nv = len(getattr(self, '_vars', [0]))
+        empty = np.zeros((0, len(self._probes[0])) if nv == 1 else (0, nv, len(self._probes[0])), dtype=np.float32)
+        tr = np.concatenate(self._trace) if self._trace else empty
         self._trace = []
         return tr
 

@@ -496,6 +496,66 @@ def test_iaf_psc_delta_cells(cabi):
             _trace_check(tr[:, q:q + 1], r['trace'][:, q:q + 1], upto)
 
 
+def test_recordables_other_than_v_m(cabi):
+    """Multimeter variables I_syn, ASCurrents_sum, threshold (and its two components), I: the three stepping
+    paths (pipelined kernel, two-phase kernel, per-step kernels) write the same values bit for bit (weights on a
+    0.25 pA grid make every synaptic sum exact), and they follow the fp64 oracle until the spike lists part."""
+    net = W.c0(t_stop_ms=150.0)
+    net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+    # two of the five types get threshold dynamics so that the threshold recordables move
+    net.types[1] = dict(net.types[1], spike_dependent_threshold=True, th_spike_add=0.5, th_spike_decay=0.01,
+                        voltage_reset_fraction=0.3, voltage_reset_add=3.0)
+    net.types[3] = dict(net.types[3], spike_dependent_threshold=True, adapting_threshold=True, th_spike_add=0.4,
+                        th_spike_decay=0.02, voltage_reset_fraction=0.2, voltage_reset_add=2.0, th_voltage_index=0.004,
+                        th_voltage_decay=0.08)
+    ids = np.arange(450, dtype=np.uint32)
+    amp = np.linspace(0.0, 60.0, 450).astype(np.float32)
+    net.clamp_step = np.concatenate([np.full(450, 301), np.full(450, 1001)]).astype(np.uint64)
+    net.clamp_target = np.concatenate([ids, ids])
+    net.clamp_delta = np.concatenate([amp, -amp])
+    names = ['V_m', 'I_syn', 'ASCurrents_sum', 'threshold', 'threshold_spike', 'threshold_voltage', 'I']
+    probes = np.array([0, 130, 131, 250, 370, 371, 420], dtype=np.uint32)
+
+    def run(**options):
+        from bmtk_b200.engine import Engine
+        e = Engine(net.dt)
+        e.set_nodes(net.types, net.type_index, n_global=net.n_neurons)
+        e.set_virtual(net.n_virtual)
+        e.add_edges(net.src, net.trg, net.weight, net.delay_steps, net.port)
+        e.set_input_spikes(net.in_virt, net.in_stamp)
+        e.set_clamp_events(net.clamp_step, net.clamp_target, net.clamp_delta)
+        e.record_spikes(True)
+        e.record_state(probes, 2, names)
+        for k, v in options.items():
+            e.set_option(k, v)
+        e.finalize()
+        e.run(net.n_steps)
+        st, sid = e.fetch_spikes()
+        return e, st.astype(np.int64), sid.astype(np.int64), e.fetch_trace()
+    a = run()
+    b = run(pipeline=0)
+    c = run(persistent=0)
+    assert a[0].counter('pipelined') == 1 and b[0].counter('pipelined') == 0
+    assert a[3].shape == (net.n_steps // 2, len(names), len(probes))
+    for other in (b, c):
+        assert np.array_equal(a[1], other[1]) and np.array_equal(a[2], other[2])
+        assert np.array_equal(a[3].view(np.uint32), other[3].view(np.uint32))
+    sim = oracle_from_network(net)
+    from bmtk_b200._cabi import RECORDABLES
+    sim.set_probes(probes, 2, [RECORDABLES[v] for v in names])
+    r = sim.run(net.n_steps)
+    assert r['n_spikes'] > 200 and r['trace'].shape == a[3].shape
+    div = _first_divergence(a[1], a[2], r['spike_step'], r['spike_id'])
+    upto = int(min(div - 1, net.n_steps)) // 2
+    assert upto > 300
+    for v, name in enumerate(names):
+        g, o = a[3][:upto, v].astype(np.float64), r['trace'][:upto, v]
+        assert np.all(np.abs(g - o) <= 1e-4 * np.abs(o) + (2e-4 if name in ('V_m', 'threshold') else 1e-3)), name
+        assert np.ptp(o) > 0, name                       # every variable moves in this run
+    # I is the clamp current; I_syn the sum of the four ports' currents
+    assert np.allclose(r['trace'][200, names.index('I')], amp[probes], atol=1e-4)
+
+
 def test_iaf_psc_alpha_cells(cabi):
     """iaf_psc_alpha conventions (reset in the spike step, refractory for round(t_ref/dt) steps,
     V >= V_th fires, weight sign picks the excitatory / inhibitory alpha current): 600 cells of the

@@ -22,7 +22,7 @@ REF = os.environ.get('BMTK_REFERENCE', '/root/reference')
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, 'bmtk')), reason='reference tree not present')
 
 
-def _copy_example(tmp_path, example, config, tstop, dt, tag):
+def _copy_example(tmp_path, example, config, tstop, dt, tag, report=None):
     root = tmp_path / tag
     shutil.copytree(os.path.join(REF, 'examples', example), str(root / example))
     shutil.copytree(os.path.join(REF, 'examples', 'point_components'), str(root / 'point_components'))
@@ -37,6 +37,10 @@ def _copy_example(tmp_path, example, config, tstop, dt, tag):
             inp['amp'] = inp['amp'] * 3000.0
             inp['delay'] = inp['delay'] / 10.0
             inp['duration'] = inp['duration'] / 10.0
+    if report:
+        conf.setdefault('reports', {})['membrane_potential'] = {
+            'cells': {'population': 'v1', 'node_id': [0, 100, 200, 300, 400]}, 'variable_name': report,
+            'module': 'multimeter_report', 'file_name': 'membrane_potential.h5'}
     json.dump(conf, open(os.path.join(ex, 'config.short.json'), 'w'))
     return ex
 
@@ -115,14 +119,19 @@ def _read_outputs(ex):
     return out
 
 
-@pytest.mark.parametrize('example,config', [('point_450glifs', 'config.simulation.json'),
-                                            ('point_120cells', 'config.simulation.json'),
-                                            ('point_120cells', 'config.simulation_iclamp.json')])
-def test_reference_adapter_and_facade_build_the_same_network_and_files(tmp_path, monkeypatch, example, config):
+@pytest.mark.parametrize('example,config,report', [
+    ('point_450glifs', 'config.simulation.json', None),
+    ('point_120cells', 'config.simulation.json', None),
+    ('point_120cells', 'config.simulation_iclamp.json', None),
+    # a multimeter on another recordable, and on two at once (the reference then leaves the LAST variable's values
+    # in the file under the FIRST one's name)
+    ('point_450glifs', 'config.simulation.json', ['I_syn']),
+    ('point_450glifs', 'config.simulation.json', ['V_m', 'ASCurrents_sum'])])
+def test_reference_adapter_and_facade_build_the_same_network_and_files(tmp_path, monkeypatch, example, config, report):
     sys.path.insert(0, os.path.join(ROOT, 'tests'))
     dt, tstop = 0.1, 300.0
-    ex_ref = _copy_example(tmp_path, example, config, tstop, dt, 'ref')
-    ex_fac = _copy_example(tmp_path, example, config, tstop, dt, 'facade')
+    ex_ref = _copy_example(tmp_path, example, config, tstop, dt, 'ref', report)
+    ex_fac = _copy_example(tmp_path, example, config, tstop, dt, 'facade', report)
     ref = _run_reference(ex_ref)
     graph, sim = _run_facade(ex_fac, monkeypatch)
 
@@ -168,6 +177,9 @@ def test_reference_adapter_and_facade_build_the_same_network_and_files(tmp_path,
     assert n_spikes > 50
     if 'csv' in a:
         assert a['csv'] == b['csv'] and a['csv_header'] == b['csv_header']
+    if report:
+        assert 'report' in a and float(np.ptp(a['report']['v1']['data'])) > 0.0
+        assert a['report']['v1']['variable'] == b['report']['v1']['variable'] == report[0]
     if 'report' in a:
         for pop in a['report']:
             ra, rb = a['report'][pop], b['report'][pop]
