@@ -85,6 +85,7 @@ _SIGNATURES = {
     'bmtk_propagate_spikes': (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, _P, _P, _P, C.c_uint32, C.c_uint32, C.c_int, _P]),
     'bmtk_propagate_spikes_noalloc': (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, _P, _P, _P, C.c_uint32, C.c_uint32, _P]),
     'bmtk_probe_scatter_reductions': (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_int, C.POINTER(C.c_double)]),
+    'bmtk_generate_distance_edges': (C.c_int, [_P, C.c_int, C.c_uint64, _P, _P, _P, _P, _P, C.POINTER(C.c_uint64)]),
     'bmtk_engine_save_state': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_load_state': (C.c_int, [_P, C.c_char_p]),
     'bmtk_engine_p2p_pingpong': (C.c_int, [_P, C.c_int, C.c_int, C.c_uint32, C.POINTER(C.c_double)]),

@@ -331,6 +331,15 @@ struct bmtk_engine {
     // persistent stepping (single rank, atomic delivery)
     bool persistent = true, phase_timers = false, ring_prefetch = false;
     uint32_t tune = 0;
+    // Overflow of a fixed-capacity list inside a chunk: the chunk is replayed from a device-side copy of the state it
+    // started from, with the list that overflowed doubled (one rank; with several ranks capacities are part of the
+    // agreed exchange layout and the error is returned).
+    bool replay = true;
+    std::vector<void*> bk_arrays;      // copies of ckpt_arrays(), in that order
+    Ctl* d_bk_ctl = nullptr;
+    uint32_t last_overflow = 0;        // device flags of the last overflow drain() saw
+    uint64_t replays = 0;
+    bool pipe_demoted = false;         // this chunk is replayed with the two-phase kernel
     uint32_t pipe_blocks_opt = 0;   // option pipeline_blocks: fewer blocks than SMs (a small network needs few update warps,
                                     // and a hand-over over fewer blocks is cheaper)
     int persist_blocks = 0;
@@ -673,6 +682,113 @@ static int upload_inputs(bmtk_engine* e) {
     return BMTK_OK;
 }
 
+// The dynamic state of an engine: neuron state arrays and the ring buffer (what a checkpoint holds and what a
+// replayed chunk starts from again).
+struct CkptArray {
+    void* dev;
+    size_t bytes;
+};
+std::vector<CkptArray> ckpt_arrays(bmtk_engine* e) {
+    const size_t np = e->n_pad;
+    std::vector<CkptArray> v = {
+        {e->st.U, 4 * np}, {e->st.asc0, 4 * np}, {e->st.asc1, 4 * np}, {e->st.y1, 4 * np * kPorts},
+        {e->st.y2, 4 * np * kPorts}, {e->st.refr, 4 * np}, {e->ring, 4 * (size_t)e->ring_slots * kPorts * np}};
+    if (e->has_theta) {
+        v.push_back({e->st.th_spike, 4 * np});
+        v.push_back({e->st.th_voltage, 4 * np});
+    }
+    if (e->has_iext) v.push_back({e->st.i_ext, 4 * np});
+    return v;
+}
+
+// Copies the dynamic state and the control block aside (device to device) before a chunk runs.
+static int backup_state(bmtk_engine* e) {
+    const std::vector<CkptArray> arrs = ckpt_arrays(e);
+    if (e->bk_arrays.empty()) {
+        for (const CkptArray& a : arrs) {
+            void* p = nullptr;
+            CU(cudaMalloc(&p, a.bytes));
+            e->bk_arrays.push_back(p);
+        }
+        CU(cudaMalloc(&e->d_bk_ctl, sizeof(Ctl)));
+    }
+    for (size_t i = 0; i < arrs.size(); ++i)
+        CU(cudaMemcpyAsync(e->bk_arrays[i], arrs[i].dev, arrs[i].bytes, cudaMemcpyDeviceToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_bk_ctl, e->d_ctl, sizeof(Ctl), cudaMemcpyDeviceToDevice, e->stream));
+    return BMTK_OK;
+}
+
+static int realloc_dev(void** p, size_t bytes) {
+    cudaFree(*p);
+    *p = nullptr;
+    CU(cudaMalloc(p, bytes));
+    return BMTK_OK;
+}
+
+// After an overflow: the state the chunk started from comes back, the lists are emptied, the host clock is set
+// back by `chunk` steps, and whatever overflowed (device flags `f`, or the deterministic delivery's event list when
+// f == 0) is doubled.
+static int restore_and_grow(bmtk_engine* e, uint64_t chunk_start, uint32_t f) {
+    CU(cudaStreamSynchronize(e->stream));
+    const std::vector<CkptArray> arrs = ckpt_arrays(e);
+    for (size_t i = 0; i < arrs.size(); ++i)
+        CU(cudaMemcpyAsync(arrs[i].dev, e->bk_arrays[i], arrs[i].bytes, cudaMemcpyDeviceToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->d_ctl, e->d_bk_ctl, sizeof(Ctl), cudaMemcpyDeviceToDevice, e->stream));
+    e->step = chunk_start;
+    e->ce_next = 0;
+    while (e->ce_next < e->ce_step.size() && e->ce_step[e->ce_next] < e->step) ++e->ce_next;
+    e->ce_group_next = 0;
+    while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step) ++e->ce_group_next;
+    e->log_segmented = false;
+    drop_graph(e);
+    int rc = BMTK_OK;
+    if (f & kErrLogFull) {
+        if (e->log_cap * 2 >= (1ull << 32)) return fail(BMTK_E_OVERFLOW, "spike log cannot grow beyond 2^32 entries");
+        e->log_cap *= 2;
+        if ((rc = realloc_dev((void**)&e->d_log_stamp, 4 * e->log_cap))) return rc;
+        if ((rc = realloc_dev((void**)&e->d_log_id, 4 * e->log_cap))) return rc;
+        if ((rc = realloc_dev((void**)&e->d_log_keys, 8 * e->log_cap))) return rc;
+        if ((rc = realloc_dev((void**)&e->d_log_keys2, 8 * e->log_cap))) return rc;
+        e->log_tmp_bytes = spike_log_sort_tmp_bytes((uint32_t)e->log_cap);
+        if ((rc = realloc_dev(&e->d_log_tmp, e->log_tmp_bytes))) return rc;
+    }
+    if (f & kErrSpikeListFull) {
+        // the pipelined kernel's lists are per block and fixed: this chunk runs on the two-phase kernel, whose
+        // window list can grow
+        e->pipe_demoted = true;
+        if ((uint64_t)e->send_cap * 2 + 4 >= (1ull << 31)) return fail(BMTK_E_OVERFLOW, "spike list cannot grow further");
+        e->send_cap *= 2;
+        const size_t seg = (size_t)e->send_cap + 4;
+        if ((rc = realloc_dev((void**)&e->d_send, 4 * seg))) return rc;
+        for (int q = 0; q < 2; ++q)
+            if (e->d_plists[q] && (rc = realloc_dev((void**)&e->d_plists[q], sizeof(uint4) * (size_t)e->send_cap))) return rc;
+    }
+    if (f & kErrVirtListFull) {
+        e->virt_cap *= 2;
+        if ((rc = realloc_dev((void**)&e->d_virt, 4 * ((size_t)e->virt_cap + 4)))) return rc;
+        if (e->d_virt2 && (rc = realloc_dev((void**)&e->d_virt2, 4 * ((size_t)e->virt_cap + 4)))) return rc;
+    }
+    if (e->deterministic && (f == 0 || (f & (kErrSpikeListFull | kErrVirtListFull | kErrEventsFull)))) {
+        if (f == 0 || (f & kErrEventsFull)) e->event_cap *= 2;
+        if (e->event_cap >= (1ull << 31)) return fail(BMTK_E_OVERFLOW, "event list cannot grow beyond 2^31 entries");
+        det_free(e->det);
+        const uint64_t ring_cells = (uint64_t)e->ring_slots * kPorts * e->n_pad;
+        if (det_alloc(e->det, (uint32_t)e->event_cap, (uint32_t)((size_t)e->send_cap * e->n_ranks + e->virt_cap + 65536),
+                      ring_cells) != cudaSuccess)
+            return fail(BMTK_E_CUDA, "deterministic workspace could not grow");
+    }
+    // empty lists, and no descriptor of the failed attempt may be taken for one of the replay (same tags)
+    CU(cudaMemsetAsync(e->d_send, 0, 4 * ((size_t)e->send_cap + 4), e->stream));
+    if (e->d_virt) CU(cudaMemsetAsync(e->d_virt, 0, 4, e->stream));
+    if (e->d_virt2) CU(cudaMemsetAsync(e->d_virt2, 0, 4, e->stream));
+    if (e->d_plist_counts) CU(cudaMemsetAsync(e->d_plist_counts, 0, 8, e->stream));
+    if (e->d_pipe_seg) CU(cudaMemsetAsync(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap, e->stream));
+    if (e->d_log_seg_cnt) CU(cudaMemsetAsync(e->d_log_seg_cnt, 0, 4 * (size_t)e->pipe_blocks, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    ++e->replays;
+    return BMTK_OK;
+}
+
 // Brings counters, spike log and traces of the finished chunk to the host.
 static double now_ns() {
     return (double)std::chrono::duration_cast<std::chrono::nanoseconds>(
@@ -723,6 +839,7 @@ static int drain(bmtk_engine* e) {
     }
     if (h.error_flags) {
         const uint32_t f = h.error_flags;
+        e->last_overflow = f;
         CU(cudaMemsetAsync(&e->d_ctl->error_flags, 0, 4, e->stream));
         if (f & kErrSpikeListFull)
             return fail(BMTK_E_OVERFLOW, "window spike list full (capacity %u per rank; the persistent kernel also holds "
@@ -798,7 +915,7 @@ static int drain(bmtk_engine* e) {
 // with several ranks, when every rank can and none has clamp changes: the ranks must all run the same
 // exchange protocol.
 static bool use_pipelined(const bmtk_engine* e) {
-    if (!e->pipeline || !e->pipe_ok) return false;
+    if (!e->pipeline || !e->pipe_ok || e->pipe_demoted) return false;
     if (e->n_ranks == 1) return true;
     return e->p2p_ready && e->peers_pipe_ok && !e->any_iext;
 }
@@ -916,6 +1033,15 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
             const uint64_t room = (uint64_t)e->trace_cap * e->probe_interval;
             chunk = std::min<uint64_t>(chunk, std::max<uint64_t>(room - e->probe_interval + 1, 1));
         }
+        // one rank: keep what the chunk starts from, so that an overflow inside it can be answered by a replay
+        const bool can_replay = e->replay && e->n_ranks == 1;
+        const uint64_t chunk_start = e->step;
+        if (can_replay) {
+            rc = backup_state(e);
+            if (rc) return rc;
+        }
+        int attempts = 0;
+    again:
         uint64_t done = 0;
         const bool use_persistent = e->persistent && (e->n_ranks == 1 || e->p2p_ready) && !e->deterministic &&
                                     !e->profile && e->persist_blocks > 0;
@@ -939,6 +1065,14 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
                 e->launches += launches_per_window(e, w);
             } else {
                 rc = enqueue_window(e, w, false);
+                if (rc == BMTK_E_OVERFLOW && can_replay && attempts < 8) {
+                    // the deterministic delivery found more events in a window than its lists hold
+                    ++attempts;
+                    e->last_overflow = 0;
+                    rc = restore_and_grow(e, chunk_start, 0);
+                    if (rc) return rc;
+                    goto again;
+                }
                 if (rc) return rc;
             }
             e->step += w;
@@ -946,9 +1080,17 @@ static int run_steps(bmtk_engine* e, uint64_t n_steps) {
             while (e->ce_group_next < e->ce_group_step.size() && e->ce_group_step[e->ce_group_next] < e->step)
                 ++e->ce_group_next;
         }
-        left -= chunk;
         rc = drain(e);
+        if (rc == BMTK_E_OVERFLOW && can_replay && attempts < 8) {
+            ++attempts;
+            const std::string why = g_last_error;
+            rc = restore_and_grow(e, chunk_start, e->last_overflow);
+            if (rc) return rc;
+            goto again;
+        }
+        e->pipe_demoted = false;
         if (rc) return rc;
+        left -= chunk;
     }
     return BMTK_OK;
 }
@@ -1009,6 +1151,8 @@ int bmtk_engine_destroy(bmtk_engine* e) {
     cudaFree(e->d_pipe_seg);
     cudaFree(e->d_log_seg_cnt);
     cudaFree(e->d_blk_prof);
+    for (void* p : e->bk_arrays) cudaFree(p);
+    cudaFree(e->d_bk_ctl);
     cudaFree(e->d_pipe_sync);
     cudaFree(e->d_log_keys); cudaFree(e->d_log_keys2); cudaFree(e->d_log_tmp);
     for (uint32_t* p : e->h_spk_blocks) cudaFreeHost(p);
@@ -1180,6 +1324,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
         return BMTK_OK;
     }
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
+    if (k == "replay_on_overflow") { e->replay = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
     if (k == "tune") { e->tune = (uint32_t)value; return BMTK_OK; }
     if (k == "chunk_steps") {
@@ -1795,22 +1940,6 @@ struct CkptHeader {
     uint32_t n_pad, ring_slots, has_theta, has_iext;
     double dt;
 };
-struct CkptArray {
-    void* dev;
-    size_t bytes;
-};
-std::vector<CkptArray> ckpt_arrays(bmtk_engine* e) {
-    const size_t np = e->n_pad;
-    std::vector<CkptArray> v = {
-        {e->st.U, 4 * np}, {e->st.asc0, 4 * np}, {e->st.asc1, 4 * np}, {e->st.y1, 4 * np * kPorts},
-        {e->st.y2, 4 * np * kPorts}, {e->st.refr, 4 * np}, {e->ring, 4 * (size_t)e->ring_slots * kPorts * np}};
-    if (e->has_theta) {
-        v.push_back({e->st.th_spike, 4 * np});
-        v.push_back({e->st.th_voltage, 4 * np});
-    }
-    if (e->has_iext) v.push_back({e->st.i_ext, 4 * np});
-    return v;
-}
 }  // namespace
 
 // Reads the layout descriptor at the head of every mapped exchange buffer and compares it with this
@@ -2076,6 +2205,9 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "phase_rows_ns") *out = (uint64_t)e->phase_rows_ns;
     else if (k == "phase_remote_wait_ns") *out = (uint64_t)e->phase_remote_wait_ns;
     else if (k == "phase_remote_rows_ns") *out = (uint64_t)e->phase_remote_rows_ns;
+    else if (k == "replays") *out = e->replays;
+    else if (k == "log_capacity") *out = e->log_cap;
+    else if (k == "event_capacity") *out = e->event_cap;
     else if (k == "persistent_blocks") *out = (uint64_t)e->persist_blocks;
     else if (k == "persistent_resident") *out = e->persist_resident ? 1 : 0;
     else if (k == "pipeline_update_warps") *out = e->pipe_upd_warps;

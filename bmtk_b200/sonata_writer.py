@@ -4,8 +4,9 @@ driven from files, the way examples/point_450glifs is laid out. Stands in for bm
 path: the on-disk layout follows what the builder writes (groups /nodes/<pop>, /edges/<pop> with
 node_id / node_type_id / node_group_id / node_group_index, source_node_id / target_node_id with their
 node_population attribute, edge_type_id, edge_group_id / edge_group_index and a property group "0";
-builder/network_adaptors/dm_network.py:103-121,305-351) without the optional lookup indices
-(builder/index_builders.py:50-96), which no reader on this path needs.
+builder/network_adaptors/dm_network.py:103-121,305-351) including the lookup indices
+indices/{source_to_target, target_to_source}/{node_id_to_range, range_to_edge_id}
+(builder/index_builders.py:50-96) that every builder-written edges file carries.
 
 Everything is written with vectorised numpy through bmtk_b200.h5io (contiguous datasets), so the
 V1-scale workload (70 M edges, about 3.2 GB of edge columns) is a matter of disk bandwidth."""
@@ -16,6 +17,41 @@ import numpy as np
 
 from . import h5io
 from .pointnet.spike_trains import SpikeTrains
+
+
+def edge_index_tables(ids):
+    """The two tables of a SONATA edge lookup index over the column `ids` (source_node_id or target_node_id), as
+    builder/index_builders.py:50-96 builds them: runs of equal consecutive ids become rows (begin, end) of
+    range_to_edge_id, ordered by id (runs of one id in file order); row i of node_id_to_range is the block of
+    range_to_edge_id rows of node id i, (0, 0) for an id without edges, up to the largest id present.
+    Returns (node_id_to_range uint64[max_id + 1, 2], range_to_edge_id uint64[runs, 2])."""
+    ids = np.asarray(ids)
+    total = len(ids)
+    if total == 0:
+        return np.zeros((0, 2), dtype=np.uint64), np.zeros((0, 2), dtype=np.uint64)
+    cut = np.nonzero(np.diff(ids))[0] + 1
+    beg = np.concatenate(([0], cut))
+    end = np.concatenate((cut, [total]))
+    run_id = ids[beg]
+    order = np.argsort(run_id, kind='stable')      # pandas sort_values (quicksort) leaves ties in no defined order;
+    r2e = np.stack([beg[order], end[order]], axis=1).astype(np.uint64)   # file order is the natural choice
+    sorted_ids = run_id[order].astype(np.int64)
+    cut2 = np.nonzero(np.diff(sorted_ids))[0] + 1
+    b2 = np.concatenate(([0], cut2))
+    e2 = np.concatenate((cut2, [len(sorted_ids)]))
+    i2r = np.zeros((int(sorted_ids.max()) + 1, 2), dtype=np.uint64)
+    i2r[sorted_ids[b2], 0] = b2
+    i2r[sorted_ids[b2], 1] = e2
+    return i2r, r2e
+
+
+def write_edge_indices(pop_group, source_ids, target_ids):
+    """Adds indices/source_to_target and indices/target_to_source to an /edges/<population> group."""
+    for name, ids in (('source_to_target', source_ids), ('target_to_source', target_ids)):
+        i2r, r2e = edge_index_tables(ids)
+        g = pop_group.create_group('indices/' + name)
+        g.create_dataset('node_id_to_range', data=i2r)
+        g.create_dataset('range_to_edge_id', data=r2e)
 
 
 def write_project(net, root, with_report=True, iclamp=None, tstop=None, extra_output=None):
@@ -79,6 +115,7 @@ def write_project(net, root, with_report=True, iclamp=None, tstop=None, extra_ou
             g.create_dataset('0/syn_weight', data=net.weight[m].astype(np.float64))
             g.create_dataset('0/delay', data=net.delay_steps[m].astype(np.float64) * net.dt)
             g.create_dataset('0/nsyns', data=np.ones(int(m.sum()), dtype=np.uint32))
+            write_edge_indices(g, src_ids, inv[net.trg[m]])
         with open(os.path.join(root, 'network', types_fname), 'w') as f:
             f.write('edge_type_id target_query source_query model_template dynamics_params\n')
             for k in range(4):

@@ -318,6 +318,42 @@ int bmtk_engine_p2p_pingpong(bmtk_engine* e, int peer_rank, int initiator, uint3
  * n_blocks + 40. Shows whether a phase is long because one block is slow or because the hand-over is. */
 int bmtk_engine_block_profile(bmtk_engine* e, uint64_t cap_blocks, uint64_t* out4, uint64_t* n_blocks);
 
+/* Synthetic network generator on the device: the stand-in for bmtk.builder on this path (the reference builds its
+ * example networks on the host with per-pair connection rules, examples/point_450glifs/build_network.py, and writes
+ * them with bmtk/builder/network_adaptors/dm_network.py:103-121). Samples the incoming edges of the target neurons
+ * [lo, hi) of a distance-dependent network: per target a number of candidates with mean lambda[target type]; each
+ * candidate picks a source class with odds q_exc : q_inh, a Gaussian displacement of sigma[class][target type] taken
+ * from the 4096-quantile table gauss_table, the grid cell (side 1 / inv_cell, grid x grid cells over the square
+ * around the disk of `radius`) it lands in, is kept with probability cell_count / cell_max and given to a uniformly
+ * chosen neuron cell_ids[class][cell_start + i] of the cell; weight = w_base[source type][target type] x
+ * lognorm_table[.] (x -inh_scale for inhibitory sources), delay uniform in [delay_min_ms, delay_max_ms] rounded to
+ * dt steps, port = (source inhibitory) + 2 (target inhibitory). Randomness: Philox4x32-10, counters
+ * (target, candidate, 0 | 1, 0), key = seed; arithmetic is single IEEE operations in a fixed order, so the edge list is
+ * a pure function of the specification (independent of the partition into [lo, hi) blocks and of the device).
+ * Edges come out ordered by (target, candidate). Call with cap = 0 and src = NULL for the count, then with arrays of
+ * at least that many entries (host memory). All pointers in the specification are HOST arrays. */
+typedef struct bmtk_gen_spec {
+    uint32_t n_neurons, n_types, lo, hi;
+    const uint16_t* type_index;        /* [n_neurons] */
+    const uint8_t* type_is_inh;        /* [n_types] */
+    const float *x, *y;                /* [n_neurons] positions, um */
+    const float* sigma;                /* [2][n_types]: (source class, target type), um */
+    const float* w_base;               /* [n_types][n_types]: (source type, target type), pA */
+    const float *q_exc, *q_inh;        /* [n_types]: odds of an excitatory / inhibitory source by target type */
+    const float* lambda;               /* [n_types]: mean number of candidates per target */
+    const float *gauss_table, *lognorm_table;   /* [4096] each */
+    const uint32_t* cell_start[2];     /* [grid*grid] per source class */
+    const uint32_t* cell_count[2];
+    const uint32_t* cell_ids[2];       /* [class_size] neuron ids sorted by cell */
+    uint32_t class_size[2];
+    float cell_max[2];                 /* largest cell_count of the class */
+    uint32_t grid;
+    float radius, inv_cell, inh_scale, delay_min_ms, delay_max_ms, dt;
+    uint64_t seed;
+} bmtk_gen_spec;
+int bmtk_generate_distance_edges(const bmtk_gen_spec* spec, int device, uint64_t cap, uint32_t* src, uint32_t* trg, float* weight,
+                                 uint16_t* delay_steps, uint8_t* port, uint64_t* n_edges);
+
 /* Device-side timing of the engine's own stream (no counterpart in the reference): mark records a
  * CUDA event in one of 8 slots after everything enqueued so far; elapsed_ms waits for `to_slot`
  * and returns the device time between two marks. */

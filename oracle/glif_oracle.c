@@ -537,3 +537,81 @@ void orc_csr_by_source(int64_t n_rows, int64_t n_edges, const uint32_t* src, con
     }
     free(fill);
 }
+
+/* ---- CPU restatement of the device-side network generator (bmtk_b200/csrc/generate.cu): candidate k of target t
+ * owns the Philox counters (t, k, 0, 0) and (t, k, 1, 0); every floating-point step is one IEEE single-precision
+ * operation in the order written here (fmaf where the device fuses), so the edge list is identical bit for bit.
+ * The reference has no counterpart (bmtk.builder evaluates Python connection rules per node pair,
+ * examples/point_450glifs/build_network.py); this is the checker of the synthetic stand-in. */
+typedef struct {
+    uint32_t n_neurons, n_types, lo, hi;
+    const uint16_t* type_index;
+    const uint8_t* type_is_inh;
+    const float *x, *y;
+    const float* sigma;
+    const float* w_base;
+    const float *q_exc, *q_inh;
+    const float* lambda;
+    const float *gauss_table, *lognorm_table;
+    const uint32_t* cell_start[2];
+    const uint32_t* cell_count[2];
+    const uint32_t* cell_ids[2];
+    uint32_t class_size[2];
+    float cell_max[2];
+    uint32_t grid;
+    float radius, inv_cell, inh_scale, delay_min_ms, delay_max_ms, dt;
+    uint64_t seed;
+} orc_gen_spec;
+
+static float gen_u24(uint32_t r) { return (float)(r >> 8) * 5.9604644775390625e-08f; }
+
+int64_t orc_generate_distance_edges(const orc_gen_spec* g, int64_t cap, uint32_t* src, uint32_t* trg, float* weight,
+                                    uint16_t* delay, uint8_t* port)
+{
+    const uint32_t key[2] = { (uint32_t)g->seed, (uint32_t)(g->seed >> 32) };
+    int64_t n = 0;
+    for (uint32_t t = g->lo; t < g->hi; ++t) {
+        const uint32_t tt = g->type_index[t];
+        const float lam = g->lambda[tt];
+        const uint32_t base = (uint32_t)lam;
+        uint32_t r[4];
+        const uint32_t c0[4] = { t, 0xffffffffu, 2u, 0u };
+        orc_philox4x32_10(c0, key, r);
+        const uint32_t K = base + (gen_u24(r[0]) < lam - (float)base ? 1u : 0u);
+        for (uint32_t k = 0; k < K; ++k) {
+            uint32_t a[4], b[4];
+            const uint32_t ca[4] = { t, k, 0u, 0u }, cb[4] = { t, k, 1u, 0u };
+            orc_philox4x32_10(ca, key, a);
+            orc_philox4x32_10(cb, key, b);
+            const float qe = g->q_exc[tt], qi = g->q_inh[tt];
+            const uint32_t sc = gen_u24(a[0]) * (qe + qi) >= qe ? 1u : 0u;
+            const float sg = g->sigma[sc * g->n_types + tt];
+            const float px = fmaf(g->gauss_table[a[1] >> 20], sg, g->x[t]);
+            const float py = fmaf(g->gauss_table[a[2] >> 20], sg, g->y[t]);
+            const float R = g->radius;
+            if (!(fmaf(px, px, py * py) < R * R)) continue;
+            const int cx = (int)floorf((px + R) * g->inv_cell), cy = (int)floorf((py + R) * g->inv_cell);
+            if (cx < 0 || cy < 0 || cx >= (int)g->grid || cy >= (int)g->grid) continue;
+            const uint32_t cell = (uint32_t)cx * g->grid + (uint32_t)cy;
+            const uint32_t cn = g->cell_count[sc][cell];
+            if (!(gen_u24(a[3]) * g->cell_max[sc] < (float)cn)) continue;
+            uint32_t pick = (uint32_t)(gen_u24(b[0]) * (float)cn);
+            if (pick >= cn) pick = cn - 1u;
+            const uint32_t s = g->cell_ids[sc][g->cell_start[sc][cell] + pick];
+            if (s == t) continue;
+            const uint32_t st = g->type_index[s];
+            float w = g->w_base[st * g->n_types + tt] * g->lognorm_table[b[1] >> 20];
+            const int s_inh = g->type_is_inh[st] != 0, t_inh = g->type_is_inh[tt] != 0;
+            if (s_inh) w = w * -g->inh_scale;
+            const float d_ms = fmaf(gen_u24(b[2]), g->delay_max_ms - g->delay_min_ms, g->delay_min_ms);
+            const float d_steps = rintf(d_ms / g->dt);
+            if (n < cap) {
+                src[n] = s; trg[n] = t; weight[n] = w;
+                delay[n] = (uint16_t)(d_steps < 1.f ? 1.f : d_steps);
+                port[n] = (uint8_t)(s_inh + 2 * t_inh);
+            }
+            ++n;
+        }
+    }
+    return n;
+}

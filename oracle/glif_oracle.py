@@ -387,3 +387,20 @@ class OracleSim:
     def v_m(self):
         e_l = np.array([t.E_L for t in self.types])
         return self.U + e_l[self.type_index]
+
+
+def generate_distance_edges(spec, lo=0, hi=None):
+    """CPU restatement of the device-side network generator: the edges into targets [lo, hi) of the specification
+    made by bmtk_b200.generator.distance_spec, as (src, trg, weight, delay_steps, port)."""
+    from bmtk_b200.generator import GenSpec, as_struct
+    L = lib()
+    L.orc_generate_distance_edges.restype = C.c_int64
+    L.orc_generate_distance_edges.argtypes = [C.c_void_p, C.c_int64] + [C.c_void_p] * 5
+    hi = spec['n_neurons'] if hi is None else hi
+    s = as_struct(spec, lo, hi, GenSpec)          # orc_gen_spec has the same layout
+    n = L.orc_generate_distance_edges(C.byref(s), 0, None, None, None, None, None)
+    src, trg = np.empty(n, dtype=np.uint32), np.empty(n, dtype=np.uint32)
+    w, d, p = np.empty(n, dtype=np.float32), np.empty(n, dtype=np.uint16), np.empty(n, dtype=np.uint8)
+    m = L.orc_generate_distance_edges(C.byref(s), n, _ptr(src), _ptr(trg), _ptr(w), _ptr(d), _ptr(p))
+    assert m == n
+    return src, trg, w, d, p

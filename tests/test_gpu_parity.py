@@ -358,10 +358,38 @@ def test_empty_networks(cabi):
 def test_spike_list_overflow_is_reported_not_fatal(cabi):
     from bmtk_b200._cabi import EngineError
     net = W.c1(n=4096, t_stop_ms=300.0)
-    eng = W.build_engine(net, options=dict(spike_capacity=4, window=16, persistent=0))
+    eng = W.build_engine(net, options=dict(spike_capacity=4, window=16, persistent=0, replay_on_overflow=0))
     with pytest.raises(EngineError) as ei:
         eng.run(net.n_steps)
     assert 'spike list full' in str(ei.value)
+
+
+@pytest.mark.parametrize('mode', ['per_step', 'two_phase', 'pipelined', 'deterministic'])
+def test_overflow_is_answered_by_growing_the_list_and_replaying_the_chunk(cabi, mode):
+    """Lists that are too small for the activity (window spike list, spike log, event list of the deterministic
+    delivery) no longer end the run: the chunk in which one overflowed starts again from the state it began with,
+    with that list doubled, until it fits. The result equals a run whose lists were large enough from the start,
+    bit for bit (weights on a 0.25 pA grid make the atomic sums exact)."""
+    net = W.c0(t_stop_ms=120.0, input_gain=30.0)     # ~1700 spikes, up to 32 in one 10-step window, ~680 events per window
+    net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+    opts = dict(per_step=dict(persistent=0), two_phase=dict(pipeline=0), pipelined=dict(), deterministic=dict())[mode]
+    det = mode == 'deterministic'
+    small = dict(opts, chunk_steps=1200, log_capacity=1024, spike_capacity=8)
+    if det:
+        small['event_capacity'] = 1024
+    roomy = W.build_engine(net, deterministic=det, options=dict(opts, chunk_steps=1200))
+    roomy.run(net.n_steps)
+    tight = W.build_engine(net, deterministic=det, options=small)
+    tight.run(net.n_steps)
+    assert roomy.counter('replays') == 0 and tight.counter('replays') >= 1
+    a, b = roomy.fetch_spikes(), tight.fetch_spikes()
+    assert len(a[0]) > 1200
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    assert np.array_equal(roomy.fetch_trace().view(np.uint32), tight.fetch_trace().view(np.uint32))
+    for c in ('events', 'spikes', 'input_spikes', 'steps'):
+        assert roomy.counter(c) == tight.counter(c), c
+    for var in ('U', 'asc0', 'y1_0', 'refr'):
+        assert np.array_equal(roomy.state(var).view(np.uint32), tight.state(var).view(np.uint32)), var
 
 
 def _point450():

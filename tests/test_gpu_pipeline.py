@@ -89,7 +89,7 @@ def test_pipelined_log_overflow_is_reported_and_reserve_is_harmless(cabi):
     reported as an error (nothing traps), and pinning the host store ahead changes no result."""
     from bmtk_b200._cabi import EngineError
     net = _grid_weights(W.c2(n=4000, in_degree=100, n_virtual=100, t_stop_ms=100.0, input_weight=90.0))
-    eng = W.build_engine(net, options=dict(pipeline=1, log_capacity=2048))
+    eng = W.build_engine(net, options=dict(pipeline=1, log_capacity=2048, replay_on_overflow=0))
     assert eng.counter('pipelined') == 1
     with pytest.raises(EngineError) as ei:
         eng.run(net.n_steps)

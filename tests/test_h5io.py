@@ -129,3 +129,49 @@ def test_rejects_foreign_files(tmp_path):
     p.write_bytes(b'not hdf5 at all')
     with pytest.raises(IOError):
         h5io.File(str(p), 'r')
+
+
+def test_edge_lookup_indices_equal_the_builders(tmp_path):
+    """The index tables written next to the edges (indices/source_to_target, indices/target_to_source) re-derived
+    from the id columns of the reference's own builder-written files must equal the tables stored in those files."""
+    import glob
+    from bmtk_b200.sonata_writer import edge_index_tables, write_edge_indices
+    ref = os.environ.get('BMTK_REFERENCE', '/root/reference')
+    files = sorted(glob.glob(os.path.join(ref, 'examples', 'point_450glifs', 'network', '*_edges.h5')) +
+                   glob.glob(os.path.join(ref, 'examples', 'point_120cells', 'network', '*_edges.h5')))
+    if not files:
+        pytest.skip('reference tree not present')
+    checked = 0
+    for path in files:
+        with h5io.File(path, 'r') as h:
+            for pop in h['/edges'].keys():
+                g = h['/edges'][pop]
+                if 'indices' not in g:
+                    continue
+                for name, col in (('source_to_target', 'source_node_id'), ('target_to_source', 'target_node_id')):
+                    i2r, r2e = edge_index_tables(g[col][()])
+                    want_i2r = g['indices'][name]['node_id_to_range'][()]
+                    want_r2e = g['indices'][name]['range_to_edge_id'][()]
+                    assert np.array_equal(i2r, want_i2r) and i2r.dtype == want_i2r.dtype
+                    # rows of one node id hold the same set of ranges (the builder's sort leaves their order open)
+                    assert r2e.shape == want_r2e.shape
+                    for b, e in i2r[:200]:
+                        assert sorted(map(tuple, r2e[int(b):int(e)])) == sorted(map(tuple, want_r2e[int(b):int(e)]))
+                    checked += 1
+    assert checked >= 4
+    # and through the writer: the groups exist and describe the columns
+    src = np.array([3, 3, 0, 0, 0, 3, 5], dtype=np.uint64)
+    trg = np.array([1, 1, 1, 2, 2, 2, 0], dtype=np.uint64)
+    p = str(tmp_path / 'e.h5')
+    with h5io.File(p, 'w') as h:
+        g = h.create_group('/edges/a_to_b')
+        g.create_dataset('source_node_id', data=src)
+        g.create_dataset('target_node_id', data=trg)
+        write_edge_indices(g, src, trg)
+    with h5io.File(p, 'r') as h:
+        s2t = h['/edges/a_to_b/indices/source_to_target']
+        assert s2t['node_id_to_range'][()].tolist() == [[0, 1], [0, 0], [0, 0], [1, 3], [0, 0], [3, 4]]
+        assert s2t['range_to_edge_id'][()].tolist() == [[2, 5], [0, 2], [5, 6], [6, 7]]
+        t2s = h['/edges/a_to_b/indices/target_to_source']
+        assert t2s['node_id_to_range'][()].tolist() == [[0, 1], [1, 2], [2, 3]]
+        assert t2s['range_to_edge_id'][()].tolist() == [[6, 7], [0, 3], [3, 6]]
