@@ -175,16 +175,16 @@ __global__ void snapshot_kernel(Ctl* ctl, uint32_t step_in_window, uint32_t inte
             float x;
             switch ((vars >> (4u * v)) & 15u) {   // the same expressions as Neuron4::probe_value
                 case BMTK_VAR_I_SYN:
-                    x = ((st.y2[i] + st.y2[(size_t)n_pad + i]) + st.y2[2 * (size_t)n_pad + i]) + st.y2[3 * (size_t)n_pad + i];
+                    x = __fadd_rn(__fadd_rn(__fadd_rn(st.y2[i], st.y2[(size_t)n_pad + i]), st.y2[2 * (size_t)n_pad + i]), st.y2[3 * (size_t)n_pad + i]);
                     break;
-                case BMTK_VAR_ASC_SUM: x = c.asc_rec[0] * st.asc0[i] + c.asc_rec[1] * st.asc1[i]; break;
+                case BMTK_VAR_ASC_SUM: x = __fmaf_rn(c.asc_rec[0], st.asc0[i], __fmul_rn(c.asc_rec[1], st.asc1[i])); break;
                 case BMTK_VAR_THRESHOLD:
-                    x = (c.th_inf + (st.th_spike ? st.th_spike[i] : 0.f) + (st.th_voltage ? st.th_voltage[i] : 0.f)) + c.E_L;
+                    x = __fadd_rn(__fadd_rn(__fadd_rn(c.th_inf, st.th_spike ? st.th_spike[i] : 0.f), st.th_voltage ? st.th_voltage[i] : 0.f), c.E_L);
                     break;
                 case BMTK_VAR_TH_SPIKE: x = st.th_spike ? st.th_spike[i] : 0.f; break;
                 case BMTK_VAR_TH_VOLTAGE: x = st.th_voltage ? st.th_voltage[i] : 0.f; break;
-                case BMTK_VAR_I: x = (st.i_ext ? st.i_ext[i] : 0.f) + c.i_e; break;
-                default: x = st.U[i] + c.E_L;
+                case BMTK_VAR_I: x = __fadd_rn(st.i_ext ? st.i_ext[i] : 0.f, c.i_e); break;
+                default: x = __fadd_rn(st.U[i], c.E_L);
             }
             trace[((size_t)sample * n_vars + v) * n_ids + q] = x;
         }
@@ -1609,7 +1609,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
         if (!coop || blocks > 512) e->persist_blocks = 0;
         if (e->persist_blocks > 0 && e->n_trials == 1 && e->window >= 2 && e->n_edges < (1ull << 32)) {
-            int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt));
+            int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt, pipelined_warps() - 1u));   // the most a block can need
             if (pb > 0 && e->pipe_blocks_opt) pb = std::min<int>(pb, (int)e->pipe_blocks_opt);
             if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
                 // chunks of 32 groups are dealt round-robin to the update warps of the blocks

@@ -160,7 +160,7 @@ int bmtk_generate_distance_edges(const bmtk_gen_spec* spec, int device, uint64_t
         void* d = nullptr;
         if (cudaMalloc(&d, bytes ? bytes : 4) != cudaSuccess) return nullptr;
         owned.push_back(d);
-        if (bytes && cudaMemcpy(d, h, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+        if (h && bytes && cudaMemcpy(d, h, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
         return d;
     };
     auto cleanup = [&]() { for (void* p : owned) cudaFree(p); };

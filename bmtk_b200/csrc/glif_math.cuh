@@ -65,13 +65,13 @@ struct Neuron4 {
     // Recordable `code` (BMTK_VAR_*) of neuron j after a step.
     __device__ __forceinline__ float probe_value(const TypeConsts& c, int j, uint32_t code) const {
         switch (code) {
-            case BMTK_VAR_I_SYN: return ((y2[0].v[j] + y2[1].v[j]) + y2[2].v[j]) + y2[3].v[j];
-            case BMTK_VAR_ASC_SUM: return c.asc_rec[0] * a0.v[j] + c.asc_rec[1] * a1.v[j];
-            case BMTK_VAR_THRESHOLD: return (c.th_inf + ths.v[j] + thv.v[j]) + c.E_L;
+            case BMTK_VAR_I_SYN: return __fadd_rn(__fadd_rn(__fadd_rn(y2[0].v[j], y2[1].v[j]), y2[2].v[j]), y2[3].v[j]);
+            case BMTK_VAR_ASC_SUM: return __fmaf_rn(c.asc_rec[0], a0.v[j], __fmul_rn(c.asc_rec[1], a1.v[j]));
+            case BMTK_VAR_THRESHOLD: return __fadd_rn(__fadd_rn(__fadd_rn(c.th_inf, ths.v[j]), thv.v[j]), c.E_L);
             case BMTK_VAR_TH_SPIKE: return ths.v[j];
             case BMTK_VAR_TH_VOLTAGE: return thv.v[j];
-            case BMTK_VAR_I: return iex.v[j] + c.i_e;
-            default: return U.v[j] + c.E_L;
+            case BMTK_VAR_I: return __fadd_rn(iex.v[j], c.i_e);
+            default: return __fadd_rn(U.v[j], c.E_L);
         }
     }
 
@@ -90,36 +90,41 @@ struct Neuron4 {
             const bool ends = refr && rf_dec == 0;   // glif_psc resets on the step the countdown ends
             const bool sdt = THETA && (c.flags & 1);  // spike-dependent threshold
 
-            // ---- integrating neuron
-            const float asc_sum = c.asc_coeff[0] * a0.v[j] + c.asc_coeff[1] * a1.v[j];
-            const float drive = iex.v[j] + c.i_e + asc_sum;
-            float u_int = v_old * c.P33 + drive * c.P30;
+            // ---- integrating neuron. Every floating-point step below is ONE IEEE-754 single-precision operation in
+            // the order written (fused multiply-adds where named so): the compiler may not contract or reorder them,
+            // and a CPU restatement with fmaf() reproduces the state bit for bit.
+            const float asc_sum = __fmaf_rn(c.asc_coeff[0], a0.v[j], __fmul_rn(c.asc_coeff[1], a1.v[j]));
+            const float drive = __fadd_rn(__fadd_rn(iex.v[j], c.i_e), asc_sum);
+            float u_int = __fmaf_rn(v_old, c.P33, __fmul_rn(drive, c.P30));
 #pragma unroll
-            for (int p = 0; p < kPorts; ++p) u_int += c.P31[p] * y1[p].v[j] + c.P32[p] * y2[p].v[j];
+            for (int p = 0; p < kPorts; ++p)
+                u_int = __fadd_rn(u_int, __fmaf_rn(c.P31[p], y1[p].v[j], __fmul_rn(c.P32[p], y2[p].v[j])));
             // iaf_psc_delta: what arrives in this step is a jump of V (its ports have P31 = P32 = psc_init = 0)
-            u_int += c.delta_gain * ((in[0].v[j] + in[1].v[j]) + (in[2].v[j] + in[3].v[j]));
+            u_int = __fmaf_rn(c.delta_gain, __fadd_rn(__fadd_rn(in[0].v[j], in[1].v[j]), __fadd_rn(in[2].v[j], in[3].v[j])), u_int);
             float th = c.th_inf;
             float ths_int = ths.v[j], thv_int = thv.v[j];
             if (THETA) {
-                if (sdt) ths_int = ths.v[j] * c.theta_spike_decay;
+                if (sdt) ths_int = __fmul_rn(ths.v[j], c.theta_spike_decay);
                 if (c.flags & 2) {
-                    const float beta = drive * c.inv_G;
-                    const float d = c.phi * (v_old - beta);
-                    thv_int = d * c.P33 + c.theta_voltage_decay * (thv.v[j] - d - c.abpara * beta) + c.abpara * beta;
+                    const float beta = __fmul_rn(drive, c.inv_G);
+                    const float d = __fmul_rn(c.phi, __fsub_rn(v_old, beta));
+                    const float ab = __fmul_rn(c.abpara, beta);
+                    const float rest = __fsub_rn(__fsub_rn(thv.v[j], d), ab);
+                    thv_int = __fadd_rn(__fmaf_rn(c.theta_voltage_decay, rest, __fmul_rn(d, c.P33)), ab);
                 }
-                th += ths_int + thv_int;
+                th = __fadd_rn(th, __fadd_rn(ths_int, thv_int));
             }
             const bool fire = !refr && ((c.flags & 8) ? (u_int >= th) : (u_int > th));
             if ((c.flags & 4) && fire) u_int = c.v_reset;   // iaf_psc_alpha: reset in the spike step
 
             // ---- refractory neuron: V is held; after-spike currents and V change when the countdown ends
-            const float u_end = sdt ? c.reset_fraction * v_old + c.reset_add : c.v_reset;
+            const float u_end = sdt ? __fmaf_rn(c.reset_fraction, v_old, c.reset_add) : c.v_reset;
 
             U.v[j] = refr ? (ends ? u_end : v_old) : u_int;
-            a0.v[j] = refr ? (ends ? c.asc_amps[0] + a0.v[j] * c.asc_refr[0] : a0.v[j]) : a0.v[j] * c.asc_decay[0];
-            a1.v[j] = refr ? (ends ? c.asc_amps[1] + a1.v[j] * c.asc_refr[1] : a1.v[j]) : a1.v[j] * c.asc_decay[1];
+            a0.v[j] = refr ? (ends ? __fmaf_rn(a0.v[j], c.asc_refr[0], c.asc_amps[0]) : a0.v[j]) : __fmul_rn(a0.v[j], c.asc_decay[0]);
+            a1.v[j] = refr ? (ends ? __fmaf_rn(a1.v[j], c.asc_refr[1], c.asc_amps[1]) : a1.v[j]) : __fmul_rn(a1.v[j], c.asc_decay[1]);
             if (THETA) {
-                ths.v[j] = refr ? ((ends && sdt) ? ths.v[j] * c.theta_spike_refr + c.th_spike_add : ths.v[j]) : ths_int;
+                ths.v[j] = refr ? ((ends && sdt) ? __fmaf_rn(ths.v[j], c.theta_spike_refr, c.th_spike_add) : ths.v[j]) : ths_int;
                 thv.v[j] = refr ? thv.v[j] : thv_int;
             }
             rf[j] = refr ? rf_dec : (fire ? c.n_ref : rf[j]);
@@ -127,8 +132,8 @@ struct Neuron4 {
 #pragma unroll
             for (int p = 0; p < kPorts; ++p) {
                 const float y1o = y1[p].v[j];
-                y2[p].v[j] = c.P21[p] * y1o + c.P11[p] * y2[p].v[j];
-                y1[p].v[j] = c.P11[p] * y1o + c.psc_init[p] * in[p].v[j];
+                y2[p].v[j] = __fmaf_rn(c.P21[p], y1o, __fmul_rn(c.P11[p], y2[p].v[j]));
+                y1[p].v[j] = __fmaf_rn(c.P11[p], y1o, __fmul_rn(c.psc_init[p], in[p].v[j]));
             }
         }
         return mask;

@@ -3,20 +3,24 @@
 // One block of 20 warps per SM stays resident for a whole chunk of steps (cooperative launch, so that
 // all blocks are co-resident). The first warps ("update warps", as many as the network needs at 128
 // neurons per warp) own four neurons per thread, state in registers for the whole launch; one or more
-// "input warps" draw the Poisson cells / pick up the replayed virtual spikes; the remaining "chunk
-// warps" stream CSR rows into the ring. Time is cut into phases of h = floor(min_delay / 2) steps. In
-// phase p
+// "input warps" draw the Poisson cells / pick up the replayed virtual spikes and queue the block's own
+// spikes; with several ranks one "sender warp" stores the block's spikes into the other ranks' exchange
+// buffers; the remaining "chunk warps" stream CSR rows into the ring. Time is cut into phases of
+// h = floor(min_delay / 2) steps. In phase p
 //   * the update warps run the phase's h steps back to back (ring slot in, state update, slot
-//     cleared where it received input); a spike is cut into chunks of at most 256 CSR entries whose
-//     descriptors {first entry, length, ring slot of emission, phase tag} go to the block's segment of
-//     a list, at a position taken from a SHARED-memory counter (no global atomic on the update path);
-//   * the input warps add the chunks of the phase's input spikes to the same list;
-//   * the chunk warps deliver the list of phase p-1, sharing it with their neighbours: chunk j of
-//     block b is delivered by chunk warp j mod D of block b + j / D (D chunk warps per block), so a busy
-//     block's spikes spill over to the following SMs. The first D descriptors of a block stay in its
-//     shared memory; the neighbours' carry the tag of their phase, so a warp simply loads the few slots
-//     it is responsible for (one round trip, no counts to read first) and keeps those with the right
-//     tag; up to 8 entries per lane are in flight.
+//     cleared where it received input); a firing lane only appends the spike to a shared-memory list;
+//   * the input warps add the chunks of the phase's input spikes to the block's segment of the phase's
+//     chunk list (descriptors {first entry, length, ring slot of emission, phase tag}, at most 256 CSR
+//     entries each, at positions from a SHARED-memory counter), write the spike log of phase p-1 and,
+//     once the update warps have arrived at their named barrier, cut the rows of the block's spiking
+//     neurons into chunks as well;
+//   * the chunk warps deliver the list of phase p-1, sharing it with their neighbours: chunk j < D of
+//     block b is delivered by chunk warp j of block b, chunk D r + i by warp D-1-i of block b + r (D chunk
+//     warps per block), so a busy block's spikes spill over to the following SMs. The first D descriptors
+//     of a block stay in its shared memory; the neighbours' carry the tag of their phase, so a warp simply
+//     loads the few slots it is responsible for (one round trip, no counts to read first) and keeps those
+//     with the right tag. A warp copies the entries of all its chunks to shared memory with asynchronous
+//     copies (all in flight together) and applies them from there.
 // Whatever is emitted in phase p is due min_delay >= 2h steps later, i.e. not before phase p+2 begins,
 // so delivering it during phase p+1 neither touches a ring slot that phase reads nor arrives late.
 // Compared with update -> barrier -> deliver -> barrier per window, the two latency chains (ring slot
@@ -43,8 +47,7 @@ namespace bmtk {
 constexpr int kBT = 640;
 constexpr int kWarps = kBT / 32;
 constexpr int kMaxUpdWarps = 16;
-constexpr int kInFlight = 8;         // row entries each delivery lane has in flight (more spills registers: slower)
-constexpr uint32_t kChunk = 32 * kInFlight;   // entries of one chunk: one round of one delivery warp
+constexpr uint32_t kChunk = 256;    // entries of one chunk: the unit of work of one delivery warp (8 per lane)
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
 constexpr uint32_t kSpill = 4;      // a block's chunks kDW*r .. kDW*r + kDW-1 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
@@ -53,6 +56,7 @@ struct __align__(16) PipeShared {
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
     uint32_t pad;
     uint4 own[3][kWarps];      // copies of the first descriptors of list L: the ones this block delivers itself
+    uint4 sdesc[kWarps][4];    // descriptors of the chunks a warp has staged (see Stager)
     uint2 rows[kMaxUpdWarps * 32 * kNeuronsPerThread];   // {row begin, row length} of this block's neurons
     uint32_t pend[2][kPendP];       // step in phase << kSrcBits | id
 };
@@ -189,35 +193,66 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
     }
 }
 
-// Streams one chunk into the ring with one warp: up to kInFlight entries per lane in flight.
-__device__ __forceinline__ void stream_chunk(const PersistArgs& a, const uint4 d, uint32_t lane) {
-    // a descriptor that does not describe a piece of the CSR is not followed (it would mean a list was read
-    // before it was complete): the launch goes on and the host reports the error
+// ---- staged streaming: a warp that has several chunks to deliver (its own, a neighbour's spill-over, the rows of
+// remote spikes) would pay one DRAM round trip per chunk if it streamed them one after the other, and holding two
+// chunks' entries in registers spills. Instead the entries of up to kStage chunks are copied to the warp's own piece
+// of shared memory with asynchronous copies (no registers, all in flight together) and applied from there as each
+// copy group lands.
+constexpr int kStage = 3;
+struct Stager {
+    uint2* buf;       // [kStage][kChunk] of this warp
+    uint4* desc;      // [kStage]
+    uint32_t m;       // chunks staged and not yet applied
+};
+
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(sa), "l"(gmem) : "memory");
+}
+
+__device__ __forceinline__ void stage_flush(const PersistArgs& a, Stager& s, uint32_t lane) {
+    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
+    const size_t plane = (size_t)a.n_pad;
+    for (uint32_t i = 0; i < s.m; ++i) {
+        switch (s.m - 1u - i) {   // copy groups still allowed in flight: those of the chunks behind this one
+            case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+            case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+            default: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        }
+        __syncwarp();
+        const uint4 d = s.desc[i];
+        const uint2* src = s.buf + i * kChunk;
+        for (uint32_t u = lane; u < d.y; u += 32u) {   // a lane applies the entries it copied itself
+            const uint2 e = src[u];
+            uint32_t slot = d.z + (e.x >> (tb + 2));
+            if (slot >= a.ring_slots) slot -= a.ring_slots;
+            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+        }
+    }
+    __syncwarp();
+    s.m = 0;
+}
+
+__device__ __forceinline__ void stage_add(const PersistArgs& a, Stager& s, const uint4 d, uint32_t lane) {
     if ((unsigned long long)d.x + d.y > a.n_entries || d.y > kChunk || d.z >= a.ring_slots) {
         if (lane == 0) atomicOr(&a.ctl->error_flags, kErrBadChunk);
         return;
     }
-    const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
-    const size_t plane = (size_t)a.n_pad;
-    uint2 e[kInFlight];
-#pragma unroll
-    for (int u = 0; u < kInFlight; ++u)
-        if (lane + 32u * u < d.y) e[u] = __ldg(&a.entries[d.x + lane + 32u * u]);
-#pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
-        if (lane + 32u * u < d.y) {
-            uint32_t slot = d.z + (e[u].x >> (tb + 2));
-            if (slot >= a.ring_slots) slot -= a.ring_slots;
-            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e[u].x >> tb) & 3u)) * plane + (e[u].x & tmask),
-                      __uint_as_float(e[u].y));
-        }
-    }
+    uint2* dst = s.buf + s.m * kChunk;
+    for (uint32_t u = lane; u < d.y; u += 32u) cp_async8(dst + u, a.entries + d.x + u);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (lane == 0) s.desc[s.m] = d;
+    if (++s.m == (uint32_t)kStage) stage_flush(a, s, lane);
+}
+
+__device__ __forceinline__ void deliver_chunk(const PersistArgs& a, Stager& s, const uint4 d, uint32_t lane) {
+    stage_add(a, s, d, lane);
 }
 
 // Delivery of list L (written in the phase with tag `tag`) by warp `w` of this block's delivery
 // warps: chunk kDW*r + w of block b - r for r < kSpill, found by their tag, then this block's own
 // chunks beyond kDW * kSpill. Called by whole warps.
-__device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t w,
+__device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& sh, Stager& sg, uint32_t L, uint32_t tag, uint32_t w,
                                              uint32_t lane, DeliveryTotals& tot) {
     const uint32_t G = gridDim.x, kDW = chunk_warps(a);
     // the neighbours' descriptors are requested first, then this block's own chunk (descriptor in shared
@@ -233,7 +268,7 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
     if (w < min(sh.chunks[L], a.pipe_seg_cap)) {
         const uint4 c = sh.own[L][w];
         events += c.y;
-        stream_chunk(a, c, lane);
+        deliver_chunk(a, sg, c, lane);
     }
     uint32_t valid = __ballot_sync(0xffffffffu, lane >= 1 && lane < kSpill && lane < G && d.w == tag);
     while (valid) {
@@ -245,7 +280,7 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
         c.z = __shfl_sync(0xffffffffu, d.z, r);
         c.w = tag;
         events += c.y;
-        stream_chunk(a, c, lane);
+        deliver_chunk(a, sg, c, lane);
     }
     // a block with more than kDW * kSpill chunks (or fewer blocks than kSpill) keeps the rest
     const uint32_t n_own = min(sh.chunks[L], a.pipe_seg_cap);
@@ -253,7 +288,7 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
     for (uint32_t j = first + w; j < n_own; j += kDW) {
         const uint4 c = __ldcg(a.pipe_seg + ((size_t)L * G + blockIdx.x) * a.pipe_seg_cap + j);
         events += c.y;
-        stream_chunk(a, c, lane);
+        deliver_chunk(a, sg, c, lane);
     }
     if (lane == 0) tot.events += events;
 }
@@ -265,7 +300,7 @@ __device__ __forceinline__ void deliver_list(const PersistArgs& a, PipeShared& s
 // dealing every rank's entries separately would leave warp 0 with a row of every rank and the others idle. For
 // its entry the warp waits for the entry's tag (its store may trail the count word), looks up the row of the
 // spiking neuron in THIS rank's CSR (all sources have a row, the targets are local) and streams it.
-__device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, uint32_t k, uint32_t tag, uint32_t prev_slot,
+__device__ __forceinline__ void deliver_remote(const PersistArgs& a, Stager& sg, u64* xp, uint32_t k, uint32_t tag, uint32_t prev_slot,
                                                uint32_t w, uint32_t n_cw, uint32_t lane, DeliveryTotals& tot, bool& dead) {
     unsigned long long events = 0ull;
     uint32_t my_n = 0;
@@ -319,8 +354,9 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, u64* xp, ui
         const uint32_t slot0 = wrap_slot(prev_slot + ((uint32_t)e >> kSrcBits), a.ring_slots);
         events += re - rb;
         for (unsigned long long c = rb; c < re; c += kChunk)
-            stream_chunk(a, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
+            deliver_chunk(a, sg, make_uint4((uint32_t)c, (uint32_t)min((unsigned long long)kChunk, re - c), slot0, 0u), lane);
     }
+    stage_flush(a, sg, lane);
     if (lane == 0) tot.events += events;
     if (a.profile && lane == 0) {
         tot.remote_wait_ns += t_counts - t_in;
@@ -391,6 +427,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         for (int i = threadIdx.x; i < words; i += kBT) dst[i] = src[i];
     }
     const TypeConsts* types = use_smem ? s_types : a.types;
+    // behind the type table: the warps' staging buffers for CSR entries
+    uint2* const s_stage = reinterpret_cast<uint2*>(smem_raw + sizeof(PipeShared) +
+                                                    (use_smem ? (sizeof(TypeConsts) * (size_t)a.n_types + 15) / 16 * 16 : 0));
 
     const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
     // delivery warps: kCW stream chunks, then the input warps, then (several ranks) the sender warp
@@ -599,6 +638,10 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         unsigned long long prev_start = step_base;
         uint32_t prev_slot = slot;   // ring slot of the previous phase's first step
         DeliveryTotals tot = {0ull, 0ull, 0ull, 0ull, 0ull};
+        Stager sg;
+        sg.buf = s_stage + (size_t)min(dwarp, kCW - 1u) * kStage * kChunk;   // only chunk warps stage (input / sender warps never use it)
+        sg.desc = sh.sdesc[threadIdx.x >> 5];
+        sg.m = 0;
         CachedCell cc = {make_uint4(0u, 0u, 0u, 0u), 0u, 0u};
         if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual) {
             const uint32_t v0 = it * gridDim.x + blockIdx.x;
@@ -655,8 +698,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             } else {
                 if (dtid == 0) sh.chunks[(p + 1u) % 3u] = 0u;   // the list of the NEXT phase was last read one phase ago
                 if (p > 0) {
-                    deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
-                    if (multi) deliver_remote(a, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
+                    deliver_list(a, sh, sg, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                    if (!multi) stage_flush(a, sg, lane);
+                    if (multi) deliver_remote(a, sg, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
                 }
                 if (timer_d) t_rows = gtimer();
                 if (IEXT && clamp_next) {
@@ -697,8 +741,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         // what the last phase emitted: delivered before the launch ends, so the ring is complete at rest
         if (p > 0) {
             if (!input_role) {
-                deliver_list(a, sh, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
-                if (multi) deliver_remote(a, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
+                deliver_list(a, sh, sg, (p + 2u) % 3u, (uint32_t)prev_start + 1u, dwarp, lane, tot);
+                    if (!multi) stage_flush(a, sg, lane);
+                if (multi) deliver_remote(a, sg, xp_self, (a.seq0 + p - 1u) & 3u, (uint32_t)prev_start + 1u, prev_slot, dwarp, kCW, lane, tot, sync_dead);
             }
             if (dwarp == log_warp) {
                 const uint32_t q = (p & 1u) ^ 1u;
@@ -739,8 +784,11 @@ static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext, bool mult
     return has_iext ? (const void*)pipelined_kernel<false, true, false> : (const void*)pipelined_kernel<false, false, false>;
 }
 
-size_t pipelined_smem(int n_types) {
-    return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0);
+// Shared memory of a block: lists, type table, and a staging buffer of kStage chunks for each of `chunk_warps` warps
+// (a small shared-memory carve-out leaves more L1 for the update warps' spilled registers).
+size_t pipelined_smem(int n_types, uint32_t chunk_warps) {
+    return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0) +
+           (size_t)chunk_warps * kStage * kChunk * sizeof(uint2);
 }
 
 uint32_t pipelined_max_update_warps() { return kMaxUpdWarps; }
@@ -756,7 +804,7 @@ int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem)
 }
 
 cudaError_t launch_pipelined(const PersistArgs& a, bool has_theta, bool has_iext, int blocks, cudaStream_t s) {
-    const size_t smem = pipelined_smem(a.n_types);
+    const size_t smem = pipelined_smem(a.n_types, kWarps - a.upd_warps - a.input_warps - (a.n_ranks > 1 ? 1u : 0u));
     const void* f = pipelined_kernel_ptr(has_theta, has_iext, a.n_ranks > 1);
     cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -615,3 +615,275 @@ int64_t orc_generate_distance_edges(const orc_gen_spec* g, int64_t cap, uint32_t
     }
     return n;
 }
+
+/* ============================================================================================
+ * Single-precision restatement of the engine's stepping with DETERMINISTIC delivery.
+ *
+ * The fp64 functions above state the model; this one states the engine's own arithmetic contract, so that the
+ * CUDA path can be compared bit for bit instead of within a tolerance:
+ *   - per-type constants are the fp64 values of orc_glif_consts_init rounded to float (a type without after-spike
+ *     currents gets decay 1 / coefficient 0, an unused receptor port all zeros);
+ *   - one neuron step is the sequence of single IEEE-754 operations written in step_f32 (fmaf where a fused
+ *     multiply-add is meant; the file is compiled with -ffp-contract=off, so nothing else fuses);
+ *   - spikes are delivered once per exchange window of `window` steps (windows restart at every chunk of
+ *     `chunk_steps` steps, as the engine's run loop cuts them): the window's spikes - neurons, replayed virtual
+ *     spikes, Poisson cells - are ordered by (emitting step, source id), every spike's row is walked in CSR order
+ *     (delay, port, target; ties in edge-list order), the weights that meet in one ring cell are added left to
+ *     right in that order starting from the first, and the cell receives that sum with one addition.
+ * What NEST does inside nest.Simulate (bmtk/simulator/pointnet/pointsimulator.py:166) is fp64; the fp64 oracle
+ * is the reference for results, this restatement pins the device arithmetic. */
+typedef struct {
+    float P11[ORC_MAX_PORTS], P21[ORC_MAX_PORTS], P31[ORC_MAX_PORTS], P32[ORC_MAX_PORTS], psc_init[ORC_MAX_PORTS];
+    float asc_decay[2], asc_coeff[2], asc_refr[2], asc_amps[2], asc_rec[2];
+    float P33, P30, th_inf, i_e, v_reset, E_L, inv_G, delta_gain;
+    float theta_spike_decay, theta_spike_refr, th_spike_add, reset_fraction, reset_add, phi, abpara, theta_voltage_decay;
+    int32_t n_ref, sdt, adapt, iaf;
+} orc_f32_consts;
+
+static void f32_consts_init(const orc_glif_params* p, double h, orc_f32_consts* f)
+{
+    orc_glif_consts c;
+    orc_glif_consts_init(p, h, &c);
+    memset(f, 0, sizeof(*f));
+    for (int k = 0; k < c.n_ports; ++k) {
+        f->P11[k] = (float)c.P11[k]; f->P21[k] = (float)c.P21[k]; f->P31[k] = (float)c.P31[k];
+        f->P32[k] = (float)c.P32[k]; f->psc_init[k] = (float)c.psc_init[k];
+    }
+    for (int j = 0; j < 2; ++j) {
+        if (c.has_asc) {
+            f->asc_decay[j] = (float)c.asc_decay_rate[j]; f->asc_coeff[j] = (float)c.asc_stable_coeff[j];
+            f->asc_refr[j] = (float)c.asc_refr_rate[j]; f->asc_amps[j] = (float)c.asc_amps[j];
+            f->asc_rec[j] = (float)(c.asc_stable_coeff[j] / c.asc_decay_rate[j]);
+        } else {
+            f->asc_decay[j] = 1.f; f->asc_refr[j] = 1.f;
+        }
+    }
+    f->P33 = (float)c.P33; f->P30 = (float)c.P30; f->th_inf = (float)c.th_inf; f->i_e = (float)c.I_e;
+    f->v_reset = (float)c.v_reset; f->E_L = (float)c.E_L; f->inv_G = (float)(1.0 / c.G); f->delta_gain = c.delta ? 1.f : 0.f;
+    f->theta_spike_decay = (float)c.theta_spike_decay; f->theta_spike_refr = (float)c.theta_spike_refr_decay;
+    f->th_spike_add = (float)c.th_spike_add; f->reset_fraction = (float)c.reset_fraction; f->reset_add = (float)c.reset_add;
+    f->phi = (float)c.phi; f->abpara = (float)c.abpara; f->theta_voltage_decay = (float)c.theta_voltage_decay;
+    f->n_ref = c.n_ref; f->sdt = c.has_theta_spike; f->adapt = c.has_theta_voltage; f->iaf = c.iaf;
+}
+
+typedef struct {
+    int64_t n_neurons, n_virtual;
+    const int32_t* type_index;
+    int32_t n_types;
+    const orc_glif_params* types;
+    const int64_t* rowptr;
+    const int32_t *target, *port, *delay;
+    const float* weight;
+    int32_t max_delay, window, theta_any;   /* theta_any: some type has threshold dynamics (the device then adds the
+                                               two components to th_inf for every type) */
+    int64_t chunk_steps;
+    const int64_t* in_step_ptr;             /* replayed virtual spikes by emitting step, [step0 + n_steps + 1] */
+    const int32_t* in_src;
+    const float* poisson_rate_hz;           /* on-line Poisson cells (NULL = none) */
+    uint64_t poisson_seed;
+    uint32_t poisson_stream;
+    int64_t n_clamp;
+    const int64_t* ce_step;
+    const int32_t* ce_target;
+    const float* ce_delta;
+    double dt;
+    int64_t step0, n_steps;
+    float *U, *asc0, *asc1, *y1, *y2, *th_spike, *th_voltage, *i_ext, *ring;   /* ring: (max_delay + window) slots */
+    int32_t* refr;
+    int64_t spike_cap;
+    int64_t* n_spikes;
+    int64_t* spike_step;
+    int32_t* spike_id;
+    int32_t n_probe;
+    const int32_t* probe_ids;
+    int32_t probe_interval, n_probe_vars;
+    uint32_t probe_vars;
+    float* trace;
+    int64_t* n_samples;
+    int64_t* n_events;
+} orc_f32_args;
+
+void orc_f32_init_state(const orc_f32_args* a)
+{
+    const int64_t N = a->n_neurons, S = (int64_t)a->max_delay + a->window;
+    for (int64_t i = 0; i < N; ++i) {
+        const orc_glif_params* p = &a->types[a->type_index[i]];
+        a->U[i] = (float)(p->V_m - p->E_L);
+        a->asc0[i] = (float)p->asc_init[0];
+        a->asc1[i] = (float)p->asc_init[1];
+        a->th_spike[i] = a->th_voltage[i] = a->i_ext[i] = 0.f;
+        a->refr[i] = 0;
+    }
+    memset(a->y1, 0, sizeof(float) * ORC_MAX_PORTS * N);
+    memset(a->y2, 0, sizeof(float) * ORC_MAX_PORTS * N);
+    memset(a->ring, 0, sizeof(float) * S * ORC_MAX_PORTS * N);
+}
+
+typedef struct { uint64_t key; } f32_item;   /* emitting step << 32 | source id */
+static int f32_item_cmp(const void* x, const void* y)
+{
+    const uint64_t a = ((const f32_item*)x)->key, b = ((const f32_item*)y)->key;
+    return a < b ? -1 : a > b;
+}
+
+int orc_f32_run(orc_f32_args* a)
+{
+    const int64_t N = a->n_neurons, S = (int64_t)a->max_delay + a->window;
+    const double h = a->dt;
+    orc_f32_consts* C = (orc_f32_consts*)malloc(sizeof(orc_f32_consts) * (size_t)a->n_types);
+    float* acc = (float*)malloc(sizeof(float) * (size_t)(S * ORC_MAX_PORTS * N));
+    uint8_t* seen = (uint8_t*)calloc((size_t)(S * ORC_MAX_PORTS * N), 1);
+    int64_t* touched = NULL;
+    int64_t touched_cap = 0, n_touched = 0;
+    f32_item* items = NULL;
+    int64_t item_cap = 0, n_items = 0;
+    uint32_t* thr = NULL;
+    if (!C || !acc || !seen) return -1;
+    for (int t = 0; t < a->n_types; ++t) f32_consts_init(&a->types[t], h, &C[t]);
+    if (a->poisson_rate_hz) {
+        thr = (uint32_t*)malloc(sizeof(uint32_t) * 4 * (size_t)a->n_virtual);
+        for (int64_t v = 0; v < a->n_virtual; ++v) orc_poisson_thresholds((double)a->poisson_rate_hz[v] * h * 1e-3, &thr[4 * v]);
+    }
+    int64_t ce = 0;
+    while (ce < a->n_clamp && a->ce_step[ce] < a->step0) ++ce;
+    int status = 0;
+#define F32_PUSH(step_, src_) do { \
+        if (n_items == item_cap) { item_cap = item_cap ? 2 * item_cap : 4096; items = (f32_item*)realloc(items, sizeof(f32_item) * (size_t)item_cap); } \
+        items[n_items++].key = ((uint64_t)(step_) << 32) | (uint64_t)(src_); } while (0)
+    int64_t n = a->step0;
+    const int64_t end = a->step0 + a->n_steps;
+    while (n < end) {
+        int64_t chunk = end - n < a->chunk_steps ? end - n : a->chunk_steps;
+        const int64_t chunk_end = n + chunk;
+        while (n < chunk_end) {
+            const int64_t w = chunk_end - n < a->window ? chunk_end - n : a->window;
+            n_items = 0;
+            for (int64_t s = 0; s < w; ++s, ++n) {
+                while (ce < a->n_clamp && a->ce_step[ce] <= n) {
+                    a->i_ext[a->ce_target[ce]] = a->i_ext[a->ce_target[ce]] + a->ce_delta[ce];
+                    ++ce;
+                }
+                const int64_t slot = n % S;
+                for (int64_t i = 0; i < N; ++i) {
+                    const orc_f32_consts* c = &C[a->type_index[i]];
+                    float in[ORC_MAX_PORTS];
+                    for (int p = 0; p < ORC_MAX_PORTS; ++p) {
+                        float* cell = &a->ring[(slot * ORC_MAX_PORTS + p) * N + i];
+                        in[p] = *cell;
+                        *cell = 0.f;
+                    }
+                    const float v_old = a->U[i];
+                    const int refr = a->refr[i] > 0;
+                    const int rf_dec = a->refr[i] - 1;
+                    const int ends = refr && rf_dec == 0;
+                    /* integrating branch (evaluated for every neuron, selected below, as on the device) */
+                    const float asc_sum = fmaf(c->asc_coeff[0], a->asc0[i], c->asc_coeff[1] * a->asc1[i]);
+                    const float drive = (a->i_ext[i] + c->i_e) + asc_sum;
+                    float u = fmaf(v_old, c->P33, drive * c->P30);
+                    for (int p = 0; p < ORC_MAX_PORTS; ++p)
+                        u = u + fmaf(c->P31[p], a->y1[p * N + i], c->P32[p] * a->y2[p * N + i]);
+                    u = fmaf(c->delta_gain, (in[0] + in[1]) + (in[2] + in[3]), u);
+                    float th = c->th_inf;
+                    float ths_int = a->th_spike[i], thv_int = a->th_voltage[i];
+                    if (a->theta_any) {
+                        if (c->sdt) ths_int = a->th_spike[i] * c->theta_spike_decay;
+                        if (c->adapt) {
+                            const float beta = drive * c->inv_G;
+                            const float d = c->phi * (v_old - beta);
+                            const float ab = c->abpara * beta;
+                            const float rest = (a->th_voltage[i] - d) - ab;
+                            thv_int = fmaf(c->theta_voltage_decay, rest, d * c->P33) + ab;
+                        }
+                        th = th + (ths_int + thv_int);
+                    }
+                    const int fire = !refr && (c->iaf ? (u >= th) : (u > th));
+                    if (c->iaf && fire) u = c->v_reset;
+                    const float u_end = c->sdt ? fmaf(c->reset_fraction, v_old, c->reset_add) : c->v_reset;
+                    a->U[i] = refr ? (ends ? u_end : v_old) : u;
+                    a->asc0[i] = refr ? (ends ? fmaf(a->asc0[i], c->asc_refr[0], c->asc_amps[0]) : a->asc0[i]) : a->asc0[i] * c->asc_decay[0];
+                    a->asc1[i] = refr ? (ends ? fmaf(a->asc1[i], c->asc_refr[1], c->asc_amps[1]) : a->asc1[i]) : a->asc1[i] * c->asc_decay[1];
+                    if (a->theta_any) {
+                        a->th_spike[i] = refr ? ((ends && c->sdt) ? fmaf(a->th_spike[i], c->theta_spike_refr, c->th_spike_add) : a->th_spike[i]) : ths_int;
+                        a->th_voltage[i] = refr ? a->th_voltage[i] : thv_int;
+                    }
+                    a->refr[i] = refr ? rf_dec : (fire ? c->n_ref : a->refr[i]);
+                    for (int p = 0; p < ORC_MAX_PORTS; ++p) {
+                        const float y1o = a->y1[p * N + i];
+                        a->y2[p * N + i] = fmaf(c->P21[p], y1o, c->P11[p] * a->y2[p * N + i]);
+                        a->y1[p * N + i] = fmaf(c->P11[p], y1o, c->psc_init[p] * in[p]);
+                    }
+                    if (fire) {
+                        if (a->spike_step) {
+                            if (*a->n_spikes < a->spike_cap) {
+                                a->spike_step[*a->n_spikes] = n + 1;
+                                a->spike_id[*a->n_spikes] = (int32_t)i;
+                            } else {
+                                status = 1;
+                            }
+                        }
+                        ++*a->n_spikes;
+                        F32_PUSH(n, i);
+                    }
+                }
+                if (a->in_step_ptr)
+                    for (int64_t k = a->in_step_ptr[n]; k < a->in_step_ptr[n + 1]; ++k) F32_PUSH(n, N + a->in_src[k]);
+                if (thr)
+                    for (int64_t v = 0; v < a->n_virtual; ++v) {
+                        const int32_t cnt = orc_poisson_count_stream((uint32_t)v, (uint64_t)n, a->poisson_stream, a->poisson_seed, &thr[4 * v]);
+                        for (int32_t q = 0; q < cnt; ++q) F32_PUSH(n, N + v);
+                    }
+                if (a->n_probe > 0 && (n + 1) % a->probe_interval == 0) {
+                    const int nv = a->n_probe_vars > 0 ? a->n_probe_vars : 1;
+                    float* row = a->trace + (*a->n_samples) * a->n_probe * nv;
+                    for (int v = 0; v < nv; ++v) {
+                        const uint32_t code = a->n_probe_vars > 0 ? (a->probe_vars >> (4 * v)) & 15u : 0u;
+                        for (int q = 0; q < a->n_probe; ++q) {
+                            const int32_t i = a->probe_ids[q];
+                            const orc_f32_consts* c = &C[a->type_index[i]];
+                            float x;
+                            switch (code) {
+                                case 1: x = ((a->y2[i] + a->y2[N + i]) + a->y2[2 * N + i]) + a->y2[3 * N + i]; break;
+                                case 2: x = fmaf(c->asc_rec[0], a->asc0[i], c->asc_rec[1] * a->asc1[i]); break;
+                                case 3: x = ((c->th_inf + a->th_spike[i]) + a->th_voltage[i]) + c->E_L; break;
+                                case 4: x = a->th_spike[i]; break;
+                                case 5: x = a->th_voltage[i]; break;
+                                case 6: x = a->i_ext[i] + c->i_e; break;
+                                default: x = a->U[i] + c->E_L;
+                            }
+                            row[v * a->n_probe + q] = x;
+                        }
+                    }
+                    ++*a->n_samples;
+                }
+            }
+            /* ---- the window's delivery */
+            qsort(items, (size_t)n_items, sizeof(f32_item), f32_item_cmp);
+            n_touched = 0;
+            for (int64_t it = 0; it < n_items; ++it) {
+                const int64_t step = (int64_t)(items[it].key >> 32), src = (int64_t)(items[it].key & 0xffffffffu);
+                for (int64_t k = a->rowptr[src]; k < a->rowptr[src + 1]; ++k) {
+                    const int64_t cell = (((step + a->delay[k]) % S) * ORC_MAX_PORTS + a->port[k]) * N + a->target[k];
+                    if (!seen[cell]) {
+                        seen[cell] = 1;
+                        acc[cell] = a->weight[k];
+                        if (n_touched == touched_cap) {
+                            touched_cap = touched_cap ? 2 * touched_cap : 4096;
+                            touched = (int64_t*)realloc(touched, sizeof(int64_t) * (size_t)touched_cap);
+                        }
+                        touched[n_touched++] = cell;
+                    } else {
+                        acc[cell] = acc[cell] + a->weight[k];
+                    }
+                }
+                *a->n_events += a->rowptr[src + 1] - a->rowptr[src];
+            }
+            for (int64_t k = 0; k < n_touched; ++k) {
+                a->ring[touched[k]] = a->ring[touched[k]] + acc[touched[k]];
+                seen[touched[k]] = 0;
+            }
+        }
+    }
+#undef F32_PUSH
+    free(C); free(acc); free(seen); free(touched); free(items); free(thr);
+    return status;
+}

@@ -404,3 +404,133 @@ def generate_distance_edges(spec, lo=0, hi=None):
     m = L.orc_generate_distance_edges(C.byref(s), n, _ptr(src), _ptr(trg), _ptr(w), _ptr(d), _ptr(p))
     assert m == n
     return src, trg, w, d, p
+
+
+class RunArgsF32(C.Structure):
+    _fields_ = [
+        ('n_neurons', C.c_int64), ('n_virtual', C.c_int64), ('type_index', _p), ('n_types', C.c_int32), ('types', _p),
+        ('rowptr', _p), ('target', _p), ('port', _p), ('delay', _p), ('weight', _p),
+        ('max_delay', C.c_int32), ('window', C.c_int32), ('theta_any', C.c_int32), ('chunk_steps', C.c_int64),
+        ('in_step_ptr', _p), ('in_src', _p), ('poisson_rate_hz', _p), ('poisson_seed', C.c_uint64),
+        ('poisson_stream', C.c_uint32),
+        ('n_clamp', C.c_int64), ('ce_step', _p), ('ce_target', _p), ('ce_delta', _p),
+        ('dt', C.c_double), ('step0', C.c_int64), ('n_steps', C.c_int64),
+        ('U', _p), ('asc0', _p), ('asc1', _p), ('y1', _p), ('y2', _p), ('th_spike', _p), ('th_voltage', _p),
+        ('i_ext', _p), ('ring', _p), ('refr', _p),
+        ('spike_cap', C.c_int64), ('n_spikes', _p), ('spike_step', _p), ('spike_id', _p),
+        ('n_probe', C.c_int32), ('probe_ids', _p), ('probe_interval', C.c_int32), ('n_probe_vars', C.c_int32),
+        ('probe_vars', C.c_uint32), ('trace', _p), ('n_samples', _p), ('n_events', _p),
+    ]
+
+
+class OracleSimF32:
+    """The engine's single-precision arithmetic with deterministic delivery, restated on the CPU (orc_f32_run):
+    what the CUDA path must reproduce BIT FOR BIT in deterministic mode. `window` and `chunk_steps` are the
+    engine's exchange window and chunk length (they fix which weights are added before they reach a ring cell)."""
+
+    def __init__(self, types, type_index, dt, window, chunk_steps=4096, n_virtual=0, src=None, trg=None, weight=None,
+                 delay_steps=None, port=None):
+        self.L = lib()
+        self.L.orc_f32_run.argtypes = [C.POINTER(RunArgsF32)]
+        self.L.orc_f32_run.restype = C.c_int
+        self.L.orc_f32_init_state.argtypes = [C.POINTER(RunArgsF32)]
+        self.dt, self.N, self.n_virtual = float(dt), int(len(type_index)), int(n_virtual)
+        self.window, self.chunk_steps = int(window), int(chunk_steps)
+        self.type_index = np.ascontiguousarray(type_index, dtype=np.int32)
+        plist = [t if isinstance(t, GlifParams) else make_params(t) for t in types]
+        self.types = (GlifParams * len(plist))(*plist)
+        self.n_types = len(plist)
+        self.theta_any = int(any(p.spike_dependent_threshold or p.adapting_threshold for p in plist))
+        n_rows = self.N + self.n_virtual
+        if src is None or len(src) == 0:
+            src = trg = delay_steps = port = np.zeros(0, dtype=np.int64)
+            weight = np.zeros(0, dtype=np.float32)
+        delay_steps = np.asarray(delay_steps, dtype=np.int64)
+        self.rowptr, order = build_csr(n_rows, src, trg, weight, delay_steps, port)
+        self.target = np.ascontiguousarray(np.asarray(trg)[order], dtype=np.int32)
+        self.port = np.ascontiguousarray(np.asarray(port)[order], dtype=np.int32)
+        self.delay = np.ascontiguousarray(delay_steps[order], dtype=np.int32)
+        self.weight = np.ascontiguousarray(np.asarray(weight)[order], dtype=np.float32)
+        self.max_delay = int(self.delay.max()) if self.delay.size else 1
+        N, S = self.N, self.max_delay + self.window
+        f = lambda n: np.zeros(n, dtype=np.float32)
+        self.U, self.asc0, self.asc1 = f(N), f(N), f(N)
+        self.y1, self.y2 = f(MAX_PORTS * N), f(MAX_PORTS * N)
+        self.th_spike, self.th_voltage, self.i_ext = f(N), f(N), f(N)
+        self.ring = f(S * MAX_PORTS * N)
+        self.refr = np.zeros(N, dtype=np.int32)
+        self.step = 0
+        self.in_step = np.zeros(0, dtype=np.int64); self.in_src = np.zeros(0, dtype=np.int32)
+        self.poisson = None
+        self.ce_step = np.zeros(0, dtype=np.int64); self.ce_target = np.zeros(0, dtype=np.int32)
+        self.ce_delta = np.zeros(0, dtype=np.float32)
+        self.probe_ids = np.zeros(0, dtype=np.int32); self.probe_interval = 1; self.probe_vars = [0]
+        self.n_events = np.zeros(1, dtype=np.int64)
+        self.L.orc_f32_init_state(C.byref(self._args(0)))
+
+    def set_input_spikes(self, emit_step, virt_index):
+        emit_step = np.asarray(emit_step, dtype=np.int64)
+        o = np.lexsort((np.asarray(virt_index), emit_step))
+        self.in_step = np.ascontiguousarray(emit_step[o])
+        self.in_src = np.ascontiguousarray(np.asarray(virt_index)[o], dtype=np.int32)
+
+    def set_poisson(self, rate_hz, seed, stream=0):
+        self.poisson = (np.ascontiguousarray(rate_hz, dtype=np.float32), int(seed), int(stream))
+
+    def set_clamp_events(self, step, target, delta):
+        step = np.asarray(step, dtype=np.int64)
+        o = np.argsort(step, kind='stable')
+        self.ce_step = np.ascontiguousarray(step[o])
+        self.ce_target = np.ascontiguousarray(np.asarray(target)[o], dtype=np.int32)
+        self.ce_delta = np.ascontiguousarray(np.asarray(delta)[o], dtype=np.float32)
+
+    def set_probes(self, ids, interval_steps=1, variables=None):
+        self.probe_ids = np.ascontiguousarray(ids, dtype=np.int32)
+        self.probe_interval = int(interval_steps)
+        self.probe_vars = [int(v) for v in (variables or [0])]
+
+    def _args(self, n_steps):
+        a = RunArgsF32()
+        a.n_neurons, a.n_virtual = self.N, self.n_virtual
+        a.type_index, a.n_types, a.types = _ptr(self.type_index), self.n_types, C.cast(self.types, C.c_void_p)
+        a.rowptr, a.target, a.port, a.delay, a.weight = (_ptr(self.rowptr), _ptr(self.target), _ptr(self.port),
+                                                         _ptr(self.delay), _ptr(self.weight))
+        a.max_delay, a.window, a.theta_any, a.chunk_steps = self.max_delay, self.window, self.theta_any, self.chunk_steps
+        a.dt, a.step0, a.n_steps = self.dt, self.step, n_steps
+        for k in ('U', 'asc0', 'asc1', 'y1', 'y2', 'th_spike', 'th_voltage', 'i_ext', 'ring', 'refr'):
+            setattr(a, k, _ptr(getattr(self, k)))
+        return a
+
+    def run(self, n_steps, spike_cap=None):
+        n_steps = int(n_steps)
+        a = self._args(n_steps)
+        end = self.step + n_steps
+        self._in_ptr = np.searchsorted(self.in_step, np.arange(end + 1), side='left').astype(np.int64)
+        a.in_step_ptr = _ptr(self._in_ptr) if self.in_step.size else None
+        a.in_src = _ptr(self.in_src)
+        if self.poisson is not None:
+            a.poisson_rate_hz, a.poisson_seed, a.poisson_stream = _ptr(self.poisson[0]), self.poisson[1], self.poisson[2]
+        a.n_clamp = len(self.ce_step)
+        a.ce_step, a.ce_target, a.ce_delta = _ptr(self.ce_step), _ptr(self.ce_target), _ptr(self.ce_delta)
+        spike_cap = max(1024, self.N * 64) if spike_cap is None else int(spike_cap)
+        n_spikes = np.zeros(1, dtype=np.int64)
+        sp_step, sp_id = np.zeros(spike_cap, dtype=np.int64), np.zeros(spike_cap, dtype=np.int32)
+        a.spike_cap, a.n_spikes, a.spike_step, a.spike_id = spike_cap, _ptr(n_spikes), _ptr(sp_step), _ptr(sp_id)
+        nv = len(self.probe_vars)
+        trace = np.zeros((n_steps // max(1, self.probe_interval) + 1, nv, max(1, len(self.probe_ids))), dtype=np.float32)
+        n_samples = np.zeros(1, dtype=np.int64)
+        a.n_probe, a.probe_ids, a.probe_interval = len(self.probe_ids), _ptr(self.probe_ids), self.probe_interval
+        a.n_probe_vars, a.probe_vars = nv, sum(v << (4 * k) for k, v in enumerate(self.probe_vars))
+        a.trace, a.n_samples = _ptr(trace), _ptr(n_samples)
+        ev0 = int(self.n_events[0])
+        a.n_events = _ptr(self.n_events)
+        rc = self.L.orc_f32_run(C.byref(a))
+        if rc < 0:
+            raise MemoryError('oracle allocation failed')
+        if rc == 1:
+            raise RuntimeError('oracle spike log full (cap %d)' % spike_cap)
+        self.step = end
+        k = int(n_spikes[0])
+        tr = trace[:int(n_samples[0]), :, :len(self.probe_ids)]
+        return dict(spike_step=sp_step[:k].copy(), spike_id=sp_id[:k].copy(), trace=(tr[:, 0] if nv == 1 else tr).copy(),
+                    n_spikes=k, n_events=int(self.n_events[0]) - ev0)

@@ -81,14 +81,14 @@ def test_v1_scale_network_from_the_device_generator(cabi, tmp_path):
     conf = pointnet.Config.from_json(info['config'])
     graph = pointnet.PointNetwork.from_config(conf)
     sim = pointnet.PointSimulator.from_config(conf, graph)
-    src, trg, w, d, port = graph.edge_arrays()
     t_read = time.time() - t0
+    sim.run()                                             # the input module adds the virtual cells' edges
+    src, trg, w, d, port = graph.edge_arrays()
     assert len(src) == net.n_edges
     # same multiset of edges after the node-id permutation of the files: compare invariant sums
     assert float(w.astype(np.float64).sum()) == pytest.approx(float(net.weight.astype(np.float64).sum()), rel=1e-9)
     assert np.array_equal(np.bincount(port, minlength=4), np.bincount(net.port, minlength=4))
     assert np.array_equal(np.bincount(np.round(d / net.dt).astype(np.int64)), np.bincount(net.delay_steps))
-    sim.run()
     st = sim.recorded_spikes()
     rate = len(st[0]) / n / 0.1
     print('generate %.1f s, write %.1f s, read+expand %.1f s, %d spikes in 100 ms (%.2f Hz)' % (t_gen, t_write, t_read, len(st[0]), rate))
