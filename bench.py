@@ -44,7 +44,7 @@ BYTES_PER_EVENT = 16.0
 # (profiles/glif_update_2M_neurons_ncu_full.md scaled to this network, profiles/propagate_atomic_c2like_100k_ncu_full.md
 # at 12.4 B per event)
 NCU_TRAFFIC_BYTES = {'glif_update': 102.8 * 230924, 'propagate': None, 'persistent_per_step': 5.97e6,
-                     'pipelined_per_step': 4.05e6}
+                     'pipelined_per_step': 3.89e6}
 
 
 def parse_args():
@@ -399,6 +399,19 @@ def main():
                 phases['remote_count_wait_us'] = eng.counter('phase_remote_wait_ns') / nw * 1e-3
                 phases['remote_rows_us'] = eng.counter('phase_remote_rows_ns') / nw * 1e-3
                 phases['local_rows_us'] = phases['row_streaming_us'] - phases['remote_count_wait_us'] - phases['remote_rows_us']
+
+    # ---------------- delivery against the device's rate of scattered fp32 reductions into a buffer of the ring's size
+    if phases is not None and rank == 0:
+        from bmtk_b200.engine import scatter_reduction_rate
+        cells = eng.csr_info()['ring_slots'] * 4 * eng.counter('n_pad')
+        ceiling = scatter_reduction_rate(cells, 8 * 1024 * 1024, device=local_rank)
+        busy_ns = (eng.counter('phase_rows_ns') / max(1, eng.counter('phase_windows'))) or 1.0
+        phases['scatter_red_ceiling_per_s'] = ceiling
+        phases['delivery_events_per_s_while_streaming'] = phases['events_per_window'] / (busy_ns * 1e-9)
+        phases['delivery_frac_of_scatter_ceiling'] = phases['delivery_events_per_s_while_streaming'] / ceiling
+        phases['delivery_note'] = ('one fp32 reduction per synaptic event into a random ring cell: the ceiling is what the device '
+                                   'sustains for such reductions alone (bmtk_probe_scatter_reductions); delivery runs beside the '
+                                   'update warps and is latency-bound per chunk, not throughput-bound')
 
     # ---------------- latency of the exchange primitive between ranks 0 and 1 (what a phase cannot go below)
     if world > 1 and args.exchange == 'p2p' and phases is not None:

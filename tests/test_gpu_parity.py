@@ -433,7 +433,11 @@ def test_reference_example_network_glif_and_iaf_cells(cabi, deterministic):
     _trace_check(tr, r['trace'], min(div - 1, net.n_steps))
     t_ms = net.n_steps * net.dt
     rg, rc = rates_by_type(net, ids, t_ms), rates_by_type(net, r['spike_id'], t_ms)
-    assert np.all(np.abs(rg - rc) <= 0.02 * rc + 0.05), (rg, rc)
+    # 2 % of the rate plus three standard deviations of the counting noise of two runs that have parted
+    # (sqrt(count_a + count_b) spikes; this example's types hold 50-100 cells and fire 0.3-8 Hz for half a second)
+    from oracle import compare as K
+    ra = K.rate_agreement(net.type_index, len(net.types), ids, r['spike_id'], t_ms)
+    assert ra['ok'], (rg, rc, ra['allowance'])
 
 
 def _stored_example(name, n_steps, probes):

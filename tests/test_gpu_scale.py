@@ -51,7 +51,10 @@ def test_c3_full_size_bookkeeping_and_mode_agreement(cabi, oracle):
     assert div > 100                                       # identical spikes until fp32 summation order matters
     assert abs(len(st) - len(st_d)) <= 0.01 * len(st_d)
     ra, rd = rates_by_type(net, ids, 100.0), rates_by_type(net, ids_d, 100.0)
-    assert np.all(np.abs(ra - rd) <= 0.02 * rd + 0.2)
+    # two deliveries of the same network over 100 ms: 2 % of the rate plus three standard deviations of the counting
+    # noise of two runs that have parted (oracle/compare.py:rate_agreement)
+    from oracle import compare as K
+    assert K.rate_agreement(net.type_index, len(net.types), ids, ids_d, 100.0)['ok'], (ra, rd)
     # events delivered = sum of the row lengths of every spike emitted (neurons and Poisson cells)
     steps, srcs = oracle.poisson_spikes(net.poisson_rate_hz, net.dt, net.poisson_seed, 0, n_steps)
     outdeg = np.diff(rowptr)
@@ -81,7 +84,8 @@ def test_c2_reduced_against_oracle(cabi, deterministic):
     assert len(a) == len(b)
     assert all(x[0] == y[0] and abs(x[1] - y[1]) <= 1 for x, y in zip(a, b))
     rg, rc = rates_by_type(net, ids, 400.0), rates_by_type(net, r['spike_id'], 400.0)
-    assert np.all(np.abs(rg - rc) <= 0.02 * rc + 0.15), (rg, rc)
+    from oracle import compare as K       # 2 % plus 3 sigma of the counting noise (5000 neurons, 400 ms)
+    assert K.rate_agreement(net.type_index, len(net.types), ids, r['spike_id'], 400.0)['ok'], (rg, rc)
 
 
 def test_trial_batching_shares_the_csr(cabi, oracle):
