@@ -578,7 +578,7 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
     net = W.c4(n=n, in_degree=min(1000, n // 4), n_virtual=max(8, int(round(2000 * args.scale))), t_stop_ms=step_ms)
     n_steps = int(round(step_ms / net.dt))
     eng = W.build_engine(net, device=local_rank, record_spikes=True, record_vm=False,
-                         options=dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000, **extra_options(args)))
+                         options={**dict(trials=t_loc, trial_base=rank * t_loc, chunk_steps=1000), **extra_options(args)})
     MAX, SUM = (dist.ReduceOp.MAX, dist.ReduceOp.SUM) if world > 1 else (None, None)
     n_warm = 0
     first_trial = None
@@ -622,6 +622,7 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
     wall = reduce(time.time() - t0, MAX)
     e2e_events = reduce(eng.counter('events') - e0, SUM)
     n_pad, window = eng.counter('n_pad'), eng.counter('window')
+    per_launch = eng.counter('pipeline_trials') if eng.counter('pipelined') else 0
     eng.close()
     peak, peak_kind = peaks()
     alg_bytes = BYTES_PER_NEURON_STEP * n_pad * world * n_steps * args.steps + BYTES_PER_EVENT * events
@@ -639,14 +640,17 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
                                    'cells per trial on their own Philox streams, dt 0.1 ms' % (T, n, net.n_edges, net.n_virtual),
                        'step': '%g ms of simulated time in every trial = %d update steps' % (step_ms, n_steps),
                        'partition': '%d trials per GPU, no exchange between GPUs' % t_loc,
-                       'l2': 'state + ring of %d trials exceed L2' % t_loc, 'window_steps': window,
+                       'l2': ('state + ring of %d trials exceed L2; a launch steps %d trials, whose ring slots fit'
+                              % (t_loc, per_launch)) if per_launch else 'state + ring of %d trials exceed L2' % t_loc,
+                       'kernel': 'pipelined, %d trials per launch' % per_launch if per_launch else 'two-phase persistent',
+                       'window_steps': window,
                        'mean_rate_hz': spikes / (n * T) / (step_ms * 1e-3 * args.steps)},
             'clocks': clocks,
             'e2e': {'value': e2e_events / wall, 'unit': 'events/s', 'h2d_bytes_per_step': 0,
                     'd2h_bytes_per_step': int(reduce(d2h, SUM) / args.steps),
                     'timing': 'wall clock; inputs are device-generated Poisson cells, every step reads its spike list back'},
             'gpu_launches': int(launches),
-            'roofline': {'kernel': 'persistent_kernel (update + delivery)', 'bound': 'hbm',
+            'roofline': {'kernel': 'pipelined_kernel' if per_launch else 'persistent_kernel (update + delivery)', 'bound': 'hbm',
                          'achieved': alg_bytes / world / (dev_ms * 1e6), 'peak': peak, 'unit': 'GB/s',
                          'frac': alg_bytes / world / (dev_ms * 1e6) / peak, 'traffic': None, 'peak_kind': peak_kind,
                          'note': 'algorithmic bytes per GPU = 128 B per neuron-step + 16 B per event, over the whole timed region'},

@@ -345,6 +345,9 @@ struct bmtk_engine {
     int persist_blocks = 0;
     bool persist_resident = false;
     uint4* d_pipe_seg = nullptr;
+    uint32_t pipe_warps_opt = 0;         // option pipeline_warps: 0 = choose, else 12 or 20 warps per block
+    bool ring_stage = true;              // pipelined kernel: next step's ring cells copied to shared memory ahead (option ring_stage)
+    uint32_t pipe_trials = 1, pipe_trials_opt = 0;   // trials one launch of the pipelined kernel steps (option pipeline_trials)
     uint32_t* d_pipe_sync = nullptr;     // pipelined kernel: the two phase counters
     uint32_t* d_log_seg_cnt = nullptr;   // pipelined kernel: spikes each block logged in the last launch
     unsigned long long* d_blk_prof = nullptr;   // pipelined kernel: per-block busy / wait sums (option phase_timers)
@@ -911,7 +914,7 @@ static int drain(bmtk_engine* e) {
     return BMTK_OK;
 }
 
-// The pipelined kernel runs when this rank can (resident state, one trial, min delay >= 2 steps) and,
+// The pipelined kernel runs when this rank can (resident state, min delay >= 2 steps) and,
 // with several ranks, when every rank can and none has clamp changes: the ranks must all run the same
 // exchange protocol.
 static bool use_pipelined(const bmtk_engine* e) {
@@ -996,17 +999,45 @@ static int run_persistent_chunk(bmtk_engine* e, uint32_t n) {
         e->log_segmented = e->record_spikes;
         a.upd_warps = e->pipe_upd_warps;
         a.blk_prof = e->phase_timers ? e->d_blk_prof : nullptr;
+        // several trials: the chunk of steps is run for `pipe_trials` trials at a time, so that the ring slots the
+        // launch scatters into stay in L2; one trial: a single launch over all cells
+        const uint32_t per_launch = e->n_trials > 1 ? e->pipe_trials : 1u;
+        a.ring_stage = (e->ring_stage && a.half > 1) ? 1u : 0u;
         // input warps: one thread per 2 Poisson cells of the block's share, at most half of the non-update warps;
         // replayed spikes alone get one warp
         {
-            const uint32_t free_warps = pipelined_warps() - e->pipe_upd_warps;
             uint32_t iw = 0;
-            if (e->has_poisson) iw = (uint32_t)((e->n_virtual / e->pipe_blocks + 63) / 64);
+            if (e->has_poisson) iw = (uint32_t)((e->n_virtual * per_launch / e->pipe_blocks + 63) / 64);
             // always at least one: the input warps also queue the block's own spikes and write the spike log
             iw = std::max(iw, 1u);
+            // the small block (12 warps, no register spills in the update) where it leaves at least 5 chunk warps: with
+            // fewer the delivering side became the slower one (measured on 50 000 neurons x 1, 2, 3 trials per launch)
+            const uint32_t others = e->pipe_upd_warps + iw + (e->n_ranks > 1 ? 1u : 0u);
+            const bool small = e->pipe_warps_opt ? e->pipe_warps_opt == pipelined_warps_small()
+                                                 : others + 5u <= pipelined_warps_small();
+            a.block_warps = small && others + 1u <= pipelined_warps_small() ? pipelined_warps_small() : pipelined_warps();
+            const uint32_t free_warps = a.block_warps - e->pipe_upd_warps;
             a.input_warps = std::max(1u, std::min(iw, free_warps / 2));
         }
-        CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
+        // the trials are dealt evenly to ceil(T / per_launch) launches (64 trials, 3 per launch: 20 x 3 + 2 x 2)
+        const uint32_t n_launch = (e->n_trials + per_launch - 1) / per_launch;
+        for (uint32_t g = 0, t0 = 0; g < n_launch; ++g) {
+            const uint32_t nt = e->n_trials / n_launch + (g < e->n_trials % n_launch ? 1u : 0u);
+            a.trial0 = t0;
+            a.cell0 = t0 * e->n_pad1;
+            a.n_cells = nt * e->n_pad1;
+            a.log_append = g > 0;
+            a.advance_clock = g + 1 == n_launch;
+            t0 += nt;
+            if (g > 0) {
+                // the next trials run the same steps: counters start over, and no descriptor of the trials before
+                // (valid by the tag of its phase) may be left where a neighbour looks for spill-over
+                CU(cudaMemsetAsync(e->d_pipe_sync, 0, 32, e->stream));
+                CU(cudaMemsetAsync(e->d_pipe_seg, 0, sizeof(uint4) * 3 * (size_t)e->pipe_blocks * kPipeSegCap, e->stream));
+                ++e->launches;
+            }
+            CU(launch_pipelined(a, e->has_theta, e->has_iext, e->pipe_blocks, e->stream));
+        }
     } else {
         CU(launch_persistent(a, e->has_theta, e->has_iext, e->persist_resident, e->persist_blocks, e->stream));
     }
@@ -1326,6 +1357,15 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     if (k == "phase_timers") { e->phase_timers = value != 0; return BMTK_OK; }
     if (k == "replay_on_overflow") { e->replay = value != 0; return BMTK_OK; }
     if (k == "ring_prefetch") { e->ring_prefetch = value != 0; return BMTK_OK; }
+    if (k == "ring_stage") { e->ring_stage = value != 0; return BMTK_OK; }
+    if (k == "pipeline_warps") {
+        if (value != 0 && value != (long long)pipelined_warps() && value != (long long)pipelined_warps_small())
+            return fail(BMTK_E_INVALID, "pipeline_warps is 0 (choose), %u or %u", pipelined_warps_small(), pipelined_warps());
+        if (e->finalized && e->n_ranks > 1)
+            return fail(BMTK_E_INVALID, "with several ranks option 'pipeline_warps' must be set before finalize");
+        e->pipe_warps_opt = (uint32_t)value;
+        return BMTK_OK;
+    }
     if (k == "tune") { e->tune = (uint32_t)value; return BMTK_OK; }
     if (k == "chunk_steps") {
         if (value < 1) return fail(BMTK_E_INVALID, "chunk_steps must be positive");
@@ -1342,6 +1382,7 @@ int bmtk_engine_set_option(bmtk_engine* e, const char* key, int64_t value) {
     else if (k == "trial_base") e->trial_base = (uint32_t)value;
     else if (k == "window") e->window_opt = (uint32_t)value;
     else if (k == "pipeline_blocks") e->pipe_blocks_opt = (uint32_t)value;
+    else if (k == "pipeline_trials") e->pipe_trials_opt = (uint32_t)value;
     else if (k == "spike_capacity") e->spike_cap_opt = (uint64_t)value;
     else if (k == "log_capacity") e->log_cap = std::max<uint64_t>(1024, (uint64_t)value);
     else if (k == "event_capacity") e->event_cap = std::max<uint64_t>(1024, (uint64_t)value);
@@ -1608,12 +1649,28 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         int coop = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
         if (!coop || blocks > 512) e->persist_blocks = 0;
-        if (e->persist_blocks > 0 && e->n_trials == 1 && e->window >= 2 && e->n_edges < (1ull << 32)) {
+        if (e->persist_blocks > 0 && e->n_trials <= 4096 && e->ring_slots < (1u << 20) && e->window >= 2 &&
+            e->n_edges < (1ull << 32)) {
             int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt, pipelined_warps() - 1u));   // the most a block can need
             if (pb > 0 && e->pipe_blocks_opt) pb = std::min<int>(pb, (int)e->pipe_blocks_opt);
             if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
                 // chunks of 32 groups are dealt round-robin to the update warps of the blocks
-                const uint64_t chunks = ((uint64_t)(e->n_pad / 4) + 31) / 32;
+                const uint64_t chunks1 = ((uint64_t)(e->n_pad1 / 4) + 31) / 32;   // of one trial
+                // trials per launch: as many as leave a third of a block's warps to the delivering side and keep the ring
+                // slots of the launch within ~3/4 of L2 (option pipeline_trials overrides)
+                e->pipe_trials = 1;
+                if (e->n_trials > 1) {
+                    int l2 = 0;
+                    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, e->device);
+                    const uint64_t ring1 = (uint64_t)e->ring_slots * kPorts * e->n_pad1 * 4;
+                    uint32_t t = 1;
+                    while (t < e->n_trials && ((chunks1 * (t + 1) + pb - 1) / pb) <= pipelined_max_update_warps() - 3u &&
+                           ring1 * (t + 1) <= (uint64_t)l2 / 4 * 3)
+                        ++t;
+                    if (e->pipe_trials_opt) t = std::min<uint32_t>(e->pipe_trials_opt, e->n_trials);
+                    e->pipe_trials = t;
+                }
+                const uint64_t chunks = chunks1 * e->pipe_trials;
                 e->pipe_upd_warps = (uint32_t)std::max<uint64_t>(1, (chunks + pb - 1) / pb);
                 e->pipe_ok = e->pipe_upd_warps <= pipelined_max_update_warps();
                 e->pipe_blocks = pb;
@@ -1621,7 +1678,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
                     // a block adds its share of the Poisson spikes to its segment of the phase list: leave half for neurons
                     double lam = 0.0;
                     for (uint64_t v = 0; v < e->n_virtual; ++v) lam += (double)e->poisson_rates[v] * e->dt * 1e-3;
-                    const double per_block = lam * (e->window / 2) / pb;
+                    const double per_block = lam * e->pipe_trials * (e->window / 2) / pb;
                     if (per_block * 4.0 + 64.0 > (double)kPipeSegCap / 2) e->pipe_ok = false;
                 }
                 if (e->pipe_ok) {
@@ -2214,6 +2271,7 @@ int bmtk_engine_get_counter(bmtk_engine* e, const char* name, uint64_t* out) {
     else if (k == "pipelined") *out = use_pipelined(e) ? 1 : 0;
     else if (k == "n_pad") *out = e->n_pad;
     else if (k == "n_pad1") *out = e->n_pad1;
+    else if (k == "pipeline_trials") *out = e->pipe_trials;
     else if (k == "trials") *out = e->n_trials;
     else return fail(BMTK_E_INVALID, "unknown counter '%s'", name);
     return BMTK_OK;

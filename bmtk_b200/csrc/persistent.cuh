@@ -55,7 +55,13 @@ struct PersistArgs {
     uint32_t* pipe_sync;       // pipelined kernel: [0..3] blocks whose producing side, [4..7] whose chunk warps finished phase p mod 4
     uint32_t log_seg_cap;      // pipelined kernel: block b logs spikes into [b * log_seg_cap, (b + 1) * log_seg_cap) ...
     uint32_t* log_seg_cnt;     // ... and leaves its entry count here
+    uint32_t block_warps;      // pipelined kernel: warps of a block (20, or 12 where that leaves enough chunk warps)
     uint32_t upd_warps;        // pipelined kernel: update warps of a block
+    // pipelined kernel, several trials: one launch steps the cells [cell0, cell0 + n_cells) - whole trials, the first of
+    // them trial0 - so that their ring slots stay in L2; the launches of a chunk of steps follow one another over the
+    // trials, append to the same spike log (log_append) and only the last moves the clock (advance_clock)
+    uint32_t cell0, n_cells, trial0, log_append, advance_clock;
+    uint32_t ring_stage;       // pipelined kernel, phases of several steps: copy the next step's ring cells to shared memory ahead
     uint32_t input_warps;      // pipelined kernel: warps of a block that prepare input spikes; the rest stream chunks
     // clamp events grouped by step: group g covers events [ce_group_ptr[g], ce_group_ptr[g+1])
     const unsigned long long* ce_group_step;

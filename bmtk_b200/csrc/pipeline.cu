@@ -44,7 +44,8 @@ namespace bmtk {
 // A block has 20 warps (640 threads, 96 registers each). The first PersistArgs::upd_warps of them are
 // update warps - as many as the network needs at 128 neurons per warp, at most 16 - and the rest
 // deliver: 13 + 7 for 230 924 neurons on 148 SMs, 3 + 17 for 50 000.
-constexpr int kBT = 640;
+constexpr int kBT = 640;            // threads of a block: 20 warps (96 registers a thread), or ...
+constexpr int kBTSmall = 384;       // ... 12 warps (up to 168 registers: the update runs without spills) where they are enough
 constexpr int kWarps = kBT / 32;
 constexpr int kMaxUpdWarps = 16;
 constexpr uint32_t kChunk = 256;    // entries of one chunk: the unit of work of one delivery warp (8 per lane)
@@ -64,12 +65,15 @@ static_assert(sizeof(PipeShared) % 16 == 0, "the type table behind it is read wi
 
 // Warps of a block that stream chunks: all but the update and input warps and, with several ranks, the sender warp.
 __device__ __forceinline__ uint32_t chunk_warps(const PersistArgs& a) {
-    return kWarps - a.upd_warps - a.input_warps - (a.n_ranks > 1u ? 1u : 0u);
+    return a.block_warps - a.upd_warps - a.input_warps - (a.n_ranks > 1u ? 1u : 0u);
 }
 
 __device__ __forceinline__ uint32_t wrap_slot(uint32_t slot, uint32_t n) { return slot >= n ? slot - n : slot; }
 
-// Adds the CSR row [begin, begin + len), emitted at ring slot slot0, to this block's segment of list L.
+// Third word of a chunk descriptor: ring slot of the emitting step | trial of the source << kTrialShift.
+constexpr uint32_t kTrialShift = 20, kSlotMask = (1u << kTrialShift) - 1u;
+
+// Adds the CSR row [begin, begin + len), emitted at ring slot (and in trial) slot0, to this block's segment of list L.
 __device__ __forceinline__ void push_chunks(const PersistArgs& a, PipeShared& sh, uint32_t L, uint32_t tag, uint32_t begin,
                                             uint32_t len, uint32_t slot0) {
     const uint32_t n = (len + kChunk - 1) / kChunk;
@@ -155,23 +159,26 @@ __device__ __forceinline__ void prepare_inputs(const PersistArgs& a, PipeShared&
                                                const CachedCell& cc, unsigned long long start,
                                                uint32_t slot, uint32_t len, uint32_t t, uint32_t n_thr, DeliveryTotals& tot) {
     if (a.poisson_thr) {
-        const uint32_t v0 = t * gridDim.x + blockIdx.x;
-        for (uint32_t v = v0; v < a.n_virtual; v += n_thr * gridDim.x) {
+        // cell v % n_virtual of trial trial0 + v / n_virtual, over the trials of this launch
+        const uint32_t v0 = t * gridDim.x + blockIdx.x, n_virt_all = a.n_virtual * (a.n_cells / a.n_pad1);
+        for (uint32_t v = v0; v < n_virt_all; v += n_thr * gridDim.x) {
+            const uint32_t tl = v / a.n_virtual, cell = v - tl * a.n_virtual, trial = a.trial0 + tl;
             // the first cell of a thread is kept in registers: no load between the barrier and its spikes
-            const uint4 thr = v == v0 ? cc.thr : __ldg(a.poisson_thr + v);
+            const uint4 thr = v == v0 ? cc.thr : __ldg(a.poisson_thr + cell);
             for (uint32_t j = 0; j < len; ++j) {
                 const unsigned long long step = start + j;
-                const uint32_t x = philox4x32_10(v, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base, (uint32_t)a.seed,
+                const uint32_t x = philox4x32_10(cell, (uint32_t)step, (uint32_t)(step >> 32), a.trial_base + trial, (uint32_t)a.seed,
                                                  (uint32_t)(a.seed >> 32)).x;
                 const uint32_t k = (x >= thr.x) + (x >= thr.y) + (x >= thr.z) + (x >= thr.w);
                 if (k) {
                     uint32_t rb = cc.begin, rl = cc.len;
                     if (v != v0) {
-                        const unsigned long long b0 = a.rowptr[a.n_global + v], b1 = a.rowptr[a.n_global + v + 1];
+                        const unsigned long long b0 = a.rowptr[a.n_global + cell], b1 = a.rowptr[a.n_global + cell + 1];
                         rb = (uint32_t)b0;
                         rl = (uint32_t)(b1 - b0);
                     }
-                    for (uint32_t c = 0; c < k; ++c) push_chunks(a, sh, L, tag, rb, rl, wrap_slot(slot + j, a.ring_slots));
+                    for (uint32_t c = 0; c < k; ++c)
+                        push_chunks(a, sh, L, tag, rb, rl, wrap_slot(slot + j, a.ring_slots) | (trial << kTrialShift));
                     tot.inputs += k;
                 }
             }
@@ -210,6 +217,11 @@ __device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(sa), "l"(gmem) : "memory");
 }
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+
 __device__ __forceinline__ void stage_flush(const PersistArgs& a, Stager& s, uint32_t lane) {
     const uint32_t tb = a.target_bits, tmask = (1u << tb) - 1u;
     const size_t plane = (size_t)a.n_pad;
@@ -222,11 +234,13 @@ __device__ __forceinline__ void stage_flush(const PersistArgs& a, Stager& s, uin
         __syncwarp();
         const uint4 d = s.desc[i];
         const uint2* src = s.buf + i * kChunk;
+        const uint32_t slot0 = d.z & kSlotMask;
+        float* const cells = a.ring + (size_t)(d.z >> kTrialShift) * a.n_pad1;   // the source's trial
         for (uint32_t u = lane; u < d.y; u += 32u) {   // a lane applies the entries it copied itself
             const uint2 e = src[u];
-            uint32_t slot = d.z + (e.x >> (tb + 2));
+            uint32_t slot = slot0 + (e.x >> (tb + 2));
             if (slot >= a.ring_slots) slot -= a.ring_slots;
-            atomicAdd(a.ring + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
+            atomicAdd(cells + ((size_t)slot * kPorts + ((e.x >> tb) & 3u)) * plane + (e.x & tmask), __uint_as_float(e.y));
         }
     }
     __syncwarp();
@@ -234,7 +248,8 @@ __device__ __forceinline__ void stage_flush(const PersistArgs& a, Stager& s, uin
 }
 
 __device__ __forceinline__ void stage_add(const PersistArgs& a, Stager& s, const uint4 d, uint32_t lane) {
-    if ((unsigned long long)d.x + d.y > a.n_entries || d.y > kChunk || d.z >= a.ring_slots) {
+    if ((unsigned long long)d.x + d.y > a.n_entries || d.y > kChunk || (d.z & kSlotMask) >= a.ring_slots ||
+        (d.z >> kTrialShift) >= a.n_trials) {
         if (lane == 0) atomicOr(&a.ctl->error_flags, kErrBadChunk);
         return;
     }
@@ -372,10 +387,11 @@ __device__ __forceinline__ void queue_block_spikes(const PersistArgs& a, PipeSha
     const uint32_t n = min(sh.count[par], kPendP);
     for (uint32_t k = t; k < n; k += n_thr) {
         const uint32_t ent = sh.pend[par][k];
-        const uint32_t local = (ent & kSrcMask) - a.lo, grp = local >> 2;
+        const uint32_t cell = (ent & kSrcMask) - a.lo, local = cell - a.cell0, grp = local >> 2;
         const uint32_t thr = ((grp >> 5) / gridDim.x) * 32u + (grp & 31u);
         const uint2 r = sh.rows[thr * kNeuronsPerThread + (local & 3u)];
-        push_chunks(a, sh, L, tag, r.x, r.y, wrap_slot(slot + (ent >> kSrcBits), a.ring_slots));
+        const uint32_t trial = a.n_trials > 1u ? cell / a.n_pad1 : 0u;
+        push_chunks(a, sh, L, tag, r.x, r.y, wrap_slot(slot + (ent >> kSrcBits), a.ring_slots) | (trial << kTrialShift));
     }
 }
 
@@ -409,8 +425,8 @@ __device__ __forceinline__ void log_previous_phase(const PersistArgs& a, PipeSha
     }
 }
 
-template <bool THETA, bool IEXT, bool MULTI>
-__global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) {
+template <bool THETA, bool IEXT, bool MULTI, int BT>
+__global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     cg::grid_group grid = cg::this_grid();
     PipeShared& sh = *reinterpret_cast<PipeShared*>(smem_raw);
@@ -424,14 +440,16 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         const int words = a.n_types * (int)(sizeof(TypeConsts) / 4);
         const uint32_t* src = reinterpret_cast<const uint32_t*>(a.types);
         uint32_t* dst = reinterpret_cast<uint32_t*>(s_types);
-        for (int i = threadIdx.x; i < words; i += kBT) dst[i] = src[i];
+        for (int i = threadIdx.x; i < words; i += BT) dst[i] = src[i];
     }
     const TypeConsts* types = use_smem ? s_types : a.types;
     // behind the type table: the warps' staging buffers for CSR entries
     uint2* const s_stage = reinterpret_cast<uint2*>(smem_raw + sizeof(PipeShared) +
                                                     (use_smem ? (sizeof(TypeConsts) * (size_t)a.n_types + 15) / 16 * 16 : 0));
 
-    const uint32_t kUT = 32u * a.upd_warps, kDT = kBT - kUT, kDW = kDT / 32u;
+    const uint32_t kUT = 32u * a.upd_warps, kDT = BT - kUT, kDW = kDT / 32u;
+    // behind the chunk warps' staging buffers: two buffers of ring cells per update thread (option ring_stage)
+    float4* const s_ring = reinterpret_cast<float4*>(s_stage + (size_t)chunk_warps(a) * kStage * kChunk);
     // delivery warps: kCW stream chunks, then the input warps, then (several ranks) the sender warp
     const uint32_t kCW = kDW - a.input_warps - (MULTI ? 1u : 0u);
     const uint32_t n_prod_threads = kUT + 32u * a.input_warps, n_cons_threads = 32u * kCW;
@@ -445,14 +463,15 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
     bool sync_dead = false;
     const bool is_upd = threadIdx.x < kUT;
     const uint32_t dtid = threadIdx.x - kUT;
-    const uint32_t n_groups = a.n_pad / kNeuronsPerThread;
+    const uint32_t n_groups = a.n_cells / kNeuronsPerThread;
     const unsigned long long step_base = __ldcg(&a.ctl->step_base);
     const uint32_t sample_base = __ldcg(&a.ctl->sample_base);
     // Neurons are dealt to the update warps in chunks of 128 (32 lanes x 4), round-robin over the blocks:
     // chunk c belongs to warp c / gridDim.x of block c % gridDim.x. Neurons are sorted by type, so every
     // block gets its share of every type.
     const uint32_t my_group = ((threadIdx.x >> 5) * gridDim.x + blockIdx.x) * 32u + (threadIdx.x & 31u);
-    const uint32_t i0 = my_group * kNeuronsPerThread;
+    const uint32_t i0 = a.cell0 + my_group * kNeuronsPerThread;   // first of the thread's four cells (trial-major with several trials)
+    const uint32_t li0 = a.n_trials > 1u ? i0 % a.n_pad1 : i0;    // ... inside its trial
     const bool mine = is_upd && my_group < n_groups;
     const bool timer_u = a.profile && threadIdx.x == 0;      // every block times itself; block 0's sums also go to the control block
     const bool timer_d = a.profile && threadIdx.x == kUT;
@@ -463,7 +482,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         bool any = false;
         while (cgi < a.ce_group_end && a.ce_group_step[cgi] <= step_base) {
             const uint32_t b = a.ce_group_ptr[cgi], e = a.ce_group_ptr[cgi + 1];
-            for (uint32_t k = b + blockIdx.x * kBT + threadIdx.x; k < e; k += gridDim.x * kBT)
+            for (uint32_t k = b + blockIdx.x * BT + threadIdx.x; k < e; k += gridDim.x * BT)
                 atomicAdd(&a.st.i_ext[a.ce_target[k] - a.lo], a.ce_delta[k]);
             ++cgi;
             any = true;
@@ -516,7 +535,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             }
 #pragma unroll
             for (int j = 0; j < kNeuronsPerThread; ++j) {
-                const unsigned long long rb = a.rowptr[a.lo + i0 + j], re = a.rowptr[a.lo + i0 + j + 1];
+                const uint32_t row = a.lo + min(li0 + (uint32_t)j, a.n_local - 1u);   // (cells beyond n_local are padding and never spike)
+                const unsigned long long rb = a.rowptr[row], re = a.rowptr[row + 1];
                 sh.rows[threadIdx.x * kNeuronsPerThread + j] = make_uint2((uint32_t)rb, (uint32_t)(re - rb));
             }
         }
@@ -528,6 +548,9 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             sample = (step_base + 1ull) / a.probe_interval - 1ull - sample_base;
             if (pctr != 0) sample += 1ull;   // the next multiple of the interval
         }
+        // phases of several steps: the ring cells of step j + 1 (final since the phase began) are copied to shared
+        // memory while step j computes, so that only the first step of a phase waits for an L2 round trip
+        float4* const my_ring = s_ring + threadIdx.x;   // [buffer][port][update thread]
         while (s < a.n_steps) {
             PIPE_PHASE_BEGIN()
             const unsigned long long t_warp = a.profile ? gtimer() : 0ull;
@@ -540,11 +563,29 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
                 uint32_t mask = 0;
                 if (mine) {
                     float* ring = a.ring + (size_t)sl * kPorts * a.n_pad + i0;
-                    F4 in[kPorts];
+                    const bool ahead = a.ring_stage && j + 1u < len;
+                    if (ahead) {
+                        const float* nxt = a.ring + (size_t)wrap_slot(sl + 1u, S) * kPorts * a.n_pad + i0;
 #pragma unroll
-                    for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
+                        for (int pt = 0; pt < kPorts; ++pt)
+                            cp_async16(my_ring + (((j + 1u) & 1u) * kPorts + pt) * kUT, nxt + (size_t)pt * a.n_pad);
+                        asm volatile("cp.async.commit_group;" ::: "memory");
+                    }
+                    F4 in[kPorts];
+                    if (a.ring_stage && j > 0u) {
+                        if (ahead) asm volatile("cp.async.wait_group 1;" ::: "memory");
+                        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+                        for (int pt = 0; pt < kPorts; ++pt) {
+                            const float4 t = my_ring[((j & 1u) * kPorts + pt) * kUT];
+                            in[pt] = F4{{t.x, t.y, t.z, t.w}};
+                        }
+                    } else {
+#pragma unroll
+                        for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
+                    }
                     mask = nr.step(types, in);
-                    if (i0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > i0 ? a.n_local - i0 : 0)) - 1u;
+                    if (li0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > li0 ? a.n_local - li0 : 0)) - 1u;
                     const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
                     for (int pt = 0; pt < kPorts; ++pt) {
@@ -615,7 +656,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
             ++p;
         }
         if (mine) nr.store(a.st, a.n_pad, i0);
-        if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl->step_base = step_base + a.n_steps;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && a.advance_clock) a.ctl->step_base = step_base + a.n_steps;
         if (timer_u) {
             if (blockIdx.x == 0) {
                 a.ctl->t_update_ns += acc_work;
@@ -633,7 +674,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         const bool input_role = dwarp >= kCW && dwarp < kCW + a.input_warps;
         const bool sender_role = MULTI && dwarp == kCW + a.input_warps;
         const uint32_t log_warp = kCW;   // the first input warp (a block always has one)
-        uint32_t log_pos = 0;   // entries this block has logged in this launch
+        const uint32_t log_pos0 = (a.log_append && a.log_stamp) ? a.log_seg_cnt[blockIdx.x] : 0u;
+        uint32_t log_pos = log_pos0;   // entries in this block's log segment
         const uint32_t it = dtid - 32u * kCW, n_it = 32u * a.input_warps;   // input thread index / count
         unsigned long long prev_start = step_base;
         uint32_t prev_slot = slot;   // ring slot of the previous phase's first step
@@ -643,8 +685,8 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         sg.desc = sh.sdesc[threadIdx.x >> 5];
         sg.m = 0;
         CachedCell cc = {make_uint4(0u, 0u, 0u, 0u), 0u, 0u};
-        if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual) {
-            const uint32_t v0 = it * gridDim.x + blockIdx.x;
+        if (input_role && a.poisson_thr && it * gridDim.x + blockIdx.x < a.n_virtual * (a.n_cells / a.n_pad1)) {
+            const uint32_t v0 = (it * gridDim.x + blockIdx.x) % a.n_virtual;
             cc.thr = __ldg(a.poisson_thr + v0);
             const unsigned long long b0 = a.rowptr[a.n_global + v0], b1 = a.rowptr[a.n_global + v0 + 1];
             cc.begin = (uint32_t)b0;
@@ -754,7 +796,7 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
         }
         if (dwarp == log_warp && lane == 0 && a.log_stamp) {
             a.log_seg_cnt[blockIdx.x] = log_pos;
-            if (log_pos) atomicAdd(&a.ctl->log_count, log_pos);
+            if (log_pos > log_pos0) atomicAdd(&a.ctl->log_count, log_pos - log_pos0);
         }
         if (timer_d) {
             if (blockIdx.x == 0) {
@@ -776,41 +818,53 @@ __global__ void __launch_bounds__(kBT, 1) pipelined_kernel(const PersistArgs a) 
 #undef PIPE_PHASE_BEGIN
 }
 
-static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext, bool multi) {
+template <int BT>
+static const void* pipelined_kernel_ptr_bt(bool has_theta, bool has_iext, bool multi) {
     if (multi)   // clamp changes are not supported with several ranks (the phase schedules would differ)
-        return has_theta ? (const void*)pipelined_kernel<true, false, true> : (const void*)pipelined_kernel<false, false, true>;
+        return has_theta ? (const void*)pipelined_kernel<true, false, true, BT> : (const void*)pipelined_kernel<false, false, true, BT>;
     if (has_theta)
-        return has_iext ? (const void*)pipelined_kernel<true, true, false> : (const void*)pipelined_kernel<true, false, false>;
-    return has_iext ? (const void*)pipelined_kernel<false, true, false> : (const void*)pipelined_kernel<false, false, false>;
+        return has_iext ? (const void*)pipelined_kernel<true, true, false, BT> : (const void*)pipelined_kernel<true, false, false, BT>;
+    return has_iext ? (const void*)pipelined_kernel<false, true, false, BT> : (const void*)pipelined_kernel<false, false, false, BT>;
+}
+
+static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext, bool multi, uint32_t block_warps) {
+    return block_warps * 32u == (uint32_t)kBTSmall ? pipelined_kernel_ptr_bt<kBTSmall>(has_theta, has_iext, multi)
+                                                   : pipelined_kernel_ptr_bt<kBT>(has_theta, has_iext, multi);
 }
 
 // Shared memory of a block: lists, type table, and a staging buffer of kStage chunks for each of `chunk_warps` warps
 // (a small shared-memory carve-out leaves more L1 for the update warps' spilled registers).
-size_t pipelined_smem(int n_types, uint32_t chunk_warps) {
+size_t pipelined_smem(int n_types, uint32_t chunk_warps, uint32_t ring_stage_warps) {
     return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0) +
-           (size_t)chunk_warps * kStage * kChunk * sizeof(uint2);
+           (size_t)chunk_warps * kStage * kChunk * sizeof(uint2) + (size_t)ring_stage_warps * 32 * 2 * kPorts * sizeof(float4);
 }
 
 uint32_t pipelined_max_update_warps() { return kMaxUpdWarps; }
 uint32_t pipelined_warps() { return kWarps; }
+uint32_t pipelined_warps_small() { return kBTSmall / 32; }
 
 int pipelined_max_blocks(int device, bool has_theta, bool has_iext, size_t smem) {
-    int per_sm = 0, sms = 0;
-    const void* f = pipelined_kernel_ptr(has_theta, has_iext, false);
-    if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, kBT, smem) != cudaSuccess) return 0;
+    int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    return per_sm > 0 ? sms : 0;   // one block per SM
+    for (uint32_t bw : {(uint32_t)kWarps, (uint32_t)(kBTSmall / 32)}) {
+        int per_sm = 0;
+        const void* f = pipelined_kernel_ptr(has_theta, has_iext, false, bw);
+        if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f, (int)bw * 32, smem) != cudaSuccess) return 0;
+        if (per_sm <= 0) return 0;
+    }
+    return sms;   // one block per SM
 }
 
 cudaError_t launch_pipelined(const PersistArgs& a, bool has_theta, bool has_iext, int blocks, cudaStream_t s) {
-    const size_t smem = pipelined_smem(a.n_types, kWarps - a.upd_warps - a.input_warps - (a.n_ranks > 1 ? 1u : 0u));
-    const void* f = pipelined_kernel_ptr(has_theta, has_iext, a.n_ranks > 1);
+    const size_t smem = pipelined_smem(a.n_types, a.block_warps - a.upd_warps - a.input_warps - (a.n_ranks > 1 ? 1u : 0u),
+                                       a.ring_stage ? a.upd_warps : 0u);
+    const void* f = pipelined_kernel_ptr(has_theta, has_iext, a.n_ranks > 1, a.block_warps);
     cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     PersistArgs copy = a;
     void* args[] = {&copy};
-    return cudaLaunchCooperativeKernel(f, dim3(blocks), dim3(kBT), args, smem, s);
+    return cudaLaunchCooperativeKernel(f, dim3(blocks), dim3(a.block_warps * 32u), args, smem, s);
 }
 
 }  // namespace bmtk

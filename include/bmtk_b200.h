@@ -158,10 +158,16 @@ int bmtk_engine_record_state(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids
  *  "persistent"     0|1 run each chunk as ONE cooperative kernel that loops over the steps with the
  *                   neuron state held in registers (default 1; single rank, atomic delivery; may
  *                   be changed between runs)
- *  "pipeline"       0|1 persistent stepping with update and delivery warps side by side on every SM and one
- *                   grid barrier per min_delay / 2 steps (default 1; used when the state fits in registers,
- *                   there is one trial and the minimum delay is at least 2 steps; counter "pipelined"; may be
- *                   changed between runs)
+ *  "pipeline"       0|1 persistent stepping with update and delivery warps side by side on every SM, handing
+ *                   over once per min_delay / 2 steps (default 1; used when the state fits in registers and the
+ *                   minimum delay is at least 2 steps; counter "pipelined"; may be changed between runs)
+ *  "pipeline_trials" with "trials" > 1: trials one launch of the pipelined kernel steps (a chunk of steps is run for
+ *                   that many trials at a time, one group after the other, so that the ring slots a launch scatters
+ *                   into stay in L2). Default 0: as many as fit the update warps of a block and 3/4 of L2;
+ *                   counter "pipeline_trials" has the value in use. Before finalize.
+ *  "ring_stage"     0|1 pipelined kernel, minimum delay of 4 steps or more (phases of several steps): the ring cells of
+ *                   the next step are copied to shared memory while a step computes (default 1; may be changed
+ *                   between runs)
  *  "ring_prefetch"  0|1 persistent kernel with resident state: fetch the next step's ring slot into shared
  *                   memory with cp.async while the current step computes (default 0: on the 2-step
  *                   windows of the benchmark network it measured 3 % slower than plain L2 loads)

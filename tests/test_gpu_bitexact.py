@@ -128,3 +128,48 @@ def test_grid_weights_make_the_atomic_kernels_exact_too(cabi, oracle):
         eng = W.build_engine(net, options=opts)
         eng.run(net.n_steps)
         _compare(net, eng, r, sim)
+
+
+def test_phases_of_four_steps_with_staged_ring_cells(cabi, oracle):
+    """E/I network with minimum delay 8 steps: the pipelined kernel runs phases of 4 steps and copies the ring cells of
+    the next step to shared memory while a step computes (option ring_stage). Weights on the 0.25 pA grid: with and
+    without the staging, and in the two-phase kernel, every bit must be the restatement's."""
+    net = W.c2(n=5000, in_degree=200, n_virtual=200, t_stop_ms=200.0, input_weight=90.0)
+    net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+    sim = oracle_f32_from_network(net, 8, 700)
+    r = sim.run(net.n_steps)
+    assert len(r['spike_step']) > 1500
+    for opts in (dict(), dict(ring_stage=0), dict(pipeline=0)):
+        eng = W.build_engine(net, options=dict(chunk_steps=700, **opts))
+        assert eng.counter('window') == 8
+        eng.run(net.n_steps)
+        assert eng.counter('pipelined') == (0 if 'pipeline' in opts else 1)
+        _compare(net, eng, r, sim)
+
+
+@pytest.mark.parametrize('per_launch', [0, 2])
+def test_trial_batches_every_trial_every_bit(cabi, oracle, per_launch):
+    """Three trials over one CSR in the pipelined kernel - all in one launch, or two per launch and then the third -
+    with weights on the 0.25 pA grid: each trial must be, bit for bit, the restatement's run of that trial's Poisson
+    stream (spikes, events, final membrane state)."""
+    T = 3
+    net = W.c2(n=4000, in_degree=150, n_virtual=200, t_stop_ms=150.0, input_weight=90.0)
+    net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+    eng = W.build_engine(net, record_vm=False, options=dict(trials=T, pipeline_trials=per_launch, chunk_steps=700))
+    eng.run(net.n_steps)
+    assert eng.counter('pipelined') == 1 and eng.counter('pipeline_trials') == (per_launch or T)
+    st, ids = eng.fetch_spikes()
+    st, ids = st.astype(np.int64), ids.astype(np.int64)
+    n_pad1, n = eng.counter('n_pad1'), net.n_neurons
+    U = eng.state('U')
+    events = 0
+    for t in range(T):
+        sim = oracle_f32_from_network(net, 8, 700)
+        sim.set_poisson(net.poisson_rate_hz, net.poisson_seed, stream=t)
+        r = sim.run(net.n_steps)
+        assert len(r['spike_step']) > 500
+        m = ids // n_pad1 == t
+        assert np.array_equal(st[m], r['spike_step']) and np.array_equal(ids[m] - t * n_pad1, r['spike_id']), t
+        assert np.array_equal(_bits(U[t * n_pad1:t * n_pad1 + n]), _bits(sim.U)), t
+        events += r['n_events']
+    assert eng.counter('events') == events

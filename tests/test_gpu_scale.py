@@ -88,16 +88,24 @@ def test_c2_reduced_against_oracle(cabi, deterministic):
     assert K.rate_agreement(net.type_index, len(net.types), ids, r['spike_id'], 400.0)['ok'], (rg, rc)
 
 
-def test_trial_batching_shares_the_csr(cabi, oracle):
+@pytest.mark.parametrize('mode', ['pipelined_one_launch', 'pipelined_groups_of_2', 'two_phase'])
+def test_trial_batching_shares_the_csr(cabi, oracle, mode):
     """Option "trials": T independent copies of a network over ONE CSR, each with its own Philox stream
     (counter word 3 = trial). Every trial must reproduce the oracle run of that trial's input stream
     (spikes within one step over the first 100 ms, then until the first divergence), the trials must
-    differ from each other, and events / input spikes must add up exactly over the trials."""
+    differ from each other, and events / input spikes must add up exactly over the trials. The pipelined
+    kernel steps all trials in one launch or, group by group, two at a time (the last group has one);
+    the two-phase kernel is the third way."""
     T = 5
     net = W.c2(n=3000, in_degree=150, n_virtual=150, t_stop_ms=300.0, input_weight=90.0)
-    eng = W.build_engine(net, record_vm=False, options=dict(trials=T))
+    opts = dict(pipelined_one_launch=dict(), pipelined_groups_of_2=dict(pipeline_trials=2, chunk_steps=1100),
+                two_phase=dict(pipeline=0))[mode]
+    eng = W.build_engine(net, record_vm=False, options=dict(trials=T, **opts))
     assert eng.counter('trials') == T and eng.csr_info()['n_edges'] == net.n_edges
     eng.run(net.n_steps)
+    assert eng.counter('pipelined') == (0 if mode == 'two_phase' else 1)
+    if mode != 'two_phase':
+        assert eng.counter('pipeline_trials') == (5 if mode == 'pipelined_one_launch' else 2)
     st, ids = eng.fetch_spikes()
     st, ids = st.astype(np.int64), ids.astype(np.int64)
     n_pad1 = eng.counter('n_pad1')
