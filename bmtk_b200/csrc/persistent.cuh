@@ -80,7 +80,7 @@ struct PersistArgs {
     uint32_t ring_prefetch;    // RESIDENT: copy the next step's ring slot to shared memory while this step computes
     unsigned long long* blk_prof;   // pipelined kernel, option phase_timers: per block {producing side busy ns, its hand-over wait ns,
                                // delivering side busy ns, its hand-over wait ns}, summed over the launch
-    uint32_t tune;             // pipelined kernel: experiment switches (none in use)
+    uint32_t tune;             // pipelined kernel: 1 = scalar arithmetic in every block size, 2 = packed in every block size
     // Spike exchange between ranks over peer memory (n_ranks > 1). Every rank owns an exchange
     // buffer of 64-bit words laid out as  counts[2][kXRanks] | inbox[2][n_ranks][xchg_cap];
     // peers[r] is rank r's buffer as mapped into this process (peers[rank] is the local one).

@@ -52,6 +52,13 @@ constexpr uint32_t kChunk = 256;    // entries of one chunk: the unit of work of
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
 constexpr uint32_t kSpill = 4;      // a block's chunks kDW*r .. kDW*r + kDW-1 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
+constexpr int kSmemTypes2 = 64;   // up to this many types the doubled constants for the packed arithmetic are kept as well
+
+// bytes of the type tables in shared memory
+__host__ __device__ constexpr size_t type_table_bytes(int n_types) {
+    return (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0) +
+           (n_types <= kSmemTypes2 ? sizeof(TypeConsts2) * (size_t)n_types : 0);
+}
 struct __align__(16) PipeShared {
     uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
@@ -443,9 +450,22 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
         for (int i = threadIdx.x; i < words; i += BT) dst[i] = src[i];
     }
     const TypeConsts* types = use_smem ? s_types : a.types;
-    // behind the type table: the warps' staging buffers for CSR entries
-    uint2* const s_stage = reinterpret_cast<uint2*>(smem_raw + sizeof(PipeShared) +
-                                                    (use_smem ? (sizeof(TypeConsts) * (size_t)a.n_types + 15) / 16 * 16 : 0));
+    // the constants of the integrating step once more, doubled, for the packed arithmetic
+    // (in the 12-warp block only: with the 96 registers of the 20-warp block the packed code spills more and came out
+    // 2-5 % slower than the scalar code, against 11 % faster where registers are plentiful; tune 1 / 2 force either)
+    const bool packed = a.n_types <= kSmemTypes2 && (a.tune & 2u ? true : a.tune & 1u ? false : BT == kBTSmall);
+    TypeConsts2* const s_types2 = reinterpret_cast<TypeConsts2*>(smem_raw + sizeof(PipeShared) +
+                                                                 (sizeof(TypeConsts) * (size_t)a.n_types + 15) / 16 * 16);
+    if (packed) {
+        const float* src = reinterpret_cast<const float*>(a.types);
+        float2* dst = reinterpret_cast<float2*>(s_types2);
+        for (int i = threadIdx.x; i < a.n_types * kDupFloats; i += BT) {
+            const float c = src[(i / kDupFloats) * (int)(sizeof(TypeConsts) / 4) + i % kDupFloats];
+            dst[i] = make_float2(c, c);
+        }
+    }
+    // behind the type tables: the warps' staging buffers for CSR entries
+    uint2* const s_stage = reinterpret_cast<uint2*>(smem_raw + sizeof(PipeShared) + type_table_bytes(a.n_types));
 
     const uint32_t kUT = 32u * a.upd_warps, kDT = BT - kUT, kDW = kDT / 32u;
     // behind the chunk warps' staging buffers: two buffers of ring cells per update thread (option ring_stage)
@@ -525,14 +545,9 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
         // ================= update warps
         Neuron4<THETA, IEXT> nr;
         bool clamp_now = false;
-        int pslot[4] = {-1, -1, -1, -1};
         if (mine) {
             nr.load(a.st, a.n_pad, i0);
             if (IEXT) nr.iex = ld4cg(a.st.i_ext + i0);
-            if (a.probe_slot) {
-                const int4 qd = *reinterpret_cast<const int4*>(a.probe_slot + i0);
-                pslot[0] = qd.x; pslot[1] = qd.y; pslot[2] = qd.z; pslot[3] = qd.w;
-            }
 #pragma unroll
             for (int j = 0; j < kNeuronsPerThread; ++j) {
                 const uint32_t row = a.lo + min(li0 + (uint32_t)j, a.n_local - 1u);   // (cells beyond n_local are padding and never spike)
@@ -584,7 +599,7 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
 #pragma unroll
                         for (int pt = 0; pt < kPorts; ++pt) in[pt] = ld4cg(ring + (size_t)pt * a.n_pad);
                     }
-                    mask = nr.step(types, in);
+                    mask = packed ? nr.step_packed(types, s_types2, in) : nr.step(types, in);
                     if (li0 + kNeuronsPerThread > a.n_local) mask &= (1u << (a.n_local > li0 ? a.n_local - li0 : 0)) - 1u;
                     const F4 zero = {{0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -604,6 +619,9 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
                 if (a.probe_slot) {
                     if (pctr == 0) {
                         if (mine && sample < a.trace_cap) {
+                            // (the trace columns of the four neurons are fetched when a sample is due, not kept in registers)
+                            const int4 qd = __ldg(reinterpret_cast<const int4*>(a.probe_slot + i0));
+                            const int pslot[4] = {qd.x, qd.y, qd.z, qd.w};
 #pragma unroll
                             for (int jj = 0; jj < 4; ++jj)
                                 if (pslot[jj] >= 0)
@@ -835,7 +853,7 @@ static const void* pipelined_kernel_ptr(bool has_theta, bool has_iext, bool mult
 // Shared memory of a block: lists, type table, and a staging buffer of kStage chunks for each of `chunk_warps` warps
 // (a small shared-memory carve-out leaves more L1 for the update warps' spilled registers).
 size_t pipelined_smem(int n_types, uint32_t chunk_warps, uint32_t ring_stage_warps) {
-    return sizeof(PipeShared) + (n_types <= kSmemTypesPipe ? (sizeof(TypeConsts) * (size_t)n_types + 15) / 16 * 16 : 0) +
+    return sizeof(PipeShared) + type_table_bytes(n_types) +
            (size_t)chunk_warps * kStage * kChunk * sizeof(uint2) + (size_t)ring_stage_warps * 32 * 2 * kPorts * sizeof(float4);
 }
 

@@ -163,8 +163,13 @@ int bmtk_engine_record_state(bmtk_engine* e, uint64_t n_ids, const uint32_t* ids
  *                   minimum delay is at least 2 steps; counter "pipelined"; may be changed between runs)
  *  "pipeline_trials" with "trials" > 1: trials one launch of the pipelined kernel steps (a chunk of steps is run for
  *                   that many trials at a time, one group after the other, so that the ring slots a launch scatters
- *                   into stay in L2). Default 0: as many as fit the update warps of a block and 3/4 of L2;
- *                   counter "pipeline_trials" has the value in use. Before finalize.
+ *                   into stay in L2). Default 0: as many as the 12-warp block takes (else the 20-warp block) within
+ *                   3/4 of L2; counter "pipeline_trials" has the value in use. Before finalize.
+ *  "pipeline_warps" 0|12|20 warps of a block of the pipelined kernel. 12 warps have up to 168 registers a thread (no
+ *                   spills in the update, packed fma.rn.f32x2 arithmetic) and are chosen (0, the default) where
+ *                   they leave at least 5 warps to stream synapse chunks; else 20 warps at 96 registers.
+ *  "tune"           pipelined kernel: 1 = scalar arithmetic, 2 = packed arithmetic in either block size (default 0:
+ *                   packed in the 12-warp block only; same bits either way)
  *  "ring_stage"     0|1 pipelined kernel, minimum delay of 4 steps or more (phases of several steps): the ring cells of
  *                   the next step are copied to shared memory while a step computes (default 1; may be changed
  *                   between runs)

@@ -114,6 +114,16 @@ def test_threshold_dynamics_iaf_and_delta_cells(cabi, oracle):
     for t in range(5):
         assert np.count_nonzero(net.type_index[r['spike_id']] == t) > 20, t     # every variant fires
     _compare(net, eng, r, sim)
+    # the same network with weights on a 1/64 grid (sums exact in any order): the threshold, clamp and probe code of
+    # the pipelined kernel in both block sizes, scalar and packed arithmetic, and of the two-phase kernel
+    net.weight = (np.round(net.weight * 64.0) / 64.0).astype(np.float32)
+    sim = oracle_f32_from_network(net, eng.counter('window'))
+    r = sim.run(net.n_steps)
+    for opts in (dict(), dict(pipeline_warps=20), dict(pipeline_warps=20, tune=2), dict(tune=1), dict(pipeline=0)):
+        eng = W.build_engine(net, options=opts)
+        eng.run(net.n_steps)
+        assert eng.counter('pipelined') == (0 if 'pipeline' in opts else 1)
+        _compare(net, eng, r, sim)
 
 
 def test_grid_weights_make_the_atomic_kernels_exact_too(cabi, oracle):
@@ -124,7 +134,9 @@ def test_grid_weights_make_the_atomic_kernels_exact_too(cabi, oracle):
     net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
     sim = oracle_f32_from_network(net, 2)
     r = sim.run(net.n_steps)
-    for opts in (dict(), dict(pipeline=0)):
+    # default: the 12-warp block with packed arithmetic; then the 20-warp block (scalar arithmetic, what the full-size
+    # network runs), each block size with the other arithmetic, and the two-phase kernel
+    for opts in (dict(), dict(pipeline_warps=20), dict(pipeline_warps=20, tune=2), dict(pipeline_warps=12, tune=1), dict(pipeline=0)):
         eng = W.build_engine(net, options=opts)
         eng.run(net.n_steps)
         _compare(net, eng, r, sim)
@@ -139,7 +151,7 @@ def test_phases_of_four_steps_with_staged_ring_cells(cabi, oracle):
     sim = oracle_f32_from_network(net, 8, 700)
     r = sim.run(net.n_steps)
     assert len(r['spike_step']) > 1500
-    for opts in (dict(), dict(ring_stage=0), dict(pipeline=0)):
+    for opts in (dict(), dict(ring_stage=0), dict(pipeline_warps=20), dict(pipeline=0)):
         eng = W.build_engine(net, options=dict(chunk_steps=700, **opts))
         assert eng.counter('window') == 8
         eng.run(net.n_steps)
