@@ -1651,7 +1651,7 @@ int bmtk_engine_finalize(bmtk_engine* e) {
         if (!coop || blocks > 512) e->persist_blocks = 0;
         if (e->persist_blocks > 0 && e->n_trials <= 4096 && e->ring_slots < (1u << 20) && e->window >= 2 &&
             e->n_edges < (1ull << 32)) {
-            int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt, pipelined_warps() - 1u));   // the most a block can need
+            int pb = pipelined_max_blocks(e->device, e->has_theta, e->has_iext, pipelined_smem((int)nt, pipelined_warps() - 2u));   // the most a block can need (one update, one input warp)
             if (pb > 0 && e->pipe_blocks_opt) pb = std::min<int>(pb, (int)e->pipe_blocks_opt);
             if (pb > 0 && pb <= (int)kPipeMaxBlocks) {
                 // chunks of 32 groups are dealt round-robin to the update warps of the blocks

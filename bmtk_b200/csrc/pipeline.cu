@@ -48,7 +48,9 @@ constexpr int kBT = 640;            // threads of a block: 20 warps (96 register
 constexpr int kBTSmall = 384;       // ... 12 warps (up to 168 registers: the update runs without spills) where they are enough
 constexpr int kWarps = kBT / 32;
 constexpr int kMaxUpdWarps = 16;
-constexpr uint32_t kChunk = 256;    // entries of one chunk: the unit of work of one delivery warp (8 per lane)
+constexpr uint32_t kChunk = 384;    // entries of one chunk: the unit of work of one delivery warp (12 per lane). Measured on one
+                                    // box: 256 / 320 / 384 / 512 entries = 17.73 / 17.75 / 17.42 / 26.9 ms per simulated second of the
+                                    // V1-scale network (most of its rows are 250-350 entries: one chunk instead of two)
 constexpr uint32_t kPendP = 2048;   // spikes one block can emit in one phase (its neurons, once each)
 constexpr uint32_t kSpill = 4;      // a block's chunks kDW*r .. kDW*r + kDW-1 go to block b + r, for r < kSpill; the rest stay home
 constexpr int kSmemTypesPipe = 128;
