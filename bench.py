@@ -745,10 +745,14 @@ def small_config(args, torch, dist, W, world, rank, local_rank, dev, barrier, re
         ost, oid = r['spike_step'], r['spike_id'].astype(np.int64)
         s100 = int(round((200.0 if name == 'c1' else 100.0) / full.dt))    # c1: the first 100 ms of the current step
         w1 = K.within_one_step(gst, gid, ost, oid, s100, n_total)
+        strict = K.within_one_step(gst, gid, ost, oid, int(round(25.0 / full.dt)), n_total)
         ra = K.rate_agreement(full.type_index, len(full.types), gid, oid, n_steps * full.dt)
         parity = {'against': 'fp64 CPU oracle, whole run', 'spikes_gpu': int(len(gst)), 'spikes_oracle': int(len(ost)),
                   'first_divergence_step': K.first_divergence(gst, gid, ost, oid),
-                  'first_100ms': w1, 'max_type_rate_rel_err': ra['max_rel_err'], 'rates_within_2pct': ra['within_rel_only']}
+                  'first_25ms_within_one_step': strict['ok'], 'first_25ms_spikes': strict['n_b'],
+                  'first_100ms': dict(w1, share_beyond=(w1['neurons_with_other_count'] + w1['spikes_beyond_one_step']) / max(1, w1['n_b'])),
+                  'max_type_rate_rel_err': ra['max_rel_err'], 'rates_within_2pct': ra['within_rel_only'],
+                  'ok': bool(strict['ok'] and ra['within_rel_only'])}
     line = {
         'metric': metric, 'value': value, 'unit': unit, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': dev_ms / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32',
