@@ -64,6 +64,7 @@ __host__ __device__ constexpr size_t type_table_bytes(int n_types) {
 struct __align__(16) PipeShared {
     uint32_t count[2];              // spikes of the phase with that parity (for the spike log)
     uint32_t chunks[3];             // chunk descriptors this block has added to list L
+    uint32_t early[2];              // by phase parity: the producing side's leader saw the other side finished before the hand-over
     uint32_t pad;
     uint4 own[3][kWarps];      // copies of the first descriptors of list L: the ones this block delivers itself
     uint4 sdesc[kWarps][4];    // descriptors of the chunks a warp has staged (see Stager)
@@ -140,6 +141,49 @@ __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mi
         }
     }
     asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
+}
+
+// Hand-over of the producing side. In networks whose phases are long against their delivery (several steps per phase,
+// few events) the chunk warps of every block are done well before the update warps, and the hand-over's own mechanics -
+// release, poll, acquire, second barrier: three dependent L2 round trips, 1.3-1.5 us - were a fifth of the phase. So the
+// side's leader (lane 0 of the first input warp, which idles while the update warps compute) looks at the other side's
+// counter BEFORE the phase ends and leaves what it saw in sh.early; when the other side was done then, the block's
+// threads leave after ONE barrier and only the leader stays to publish the block.
+template <bool MULTI>
+__device__ __forceinline__ void prod_handover(const PersistArgs& a, PipeShared& sh, uint32_t p, uint32_t* mine, const uint32_t* other,
+                                              uint32_t target, uint32_t n_threads, bool leader, bool& dead) {
+    asm volatile("barrier.sync 2, %0;" ::"r"(n_threads) : "memory");
+    const bool done = *reinterpret_cast<volatile uint32_t*>(&sh.early[p & 1u]) != 0u;   // written before the barrier
+    if (leader) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
+    if (!done) {
+        if (leader && !dead) {
+            unsigned int spins = 0;
+            while ((int32_t)(*reinterpret_cast<const volatile uint32_t*>(other) - target) < 0) {
+                if (++spins > kSyncSpins) {
+                    atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
+                    dead = true;
+                    break;
+                }
+            }
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
+        }
+        asm volatile("barrier.sync 2, %0;" ::"r"(n_threads) : "memory");
+    }
+}
+
+// The leader's early look (a few polls at most: it must not be late for the update warps).
+__device__ __forceinline__ void early_look(PipeShared& sh, uint32_t p, const uint32_t* other, uint32_t target, bool wait, bool dead) {
+    bool done = !wait;   // the last phase of a launch waits for nobody
+    if (wait && !dead) {
+        for (int tries = 0; tries < 3 && !done; ++tries)
+            done = (int32_t)(*reinterpret_cast<const volatile uint32_t*>(other) - target) >= 0;
+        if (done) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
+        }
+    }
+    *reinterpret_cast<volatile uint32_t*>(&sh.early[p & 1u]) = done ? 1u : 0u;
 }
 
 // Option phase_timers: every warp adds the time from the start of its phase to the moment it reaches the hand-over
@@ -659,8 +703,8 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
                 const unsigned long long now = gtimer();
                 hist_add(a, 0u, now - t_warp);
             }
-            side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads,
-                          threadIdx.x == 0, s + len < a.n_steps, sync_dead);
+            prod_handover<MULTI>(a, sh, p, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, n_prod_threads, false,
+                                 sync_dead);
             if (timer_u) {
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
@@ -754,6 +798,10 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
                     if (MULTI) asm volatile("barrier.sync 4, 64;" ::: "memory");
                     log_previous_phase(a, sh, lane, q, prev_start, log_pos, tot);
                 }
+                // has the other side finished already? (the leader has time to look: the update warps are still at work)
+                // (only in phases of several steps: in one-step phases - the V1-scale network - the other side is never done
+                // that early, and the look made this warp late for the update warps: 19.6 against 17.4 ms)
+                if (it == 0u) early_look(sh, p, cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, s + len < a.n_steps, sync_dead || a.half < 2u);
                 // then, once every update warp of the block has finished the phase, the block's own spikes
                 asm volatile("barrier.sync 3, %0;" ::"r"(n_bar3) : "memory");
                 queue_block_spikes(a, sh, L, tag, par, slot, it, n_it);
@@ -780,8 +828,8 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
             if (a.profile && lane == 0u) hist_add(a, input_role ? 1u : 2u, gtimer() - t_warp);
             if (input_role)
-                side_handover<MULTI>(a, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, 2, n_prod_threads, false,
-                              s + len < a.n_steps, sync_dead);
+                prod_handover<MULTI>(a, sh, p, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, n_prod_threads, it == 0u,
+                                     sync_dead);
             else
                 side_handover<MULTI>(a, cnt_cons + (p & 3u), cnt_prod + (p & 3u), (p / 4u + 1u) * gridDim.x, 1, n_cons_threads,
                               dtid == 0, true, sync_dead);

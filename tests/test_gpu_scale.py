@@ -140,3 +140,25 @@ def test_trial_batching_shares_the_csr(cabi, oracle, mode):
     assert _first_divergence(st[m], ids[m], s2.astype(np.int64), i2.astype(np.int64)) > 300
     U = eng.state('U')
     assert U.shape == (T * n_pad1,)
+
+
+def test_trial_groups_replay_after_an_overflow(cabi):
+    """Trial batches stepped two trials per launch with a spike log far too small: the chunk in which the log
+    overflowed (in whichever group) starts again from its first step with the log doubled, all groups over; the
+    result is, bit for bit, that of a run with ample lists (weights on a 0.25 pA grid)."""
+    T = 5
+    net = W.c2(n=3000, in_degree=150, n_virtual=150, t_stop_ms=120.0, input_weight=90.0)
+    net.weight = (np.round(net.weight * 4.0) / 4.0).astype(np.float32)
+    roomy = W.build_engine(net, record_vm=False, options=dict(trials=T, pipeline_trials=2, chunk_steps=500))
+    roomy.run(net.n_steps)
+    tight = W.build_engine(net, record_vm=False, options=dict(trials=T, pipeline_trials=2, chunk_steps=500, log_capacity=1024))
+    tight.run(net.n_steps)
+    assert roomy.counter('pipelined') == 1 and tight.counter('pipelined') == 1
+    assert roomy.counter('replays') == 0 and tight.counter('replays') >= 1
+    a, b = roomy.fetch_spikes(), tight.fetch_spikes()
+    assert len(a[0]) > 3000
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    for c in ('events', 'spikes', 'input_spikes', 'steps'):
+        assert roomy.counter(c) == tight.counter(c), c
+    for var in ('U', 'asc0', 'y1_0', 'refr'):
+        assert np.array_equal(roomy.state(var).view(np.uint32), tight.state(var).view(np.uint32)), var
