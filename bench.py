@@ -44,7 +44,7 @@ BYTES_PER_EVENT = 16.0
 # (profiles/glif_update_2M_neurons_ncu_full.md scaled to this network, profiles/propagate_atomic_c2like_100k_ncu_full.md
 # at 12.4 B per event)
 NCU_TRAFFIC_BYTES = {'glif_update': 102.8 * 230924, 'propagate': None, 'persistent_per_step': 5.97e6,
-                     'pipelined_per_step': 3.89e6}
+                     'pipelined_per_step': 3.81e6}
 
 
 def parse_args():

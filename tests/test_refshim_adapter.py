@@ -7,7 +7,7 @@ MultimeterMod code runs as it is. Both adapters drive the same engine class (the
 Engine API, so that this runs without a GPU): what differs between the two runs is only the adapter.
 Compared bit for bit: neurons and their parameters, the edge list handed to the engine (source, target,
 weight, delay, receptor port, in order), virtual-cell spike times, clamp tables, and the spikes / membrane
-report files the modules write. Needs the reference tree (BMTK_REFERENCE, default /root/reference)."""
+report files the modules write. Needs the reference tree (environment variable BMTK_REFERENCE); skipped without it."""
 import gc
 import json
 import os
