@@ -117,25 +117,26 @@ constexpr unsigned int kSyncSpins = 32000000u;   // far longer than the bounded 
 // the barrier is cumulative: it covers the stores and reductions of all threads that arrived.
 template <bool MULTI>
 __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mine, const uint32_t* other, uint32_t target,
-                                              int barrier_id, uint32_t n_threads, bool leader, bool wait, bool& dead) {
-    // barrier.sync, not bar.sync (= barrier.sync.aligned): the leader reaches the second barrier long after the
-    // other lanes of its warp
+                                              int barrier_id, uint32_t n_threads, bool leader_warp, bool wait, bool& dead) {
+    // barrier.sync, not bar.sync (= barrier.sync.aligned): the leader's warp reaches the second barrier long after the
+    // other warps. `leader_warp`: this thread's warp is the side's leader. ALL its lanes poll (one broadcast load): a
+    // wait in which lane 0 polled and the others stood by left the warp split in two for the whole next phase.
     asm volatile("barrier.sync %0, %1;" ::"r"(barrier_id), "r"(n_threads) : "memory");
-    if (leader) {
+    if (leader_warp) {
         // release: cumulative over what the threads that arrived at the barrier have written (a full
         // fence here would also hold up the other role's warps, which are in the middle of their loads)
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
+        if ((threadIdx.x & 31u) == 0u) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
         if (wait && !dead) {
             // plain polling loads (an acquire load per poll would invalidate the SM's L1 under the other
             // role's feet every time), one acquire load once the count is there
             unsigned int spins = 0;
             while ((int32_t)(*reinterpret_cast<const volatile uint32_t*>(other) - target) < 0) {
                 if (++spins > kSyncSpins) {
-                    atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
                     dead = true;
                     break;
                 }
             }
+            if (dead && (threadIdx.x & 31u) == 0u) atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
             uint32_t v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
         }
@@ -151,20 +152,20 @@ __device__ __forceinline__ void side_handover(const PersistArgs& a, uint32_t* mi
 // threads leave after ONE barrier and only the leader stays to publish the block.
 template <bool MULTI>
 __device__ __forceinline__ void prod_handover(const PersistArgs& a, PipeShared& sh, uint32_t p, uint32_t* mine, const uint32_t* other,
-                                              uint32_t target, uint32_t n_threads, bool leader, bool& dead) {
+                                              uint32_t target, uint32_t n_threads, bool leader_warp, bool& dead) {
     asm volatile("barrier.sync 2, %0;" ::"r"(n_threads) : "memory");
     const bool done = *reinterpret_cast<volatile uint32_t*>(&sh.early[p & 1u]) != 0u;   // written before the barrier
-    if (leader) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
+    if (leader_warp && (threadIdx.x & 31u) == 0u) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(mine) : "memory");
     if (!done) {
-        if (leader && !dead) {
+        if (leader_warp && !dead) {   // all lanes of the leader's warp: see side_handover
             unsigned int spins = 0;
             while ((int32_t)(*reinterpret_cast<const volatile uint32_t*>(other) - target) < 0) {
                 if (++spins > kSyncSpins) {
-                    atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
                     dead = true;
                     break;
                 }
             }
+            if (dead && (threadIdx.x & 31u) == 0u) atomicOr(&a.ctl->error_flags, kErrSyncTimeout);
             uint32_t v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
         }
@@ -174,6 +175,7 @@ __device__ __forceinline__ void prod_handover(const PersistArgs& a, PipeShared& 
 
 // The leader's early look (a few polls at most: it must not be late for the update warps).
 __device__ __forceinline__ void early_look(PipeShared& sh, uint32_t p, const uint32_t* other, uint32_t target, bool wait, bool dead) {
+    // (called by all lanes of the leader's warp)
     bool done = !wait;   // the last phase of a launch waits for nobody
     if (wait && !dead) {
         for (int tries = 0; tries < 3 && !done; ++tries)
@@ -183,7 +185,7 @@ __device__ __forceinline__ void early_look(PipeShared& sh, uint32_t p, const uin
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(other) : "memory");
         }
     }
-    *reinterpret_cast<volatile uint32_t*>(&sh.early[p & 1u]) = done ? 1u : 0u;
+    if ((threadIdx.x & 31u) == 0u) *reinterpret_cast<volatile uint32_t*>(&sh.early[p & 1u]) = done ? 1u : 0u;
 }
 
 // Option phase_timers: every warp adds the time from the start of its phase to the moment it reaches the hand-over
@@ -373,21 +375,29 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, Stager& sg,
     unsigned long long events = 0ull;
     uint32_t my_n = 0;
     const unsigned long long t_in = a.profile ? gtimer() : 0ull;
-    if (lane < a.n_ranks && lane != a.rank && !dead) {
-        const u64* p = xp_cnt(xp, k, lane, blockIdx.x);
+    {
+        // every lane stays in the loop until all the lanes with a rank to wait for have their word (a wait that only
+        // some lanes of a warp spin in can leave the warp split for what follows)
+        const bool need = lane < a.n_ranks && lane != a.rank && !dead;
+        const u64* p = xp_cnt(xp, k, need ? lane : a.rank, blockIdx.x);
+        bool have = !need;
+        u64 cw = 0;
         unsigned int spins = 0;
-        u64 cw;
-        while ((uint32_t)((cw = ld_word(p)) >> 32) != tag) {
+        for (;;) {
+            if (!have) {
+                cw = ld_word(p);
+                have = (uint32_t)(cw >> 32) == tag;
+            }
+            if (__all_sync(0xffffffffu, have)) break;
             if (++spins > kWaitSpins) {
-                atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                if (!have) atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
                 dead = true;
                 break;
             }
             __nanosleep(50);
         }
-        if ((uint32_t)(cw >> 32) == tag) my_n = min((uint32_t)cw, kXPipeSeg);
+        if (need && have) my_n = min((uint32_t)cw, kXPipeSeg);
     }
-    dead = __any_sync(0xffffffffu, dead);
     const unsigned long long t_counts = a.profile ? gtimer() : 0ull;
     // exclusive prefix of the ranks' counts over the lanes
     uint32_t incl = my_n;
@@ -405,11 +415,11 @@ __device__ __forceinline__ void deliver_remote(const PersistArgs& a, Stager& sg,
         const uint32_t i = j - __shfl_sync(0xffffffffu, my_off, r);
         const u64* ent = xp_ent(xp, k, (uint32_t)r, blockIdx.x, a.n_ranks, gridDim.x);
         u64 e = 0;
-        if (lane == 0) {
-            unsigned int spins = 0;
+        {
+            unsigned int spins = 0;   // all lanes read the entry's word (a broadcast)
             while ((uint32_t)((e = ld_word(ent + i)) >> 32) != tag) {
                 if (++spins > kWaitSpins) {
-                    atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
+                    if (lane == 0) atomicOr(&a.ctl->error_flags, kErrExchangeTimeout);
                     break;
                 }
                 __nanosleep(50);
@@ -801,7 +811,7 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
                 // has the other side finished already? (the leader has time to look: the update warps are still at work)
                 // (only in phases of several steps: in one-step phases - the V1-scale network - the other side is never done
                 // that early, and the look made this warp late for the update warps: 19.6 against 17.4 ms)
-                if (it == 0u) early_look(sh, p, cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, s + len < a.n_steps, sync_dead || a.half < 2u);
+                if (it < 32u) early_look(sh, p, cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, s + len < a.n_steps, sync_dead || a.half < 2u);
                 // then, once every update warp of the block has finished the phase, the block's own spikes
                 asm volatile("barrier.sync 3, %0;" ::"r"(n_bar3) : "memory");
                 queue_block_spikes(a, sh, L, tag, par, slot, it, n_it);
@@ -828,11 +838,11 @@ __global__ void __launch_bounds__(BT, 1) pipelined_kernel(const PersistArgs a) {
             const unsigned long long t_work = timer_d ? gtimer() : 0ull;
             if (a.profile && lane == 0u) hist_add(a, input_role ? 1u : 2u, gtimer() - t_warp);
             if (input_role)
-                prod_handover<MULTI>(a, sh, p, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, n_prod_threads, it == 0u,
+                prod_handover<MULTI>(a, sh, p, cnt_prod + (p & 3u), cnt_cons + (p & 3u), (p / 4u + 1u) * gridDim.x, n_prod_threads, it < 32u,
                                      sync_dead);
             else
                 side_handover<MULTI>(a, cnt_cons + (p & 3u), cnt_prod + (p & 3u), (p / 4u + 1u) * gridDim.x, 1, n_cons_threads,
-                              dtid == 0, true, sync_dead);
+                              dwarp == 0u, true, sync_dead);
             if (timer_d) {
                 const unsigned long long t_end = gtimer();
                 acc_work += t_end - t_mark;   // the whole phase; acc_wait is the part spent in the hand-over
