@@ -1,7 +1,7 @@
 // Pipelined persistent kernel: neuron update and spike delivery run CONCURRENTLY on every SM.
 //
-// One block of 20 warps per SM stays resident for a whole chunk of steps (cooperative launch, so that
-// all blocks are co-resident). The first warps ("update warps", as many as the network needs at 128
+// One block of 20 warps per SM (12 where that is enough: more registers a thread, no spills, packed arithmetic in the
+// update) stays resident for a whole chunk of steps (cooperative launch, so that all blocks are co-resident). The first warps ("update warps", as many as the network needs at 128
 // neurons per warp) own four neurons per thread, state in registers for the whole launch; one or more
 // "input warps" draw the Poisson cells / pick up the replayed virtual spikes and queue the block's own
 // spikes; with several ranks one "sender warp" stores the block's spikes into the other ranks' exchange
@@ -10,7 +10,7 @@
 //   * the update warps run the phase's h steps back to back (ring slot in, state update, slot
 //     cleared where it received input); a firing lane only appends the spike to a shared-memory list;
 //   * the input warps add the chunks of the phase's input spikes to the block's segment of the phase's
-//     chunk list (descriptors {first entry, length, ring slot of emission, phase tag}, at most 256 CSR
+//     chunk list (descriptors {first entry, length, ring slot of emission | trial, phase tag}, at most 384 CSR
 //     entries each, at positions from a SHARED-memory counter), write the spike log of phase p-1 and,
 //     once the update warps have arrived at their named barrier, cut the rows of the block's spiking
 //     neurons into chunks as well;
@@ -28,6 +28,8 @@
 // left: the update + input warps of phase p+1 wait for the chunk warps of phase p of all blocks, the
 // chunk warps of phase p+1 for the update + input warps of phase p of all blocks (side_handover).
 // Lists rotate over three buffers: written in phase p, read in p+1, cleared in p+2.
+// With several trials over one CSR a launch steps the cells of a few whole trials (PersistArgs::cell0, n_cells); the
+// launches of a chunk of steps follow one another over the trials.
 //
 // Replaces NEST's update/deliver cycle inside nest.Simulate (bmtk/simulator/pointnet/pointsimulator.py:166).
 #include <cooperative_groups.h>
@@ -41,9 +43,9 @@ namespace cg = cooperative_groups;
 
 namespace bmtk {
 
-// A block has 20 warps (640 threads, 96 registers each). The first PersistArgs::upd_warps of them are
-// update warps - as many as the network needs at 128 neurons per warp, at most 16 - and the rest
-// deliver: 13 + 7 for 230 924 neurons on 148 SMs, 3 + 17 for 50 000.
+// A block has 20 warps (640 threads, 96 registers each) or 12 (384 threads, up to 168 registers). The first
+// PersistArgs::upd_warps of them are update warps - as many as the network needs at 128 neurons per warp, at most
+// 16 - and the rest deliver: 13 + 7 of 20 for 230 924 neurons on 148 SMs, 3 + 9 of 12 for 50 000.
 constexpr int kBT = 640;            // threads of a block: 20 warps (96 registers a thread), or ...
 constexpr int kBTSmall = 384;       // ... 12 warps (up to 168 registers: the update runs without spills) where they are enough
 constexpr int kWarps = kBT / 32;
