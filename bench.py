@@ -97,25 +97,37 @@ def peaks():
 
 
 class ClockSampler(object):
-    """nvidia-smi clocks and throttle reasons sampled every 100 ms during the timed region."""
-    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+    """nvidia-smi clocks and throttle reasons sampled every 20 ms. The sampler is started (and has printed its first
+    line) before the timed region begins; begin() / stop() bracket the region and only the samples whose time
+    stamp lies inside it are reported (`window`: "timed region"). A region too short to hold a sample reports the
+    samples nearest to it instead and says so."""
+    Q = ('timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
          'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
          'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
     def __init__(self, gpu_index):
         self.f = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
         self.p = None
+        self.t0 = self.t1 = None
         try:
             self.p = subprocess.Popen(['nvidia-smi', '-i', str(gpu_index), '--query-gpu=' + self.Q,
-                                       '--format=csv,noheader,nounits', '-lms', '100'], stdout=self.f,
+                                       '--format=csv,noheader,nounits', '-lms', '20'], stdout=self.f,
                                       stderr=subprocess.DEVNULL)
         except OSError:
-            pass
+            return
+        t = time.time()
+        while time.time() - t < 2.0 and os.path.getsize(self.f.name) == 0:    # until the first sample is there
+            time.sleep(0.01)
+
+    def begin(self):
+        self.t0 = time.time()
 
     def stop(self):
+        self.t1 = time.time()
         out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
         if self.p is None:
             return out
+        time.sleep(0.03)   # one more sample, in case the region was shorter than the period
         self.p.terminate()
         try:
             self.p.wait(timeout=5)
@@ -123,24 +135,32 @@ class ClockSampler(object):
             self.p.kill()
         self.f.flush()
         self.f.seek(0)
-        sm, mx, reasons, pw = [], [], set(), []
+        import datetime
+        rows = []
         names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
         for line in self.f.read().splitlines():
             c = [x.strip() for x in line.split(',')]
             if len(c) < 9:
                 continue
             try:
-                sm.append(float(c[1])); mx.append(float(c[2])); pw.append(float(c[3]))
+                ts = datetime.datetime.strptime(c[0], '%Y/%m/%d %H:%M:%S.%f').timestamp()
+                rows.append((ts, float(c[1]), float(c[2]), float(c[3]),
+                             [nm for nm, v in zip(names, c[5:9]) if v.lower().startswith('active')]))
             except ValueError:
                 continue
-            for nm, v in zip(names, c[5:9]):
-                if v.lower().startswith('active'):
-                    reasons.add(nm)
         self.f.close()
         os.unlink(self.f.name)
-        if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
-                       samples=len(sm), power_w_max=float(max(pw)))
+        t0 = self.t0 if self.t0 is not None else 0.0
+        inside = [r for r in rows if t0 <= r[0] <= self.t1]
+        window = 'timed region'
+        if not inside and rows:
+            mid = 0.5 * (t0 + self.t1)
+            inside = sorted(rows, key=lambda r: abs(r[0] - mid))[:2]
+            window = 'nearest samples (the timed region was shorter than the sampling period)'
+        if inside:
+            out.update(sm_mhz=float(np.median([r[1] for r in inside])), sm_max_mhz=float(max(r[2] for r in inside)),
+                       reasons=sorted(set(x for r in inside for x in r[4])), samples=len(inside),
+                       power_w_max=float(max(r[3] for r in inside)), window=window)
         return out
 
 
@@ -341,9 +361,11 @@ def main():
         n_warm = max(n_warm, len(sp[0]))
     # the timed launches leave their spikes in the host store: pin it before the clock starts
     eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     torch.cuda.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.begin()
     ev0, sp0, l0 = eng.counter('events'), eng.counter('spikes'), eng.counter('launches')
     eng.mark(0)
     w0 = time.time()
@@ -591,9 +613,11 @@ def trial_sweep(args, torch, dist, W, world, rank, local_rank, dev, barrier, red
             first_trial = (sp[0][m].copy(), sp[1][m].copy())
         n_warm = max(n_warm, len(sp[0]))
     eng.set_option('spike_store_reserve', int(n_warm * 1.25 + 1e5) * args.steps)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     torch.cuda.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.begin()
     ev0, sp0, l0 = eng.counter('events'), eng.counter('spikes'), eng.counter('launches')
     eng.mark(0)
     for _ in range(args.steps):
@@ -691,6 +715,8 @@ def small_config(args, torch, dist, W, world, rank, local_rank, dev, barrier, re
             first = (sp[0].copy(), sp[1].copy())
     eng.set_option('spike_store_reserve', int(len(first[0]) * 1.25 + 1e5))
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.begin()   # (the region of these legs includes the reload of the rest state before every step)
     dev_ms, wall_ms, events, spikes, launches, d2h = 0.0, 0.0, 0, 0, 0, 0
     for _ in range(args.steps):
         eng.load_state(ck)
